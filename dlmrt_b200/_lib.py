@@ -1,0 +1,87 @@
+"""ctypes binding of libdlmrt_b200.so (include/dlmrt_b200.h). There is no fallback: a missing or unbuildable
+library is an ImportError, and a non-zero return code is an exception."""
+
+import ctypes as C
+from pathlib import Path
+
+MAX_WORLD = 8
+EPOCH_SLOTS = 256
+STATUS_WORDS = 4
+FUSED_MAX_N = 3072
+
+OK, ERR_SHAPE, ERR_ALIGN, ERR_WORLD, ERR_NULL, ERR_GRID, ERR_CUDA, ERR_WORKSPACE, ERR_TIMEOUT, ERR_ARCH = \
+    0, -1, -2, -3, -4, -5, -6, -7, -8, -9
+REDUCE, REDUCE_NORM, REDUCE_NORM_RESIDUAL = 0, 1, 2
+
+LIB_PATH = Path(__file__).resolve().parent / "libdlmrt_b200.so"
+
+
+class DlmComm(C.Structure):
+    _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("rows", C.c_int32), ("n", C.c_int32),
+                ("mode", C.c_int32), ("eps", C.c_float), ("scale", C.c_float),
+                ("recv", C.c_void_p * MAX_WORLD), ("out", C.c_void_p), ("out_mc", C.c_void_p),
+                ("out_peers", C.c_void_p * MAX_WORLD), ("rearm", C.c_void_p), ("rearm_bytes", C.c_int64),
+                ("epochs", C.c_void_p), ("h", C.c_void_p), ("weight", C.c_void_p), ("status", C.c_void_p),
+                ("stamps", C.c_void_p), ("timeout_ns", C.c_int64), ("pdl", C.c_int32), ("max_ctas", C.c_int32)]
+
+
+class DlmGemm(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("w", C.c_void_p), ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
+                ("ldx", C.c_int64), ("ldw", C.c_int64), ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
+                ("splits", C.c_int32)]
+
+
+class DlmStatus(C.Structure):
+    _fields_ = [("code", C.c_int32), ("block", C.c_int32), ("slot", C.c_int32), ("phase", C.c_int32),
+                ("epoch", C.c_int32)]
+
+
+class DlmError(RuntimeError):
+    """A DLM_ERR_* return code from the library; `.code` holds it."""
+
+    def __init__(self, code, where):
+        self.code = code
+        detail = f" (cudaError {lib().dlm_last_cuda_error()})" if code == ERR_CUDA else ""
+        super().__init__(f"{where}: {lib().dlm_strerror(code).decode()}{detail}")
+
+
+_lib = None
+
+SIGNATURES = {
+    "dlm_reduce_bf16": (C.c_int, [C.c_void_p, C.POINTER(DlmComm), C.c_void_p]),
+    "dlm_reduce_bf16_loopback": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(DlmComm), C.c_int, C.c_void_p]),
+    "dlm_gemm_bf16": (C.c_int, [C.POINTER(DlmGemm), C.c_void_p, C.c_int64, C.c_int, C.c_void_p]),
+    "dlm_rowpar_bf16": (C.c_int, [C.POINTER(DlmGemm), C.POINTER(DlmComm), C.c_void_p]),
+    "dlm_rowpar_bf16_loopback": (C.c_int, [C.POINTER(DlmGemm), C.POINTER(DlmComm), C.c_int, C.c_void_p]),
+    "dlm_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
+    "dlm_choose_splits": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int]),
+    "dlm_status_read": (C.c_int, [C.c_void_p, C.POINTER(DlmStatus), C.c_void_p]),
+    "dlm_abi_check": (C.c_int, [C.c_size_t, C.c_size_t, C.c_size_t]),
+    "dlm_strerror": (C.c_char_p, [C.c_int]),
+    "dlm_last_cuda_error": (C.c_int, []),
+    "dlm_device_sms": (C.c_int, []),
+    "dlm_device_arch": (C.c_int, []),
+    "dlm_launch_count": (C.c_int64, []),
+}
+
+
+def lib():
+    """The loaded library; raises ImportError when it has not been built (python -m dlmrt_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise ImportError(f"{LIB_PATH} is missing: build it with `python -m dlmrt_b200.build` "
+                              "(there is no CPU or PyTorch fallback for this path)")
+        handle = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        if handle.dlm_abi_check(C.sizeof(DlmComm), C.sizeof(DlmGemm), C.sizeof(DlmStatus)) != OK:
+            raise ImportError(f"{LIB_PATH}: struct layout differs from this binding; rebuild the library")
+        _lib = handle
+    return _lib
+
+
+def check(code, where):
+    if code != OK:
+        raise DlmError(code, where)

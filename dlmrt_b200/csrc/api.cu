@@ -1,0 +1,362 @@
+// extern "C" boundary of libdlmrt_b200.so (include/dlmrt_b200.h): argument checks, tensor-map construction, launch.
+// Mirrors the host checks of the reference's launch<> (dlmrt/ops/csrc/tp_comm.cu:282-287) as return codes.
+#include <cstring>
+
+#include "../../include/dlmrt_b200.h"
+#include "kernels.cuh"
+
+using namespace dlm;
+
+namespace {
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int cuda_fail(cudaError_t err) {
+    g_last_cuda_error = static_cast<int>(err);
+    (void)cudaGetLastError();
+    return DLM_ERR_CUDA;
+}
+
+struct DeviceInfo {
+    int device = -1, sms = 0, major = 0;
+};
+
+int device_info(DeviceInfo* out) {
+    static DeviceInfo cache[64];
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return cuda_fail(err);
+    if (dev < 0 || dev >= 64) return DLM_ERR_ARCH;
+    if (cache[dev].device != dev) {
+        cudaDeviceProp prop;
+        err = cudaGetDeviceProperties(&prop, dev);
+        if (err != cudaSuccess) return cuda_fail(err);
+        cache[dev].device = dev;
+        cache[dev].sms = prop.multiProcessorCount;
+        cache[dev].major = prop.major;
+    }
+    *out = cache[dev];
+    return out->major == 10 ? DLM_OK : DLM_ERR_ARCH;
+}
+
+int check_comm(const DlmComm* c) {
+    if (c == nullptr) return DLM_ERR_NULL;
+    if (c->world < 1 || c->world > DLM_MAX_WORLD || c->rank < 0 || c->rank >= c->world) return DLM_ERR_WORLD;
+    if (c->rows <= 0 || c->rows % c->world) return DLM_ERR_WORLD;
+    if (c->n <= 0 || c->n % 256 || c->n > DLM_MAX_N) return DLM_ERR_SHAPE;
+    if (c->mode < DLM_REDUCE || c->mode > DLM_REDUCE_NORM_RESIDUAL) return DLM_ERR_SHAPE;
+    if (c->out == nullptr || c->epochs == nullptr) return DLM_ERR_NULL;
+    for (int s = 0; s < c->world; ++s) {
+        if (c->recv[s] == nullptr) return DLM_ERR_NULL;
+        if (!aligned16(c->recv[s])) return DLM_ERR_ALIGN;
+        if (c->out_mc == nullptr) {
+            if (c->out_peers[s] == nullptr) return DLM_ERR_NULL;
+            if (!aligned16(c->out_peers[s])) return DLM_ERR_ALIGN;
+        }
+    }
+    if (c->mode != DLM_REDUCE && c->weight == nullptr) return DLM_ERR_NULL;
+    if (c->mode == DLM_REDUCE_NORM_RESIDUAL && c->h == nullptr) return DLM_ERR_NULL;
+    if (!aligned16(c->out) || !aligned16(c->out_mc) || !aligned16(c->rearm) || !aligned16(c->h) || !aligned16(c->weight))
+        return DLM_ERR_ALIGN;
+    if (c->rearm_bytes < 0 || c->rearm_bytes % 16 || (c->rearm == nullptr && c->rearm_bytes != 0)) return DLM_ERR_ALIGN;
+    if (c->rearm_bytes / 16 > 0x7FFFFFFF || c->timeout_ns < 0 || c->max_ctas < 0) return DLM_ERR_SHAPE;
+    return DLM_OK;
+}
+
+void fill_comm(CommDev* d, const DlmComm* c) {
+    std::memset(d, 0, sizeof(*d));
+    for (int s = 0; s < c->world; ++s) {
+        d->recv[s] = static_cast<__nv_bfloat16*>(c->recv[s]);
+        d->out_peers[s] = static_cast<__nv_bfloat16*>(c->out_peers[s]);
+    }
+    d->out = static_cast<__nv_bfloat16*>(c->out);
+    d->out_mc = static_cast<__nv_bfloat16*>(c->out_mc);
+    d->rearm = static_cast<__nv_bfloat16*>(c->rearm);
+    d->rearm_vecs = static_cast<int>(c->rearm_bytes / 16);
+    d->h = static_cast<__nv_bfloat16*>(c->h);
+    d->weight = static_cast<const __nv_bfloat16*>(c->weight);
+    d->epochs = c->epochs;
+    d->status = c->status;
+    d->stamps = reinterpret_cast<long long*>(c->stamps);
+    d->timeout_ns = c->timeout_ns > 0 ? c->timeout_ns : 2000000000ll;
+    d->rank = c->rank;
+    d->world = c->world;
+    d->rows = c->rows;
+    d->n = c->n;
+    d->R = c->rows / c->world;
+    d->mode = c->mode;
+    d->eps = c->eps;
+    d->scale = c->scale;
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(p);
+        else
+            (void)cudaGetLastError();
+    }
+    return fn;
+}
+
+// A [rows, cols] BF16 row-major matrix with leading dimension ld, read in boxes of 64 columns x box_rows rows with
+// the 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* base, int rows, int cols, long long ld, int box_rows) {
+    EncodeTiled fn = encode_tiled();
+    if (fn == nullptr) return DLM_ERR_CUDA;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        g_last_cuda_error = 100000 + static_cast<int>(r);
+        return DLM_ERR_CUDA;
+    }
+    return DLM_OK;
+}
+
+int choose_splits(int m, int n, int k, int max_ctas, int sms) {
+    (void)m;
+    const int avail = max_ctas > 0 && max_ctas < sms ? max_ctas : sms;
+    const int tiles = n / kBlockF, nkb = k / kBlockK;
+    int s = avail / tiles;
+    const int by_k = nkb / 4 > 0 ? nkb / 4 : 1;  // at least four k-blocks per CTA: below that the partial tiles cost more than they save
+    if (s > by_k) s = by_k;
+    if (s > kMaxSplits) s = kMaxSplits;
+    if (s < 1) s = 1;
+    return s;
+}
+
+int check_gemm(const DlmGemm* g) {
+    if (g == nullptr) return DLM_ERR_NULL;
+    if (g->x == nullptr || g->w == nullptr || g->workspace == nullptr) return DLM_ERR_NULL;
+    if (g->m < 16 || g->m > DLM_MAX_M || g->m % 16) return DLM_ERR_SHAPE;
+    if (g->n < kBlockF || g->n % kBlockF || g->k < kBlockK || g->k % kBlockK) return DLM_ERR_SHAPE;
+    if (g->n / kBlockF > 64) return DLM_ERR_SHAPE;
+    if (g->ldx < g->k || g->ldw < g->k || g->ldx % 8 || g->ldw % 8) return DLM_ERR_ALIGN;
+    if (!aligned16(g->x) || !aligned16(g->w) || (reinterpret_cast<uintptr_t>(g->workspace) & 255)) return DLM_ERR_ALIGN;
+    if (g->splits < 0 || g->splits > kMaxSplits) return DLM_ERR_SHAPE;
+    return DLM_OK;
+}
+
+// Fills the device-side GEMM block; returns the per-rank grid in *grid.
+int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid) {
+    std::memset(d, 0, sizeof(*d));
+    int rc = make_map(&d->tm_w, g->w, g->n, g->k, g->ldw, kBlockF);
+    if (rc == DLM_OK) rc = make_map(&d->tm_x, g->x, g->m, g->k, g->ldx, g->m);
+    if (rc != DLM_OK) return rc;
+    const int tiles = g->n / kBlockF, nkb = g->k / kBlockK;
+    int splits = g->splits > 0 ? g->splits : choose_splits(g->m, g->n, g->k, max_ctas, sms);
+    if (splits > nkb) splits = nkb;
+    const int avail = max_ctas > 0 && max_ctas < sms ? max_ctas : sms;
+    if (tiles * splits > avail) return DLM_ERR_GRID;
+    const size_t need = 256 + static_cast<size_t>(splits) * g->m * g->n * sizeof(float);
+    if (g->workspace_bytes < static_cast<int64_t>(need)) return DLM_ERR_WORKSPACE;
+    d->counters = static_cast<int*>(g->workspace);
+    d->ws = reinterpret_cast<float*>(static_cast<char*>(g->workspace) + 256);
+    d->m = g->m;
+    d->n = g->n;
+    d->k = g->k;
+    d->splits = splits;
+    d->stages = rowpar_stages(g->m);
+    *grid = tiles * splits;
+    return DLM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int dlm_reduce_bf16(const void* partial, const DlmComm* comm, dlm_stream_t stream) {
+    int rc = check_comm(comm);
+    if (rc != DLM_OK) return rc;
+    if (partial == nullptr) return DLM_ERR_NULL;
+    if (!aligned16(partial)) return DLM_ERR_ALIGN;
+    DeviceInfo info;
+    rc = device_info(&info);
+    if (rc != DLM_OK) return rc;
+    ReduceParams<1> p;
+    fill_comm(&p.c[0], comm);
+    p.partial[0] = static_cast<const __nv_bfloat16*>(partial);
+    int grid = comm->max_ctas > 0 && comm->max_ctas < info.sms ? comm->max_ctas : info.sms;
+    if (grid > DLM_EPOCH_SLOTS) grid = DLM_EPOCH_SLOTS;
+    return launch_reduce(p, grid, comm->n / kVec, {static_cast<cudaStream_t>(stream), comm->pdl != 0, false});
+}
+
+int dlm_reduce_bf16_loopback(const void* const* partial, const DlmComm* comm, int nranks, dlm_stream_t stream) {
+    DeviceInfo info;
+    int rc = device_info(&info);
+    if (rc != DLM_OK) return rc;
+    if (partial == nullptr || comm == nullptr) return DLM_ERR_NULL;
+    if (nranks < 1 || nranks > DLM_MAX_WORLD) return DLM_ERR_WORLD;
+    ReduceParams<kMaxWorld> p;
+    std::memset(&p, 0, sizeof(p));
+    for (int i = 0; i < nranks; ++i) {
+        rc = check_comm(&comm[i]);
+        if (rc != DLM_OK) return rc;
+        if (comm[i].world != nranks || comm[i].rank != i || comm[i].out_mc != nullptr) return DLM_ERR_WORLD;
+        if (comm[i].rows != comm[0].rows || comm[i].n != comm[0].n) return DLM_ERR_SHAPE;
+        if (partial[i] == nullptr) return DLM_ERR_NULL;
+        if (!aligned16(partial[i])) return DLM_ERR_ALIGN;
+        fill_comm(&p.c[i], &comm[i]);
+        p.partial[i] = static_cast<const __nv_bfloat16*>(partial[i]);
+    }
+    int grid = info.sms / nranks;
+    if (comm[0].max_ctas > 0 && comm[0].max_ctas < grid) grid = comm[0].max_ctas;
+    if (grid < 1) return DLM_ERR_GRID;
+    return launch_reduce_loopback(p, grid, nranks, comm[0].n / kVec, {static_cast<cudaStream_t>(stream), false, true});
+}
+
+int dlm_gemm_bf16(const DlmGemm* gemm, void* out, int64_t ldo, int pdl, dlm_stream_t stream) {
+    int rc = check_gemm(gemm);
+    if (rc != DLM_OK) return rc;
+    if (out == nullptr) return DLM_ERR_NULL;
+    if (!aligned16(out) || ldo < gemm->n || ldo % 8) return DLM_ERR_ALIGN;
+    DeviceInfo info;
+    rc = device_info(&info);
+    if (rc != DLM_OK) return rc;
+    RowparParams<1> p;
+    std::memset(&p, 0, sizeof(p));
+    int grid = 0;
+    rc = fill_gemm(&p.g[0], gemm, 0, info.sms, &grid);
+    if (rc != DLM_OK) return rc;
+    p.g[0].out = static_cast<__nv_bfloat16*>(out);
+    p.g[0].ldo = ldo;
+    p.fused = 0;
+    return launch_rowpar(p, grid, {static_cast<cudaStream_t>(stream), pdl != 0, false});
+}
+
+static int check_pair(const DlmGemm* gemm, const DlmComm* comm) {
+    int rc = check_gemm(gemm);
+    if (rc == DLM_OK) rc = check_comm(comm);
+    if (rc != DLM_OK) return rc;
+    if (gemm->m != comm->rows || gemm->n != comm->n || comm->n > DLM_FUSED_MAX_N) return DLM_ERR_SHAPE;
+    return DLM_OK;
+}
+
+int dlm_rowpar_bf16(const DlmGemm* gemm, const DlmComm* comm, dlm_stream_t stream) {
+    int rc = check_pair(gemm, comm);
+    if (rc != DLM_OK) return rc;
+    DeviceInfo info;
+    rc = device_info(&info);
+    if (rc != DLM_OK) return rc;
+    RowparParams<1> p;
+    std::memset(&p, 0, sizeof(p));
+    int grid = 0;
+    rc = fill_gemm(&p.g[0], gemm, comm->max_ctas, info.sms, &grid);
+    if (rc != DLM_OK) return rc;
+    fill_comm(&p.c[0], comm);
+    p.fused = 1;
+    return launch_rowpar(p, grid, {static_cast<cudaStream_t>(stream), comm->pdl != 0, false});
+}
+
+int dlm_rowpar_bf16_loopback(const DlmGemm* gemm, const DlmComm* comm, int nranks, dlm_stream_t stream) {
+    DeviceInfo info;
+    int rc = device_info(&info);
+    if (rc != DLM_OK) return rc;
+    if (gemm == nullptr || comm == nullptr) return DLM_ERR_NULL;
+    if (nranks < 1 || nranks > DLM_MAX_WORLD) return DLM_ERR_WORLD;
+    RowparParams<kMaxWorld> p;
+    std::memset(&p, 0, sizeof(p));
+    const int per_rank = info.sms / nranks;
+    int grid = 0;
+    for (int i = 0; i < nranks; ++i) {
+        rc = check_pair(&gemm[i], &comm[i]);
+        if (rc != DLM_OK) return rc;
+        if (comm[i].world != nranks || comm[i].rank != i || comm[i].out_mc != nullptr) return DLM_ERR_WORLD;
+        if (gemm[i].m != gemm[0].m || gemm[i].n != gemm[0].n || gemm[i].k != gemm[0].k) return DLM_ERR_SHAPE;
+        int cap = comm[0].max_ctas > 0 && comm[0].max_ctas < per_rank ? comm[0].max_ctas : per_rank;
+        int gi = 0;
+        DlmGemm gg = gemm[i];
+        if (gg.splits == 0) gg.splits = choose_splits(gg.m, gg.n, gg.k, cap, per_rank);
+        rc = fill_gemm(&p.g[i], &gg, cap, per_rank, &gi);
+        if (rc != DLM_OK) return rc;
+        if (i > 0 && gi != grid) return DLM_ERR_SHAPE;
+        grid = gi;
+        fill_comm(&p.c[i], &comm[i]);
+    }
+    p.fused = 1;
+    return launch_rowpar_loopback(p, grid, nranks, {static_cast<cudaStream_t>(stream), false, true});
+}
+
+size_t dlm_workspace_bytes(int m, int n, int k) {
+    (void)k;
+    if (m <= 0 || n <= 0) return 0;
+    return 256 + static_cast<size_t>(kMaxSplits) * static_cast<size_t>(m) * static_cast<size_t>(n) * sizeof(float);
+}
+
+int dlm_choose_splits(int m, int n, int k, int max_ctas) {
+    DeviceInfo info;
+    int sms = 148;
+    if (device_info(&info) == DLM_OK) sms = info.sms;
+    if (n < kBlockF || n % kBlockF || k < kBlockK || k % kBlockK) return DLM_ERR_SHAPE;
+    int s = choose_splits(m, n, k, max_ctas, sms);
+    const int nkb = k / kBlockK;
+    return s > nkb ? nkb : s;
+}
+
+int dlm_status_read(int32_t* device_status, DlmStatus* out, dlm_stream_t stream) {
+    if (device_status == nullptr || out == nullptr) return DLM_ERR_NULL;
+    int32_t host[DLM_STATUS_WORDS];
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t err = cudaMemcpyAsync(host, device_status, sizeof(host), cudaMemcpyDeviceToHost, s);
+    if (err == cudaSuccess) err = cudaMemsetAsync(device_status, 0, sizeof(host), s);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+    if (err != cudaSuccess) return cuda_fail(err);
+    out->code = host[0];
+    out->block = host[1] >> 8;
+    out->slot = host[1] & 0xFF;
+    out->phase = host[2];
+    out->epoch = host[3];
+    return DLM_OK;
+}
+
+int dlm_abi_check(size_t sizeof_comm, size_t sizeof_gemm, size_t sizeof_status) {
+    return sizeof_comm == sizeof(DlmComm) && sizeof_gemm == sizeof(DlmGemm) && sizeof_status == sizeof(DlmStatus)
+               ? DLM_OK
+               : DLM_ERR_SHAPE;
+}
+
+const char* dlm_strerror(int code) {
+    switch (code) {
+        case DLM_OK: return "ok";
+        case DLM_ERR_SHAPE: return "unsupported shape (hidden size a multiple of 256, at most 8192; m a multiple of 16, at most 256; k a multiple of 64)";
+        case DLM_ERR_ALIGN: return "address or leading dimension not 16-byte aligned";
+        case DLM_ERR_WORLD: return "rows must split over ranks; at most 8 ranks; rank within the world";
+        case DLM_ERR_NULL: return "required pointer is null";
+        case DLM_ERR_GRID: return "grid cannot be co-resident on this GPU";
+        case DLM_ERR_CUDA: return "CUDA call failed (dlm_last_cuda_error)";
+        case DLM_ERR_WORKSPACE: return "workspace too small (dlm_workspace_bytes)";
+        case DLM_ERR_TIMEOUT: return "device wait ran out: data from a rank never arrived";
+        case DLM_ERR_ARCH: return "not an sm_100 device";
+        default: return "unknown error";
+    }
+}
+
+int dlm_last_cuda_error(void) { return g_last_cuda_error; }
+
+int dlm_device_sms(void) {
+    DeviceInfo info;
+    const int rc = device_info(&info);
+    return rc == DLM_OK || rc == DLM_ERR_ARCH ? info.sms : 0;
+}
+
+int dlm_device_arch(void) {
+    DeviceInfo info;
+    return device_info(&info) == DLM_OK ? 100 : 0;
+}
+
+int64_t dlm_launch_count(void) { return g_launches; }
+
+}  // extern "C"

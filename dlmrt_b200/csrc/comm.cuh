@@ -1,0 +1,222 @@
+// Device side of the barrier-free tensor-parallel reduction, shared by the stand-alone reduction kernel and by the
+// fused GEMM + reduction kernels.
+//
+// Protocol (the one dlmrt/ops/csrc/tp_comm.cu:1-22 describes; every rank runs the same code):
+//   push      row s*R + c of this rank's BF16 partial goes into rank s's receive slot [e % 3][rank][c] with plain
+//             16-byte stores over NVLink. The payload is its own flag: slots start filled with 0xFFFF lanes, which
+//             BF16 arithmetic never produces, so a vector has arrived once no lane holds that value.
+//   re-arm    the receive buffer peers write two invocations from now ((e + 2) % 3) and the previous output of this
+//             chain are refilled with the sentinel.
+//   own       the CTA that owns row c polls its `world` slots, sums them in FP32 in rank order from +0.0f, optionally
+//             adds the residual and applies RMSNorm, rounds to BF16 and stores the row into OUT on every rank (one
+//             multimem.st through the NVSwitch, or one store per rank).
+//   collect   every CTA polls the rows of its own OUT copy that correspond to the rows it owned, so OUT is complete on
+//             this rank when the kernel ends.
+// Differences from the reference kernel, by design: there are no dedicated pusher CTAs (every CTA pushes, re-arms,
+// then owns rows, so a fused GEMM's tiles can be pushed by the CTA that produced them); address tables live in
+// kernel parameters; every wait is bounded and reports through status words instead of trapping; invocation
+// counters are kept equal across all DLM_EPOCH_SLOTS entries so kernels of different grid sizes can share them.
+#pragma once
+
+#include "common.cuh"
+
+namespace dlm {
+
+constexpr int kMaxWorld = 8;
+constexpr int kEpochSlots = 256;
+
+enum Mode { kReduce = 0, kReduceNorm = 1, kReduceNormResidual = 2 };
+
+struct CommDev {
+    __nv_bfloat16* recv[kMaxWorld];
+    __nv_bfloat16* out_peers[kMaxWorld];
+    __nv_bfloat16* out;
+    __nv_bfloat16* out_mc;
+    __nv_bfloat16* rearm;
+    __nv_bfloat16* h;
+    const __nv_bfloat16* weight;
+    int* epochs;
+    int* status;
+    long long* stamps;
+    long long timeout_ns;
+    int rearm_vecs;
+    int rank, world, rows, n, R;
+    int mode;
+    float eps, scale;
+};
+
+struct CommCtx {
+    int block, blocks;  // this CTA's index among the CTAs of its rank, and their number
+    int e, buf;         // invocation number and receive buffer e % 3
+    long long deadline;
+    size_t slot_elems, buf_elems;
+};
+
+__device__ __forceinline__ void stamp(const CommDev& c, const CommCtx& x, int phase) {
+    if (c.stamps && threadIdx.x == 0) c.stamps[x.block * 4 + phase] = globaltimer();
+}
+
+__device__ __forceinline__ CommCtx comm_begin(const CommDev& c, int block, int blocks) {
+    CommCtx x;
+    x.block = block;
+    x.blocks = blocks;
+    x.e = c.epochs[block] + 1;
+    x.buf = x.e % 3;
+    x.deadline = globaltimer() + c.timeout_ns;
+    x.slot_elems = static_cast<size_t>(c.R) * c.n;
+    x.buf_elems = static_cast<size_t>(c.world) * x.slot_elems;
+    return x;
+}
+
+// Where row `row` (0 <= row < rows), column `col` of this rank's partial lands: owner rank s = row / R.
+__device__ __forceinline__ __nv_bfloat16* push_address(const CommDev& c, const CommCtx& x, int row, int col) {
+    const int s = row / c.R, r = row - s * c.R;
+    return c.recv[s] + x.buf * x.buf_elems + c.rank * x.slot_elems + static_cast<size_t>(r) * c.n + col;
+}
+
+// Push phase of the stand-alone reduction: the whole partial, spread over all threads of all CTAs of the rank.
+// Consecutive logical rows go to consecutive destinations starting at this rank, so the first stores of all ranks
+// spread over all destinations instead of all landing on rank 0 (tp_comm.cu:154-163).
+__device__ __forceinline__ void push_partial(const CommDev& c, const CommCtx& x, const __nv_bfloat16* partial) {
+    const int vpr = c.n / kVec;
+    const int total = c.rows * vpr;
+    const int stride = x.blocks * blockDim.x;
+    for (int i = x.block * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int l = i / vpr, col = (i - l * vpr) * kVec;
+        const int r = l / c.world, s = (c.rank + l % c.world) % c.world;
+        const int row = s * c.R + r;
+        const uint4 v = *reinterpret_cast<const uint4*>(partial + static_cast<size_t>(row) * c.n + col);
+        store_v4(push_address(c, x, row, col), v);
+    }
+}
+
+// Re-arm the receive buffer peers write in invocation e + 2 and the previous call site's output (over that output's
+// own size: calls on one chain may differ in rows, tp_comm.cu:201-208).
+__device__ __forceinline__ void rearm(const CommDev& c, const CommCtx& x) {
+    const uint4 sentinel = make_uint4(kSentinel, kSentinel, kSentinel, kSentinel);
+    const int stride = x.blocks * blockDim.x;
+    const int first = x.block * blockDim.x + threadIdx.x;
+    __nv_bfloat16* stale = c.recv[c.rank] + ((x.e + 2) % 3) * x.buf_elems;
+    const int total = static_cast<int>(x.buf_elems / kVec);
+    for (int i = first; i < total; i += stride) store_v4(stale + static_cast<size_t>(i) * kVec, sentinel);
+    for (int i = first; i < c.rearm_vecs; i += stride) store_v4(c.rearm + static_cast<size_t>(i) * kVec, sentinel);
+}
+
+// Waits until the 16-byte vectors at base + s * stride (s < world) have all arrived and returns them. Every round
+// issues all pending loads before testing any (one L2 round trip per round, tp_comm.cu:52-54). Returns false when the
+// deadline passed first; the words of slots that did not arrive are then meaningless.
+__device__ __forceinline__ bool poll_all(const __nv_bfloat16* base, size_t stride, int world, uint4 (&v)[kMaxWorld],
+                                         const CommDev& c, const CommCtx& x, int phase) {
+    unsigned pending = (1u << world) - 1;
+    while (true) {
+        const unsigned was = pending;
+#pragma unroll
+        for (int s = 0; s < kMaxWorld; ++s)
+            if (was >> s & 1) v[s] = load_volatile(base + s * stride);
+#pragma unroll
+        for (int s = 0; s < kMaxWorld; ++s)
+            if ((was >> s & 1) && arrived(v[s])) pending &= ~(1u << s);
+        if (!pending) return true;
+        if (globaltimer() > x.deadline) {
+            report(c.status, kErrTimeout, __ffs(pending) - 1, phase, x.e);
+            return false;
+        }
+    }
+}
+
+// Sum over a thread block of (blockDim >= threads) threads of which the first `threads` (a multiple of 32) carry
+// values; the same tree as the reference's block_sum (tp_comm.cu:98-109): butterfly inside each warp, then a
+// butterfly over the warp sums padded with zeros to 32 lanes. All threads of the block must call it.
+__device__ __forceinline__ float block_sum(float x, float* scratch, int threads) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffff, x, o);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) scratch[warp] = x;
+    __syncthreads();
+    x = lane < (threads >> 5) ? scratch[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffff, x, o);
+    __syncthreads();  // scratch is reused by the next row
+    return x;
+}
+
+// Owner phase + collect phase. Thread t < n / 8 holds columns [8t, 8t + 8) of the row being reduced; threads beyond
+// that only take part in the block-wide synchronisation. `scratch` is 32 floats of shared memory.
+template <int MODE>
+__device__ __forceinline__ void own_and_collect(const CommDev& c, const CommCtx& x, float* scratch) {
+    const int t = threadIdx.x;
+    const int threads = c.n / kVec;
+    const bool active = t < threads;
+    const size_t col = static_cast<size_t>(active ? t : 0) * kVec;
+    const __nv_bfloat16* mine = c.recv[c.rank] + x.buf * x.buf_elems;
+    uint4 slots[kMaxWorld];
+    for (int r = x.block; r < c.R; r += x.blocks) {
+        const size_t off = static_cast<size_t>(c.rank * c.R + r) * c.n + col;
+        // Local operands first, so their latency overlaps the wait for the peers (tp_comm.cu:225-228).
+        uint4 hraw = make_uint4(0, 0, 0, 0), wraw = make_uint4(0, 0, 0, 0);
+        if (MODE == kReduceNormResidual && active) hraw = *reinterpret_cast<const uint4*>(c.h + off);
+        if (MODE != kReduce && active) wraw = *reinterpret_cast<const uint4*>(c.weight + col);
+        bool ok = true;
+        if (active) ok = poll_all(mine + static_cast<size_t>(r) * c.n + col, x.slot_elems, c.world, slots, c, x, kPhaseReceive);
+        float v[kVec] = {};
+        if (active) {
+#pragma unroll
+            for (int s = 0; s < kMaxWorld; ++s)
+                if (s < c.world) add_bf16x8(v, slots[s]);
+        }
+        if (MODE != kReduce) {
+            // The reduced sum is rounded to BF16 before the residual add, as an unfused all-reduce would hand it over.
+            const uint4 rounded = pack_bf16x8(v);
+#pragma unroll
+            for (int i = 0; i < kVec; ++i) v[i] = 0.f;
+            add_bf16x8(v, rounded);
+            if (MODE == kReduceNormResidual) {
+                add_bf16x8(v, hraw);
+                if (active && ok) *reinterpret_cast<uint4*>(c.h + off) = pack_bf16x8(v);
+            }
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < kVec; ++i) ss = fmaf(v[i], v[i], ss);
+            if (!active) ss = 0.f;
+            const float rs = rsqrtf(block_sum(ss, scratch, threads) / c.n + c.eps) * c.scale;
+            const __nv_bfloat162* w = reinterpret_cast<const __nv_bfloat162*>(&wraw);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(w[i]);
+                v[2 * i] = v[2 * i] * rs * f.x;
+                v[2 * i + 1] = v[2 * i + 1] * rs * f.y;
+            }
+        }
+        // Broadcast the row: one multicast store, or one store per rank. A row whose inputs never arrived is not
+        // broadcast, so every rank's collect phase reports the failure too.
+        if (active && ok) {
+            const uint4 packed = pack_bf16x8(v);
+            if (c.out_mc) {
+                multicast_store(c.out_mc + off, packed);
+            } else {
+                for (int s = 0; s < c.world; ++s) store_v4(c.out_peers[s] + off, packed);
+            }
+        }
+    }
+    stamp(c, x, 2);
+    // Collect: rows s * R + r of this rank's OUT copy, from every owner s.
+    if (active) {
+        for (int r = x.block; r < c.R; r += x.blocks)
+            if (!poll_all(c.out + static_cast<size_t>(r) * c.n + col, x.slot_elems, c.world, slots, c, x, kPhaseOut)) break;
+    }
+    stamp(c, x, 3);
+}
+
+__device__ __forceinline__ void own_and_collect(const CommDev& c, const CommCtx& x, float* scratch) {
+    if (c.mode == kReduce) own_and_collect<kReduce>(c, x, scratch);
+    else if (c.mode == kReduceNorm) own_and_collect<kReduceNorm>(c, x, scratch);
+    else own_and_collect<kReduceNormResidual>(c, x, scratch);
+}
+
+// Advance the invocation counters: every entry of the table ends equal to e, whatever the grid size.
+__device__ __forceinline__ void comm_end(const CommDev& c, const CommCtx& x) {
+    if (threadIdx.x == 0)
+        for (int j = x.block; j < kEpochSlots; j += x.blocks) c.epochs[j] = x.e;
+}
+
+}  // namespace dlm

@@ -1,0 +1,59 @@
+// Kernel parameter blocks and host launchers shared between the .cu files of the library.
+#pragma once
+
+#include <cuda.h>
+
+#include "comm.cuh"
+
+namespace dlm {
+
+constexpr int kFusedThreads = 384;  // 12 warps: TMA producer, MMA issuer, TMEM allocator, spare, 8 epilogue warps
+constexpr int kBlockF = 128;        // weight rows (output features) per tile: the MMA's M
+constexpr int kBlockK = 64;         // BF16 per k-block: one 128-byte swizzled row
+constexpr int kUmmaK = 16;          // K of one tcgen05.mma kind::f16
+constexpr int kMaxSplits = 8;
+constexpr int kMaxStages = 8;
+constexpr int kSmemBudget = 200 * 1024;
+
+// The GEMM half of one rank. `out` is used by the plain GEMM (no communication) only.
+struct alignas(64) GemmDev {
+    CUtensorMap tm_w;  // W [n, k] BF16, box 64 x 128, 128-byte swizzle
+    CUtensorMap tm_x;  // x [m, k] BF16, box 64 x m, 128-byte swizzle
+    float* ws;         // FP32 partial tiles [n / 128][splits][m][128]
+    int* counters;     // [n / 128] arrivals per feature tile, self-resetting
+    __nv_bfloat16* out;
+    long long ldo;
+    int m, n, k, splits, stages;
+};
+
+template <int NR>
+struct ReduceParams {
+    CommDev c[NR];
+    const __nv_bfloat16* partial[NR];
+};
+
+template <int NR>
+struct alignas(64) RowparParams {
+    GemmDev g[NR];
+    CommDev c[NR];
+    int fused;  // 0: plain GEMM into g.out; 1: push + reduce
+};
+
+struct LaunchOpts {
+    cudaStream_t stream;
+    bool pdl;
+    bool cooperative;
+};
+
+int launch_reduce(const ReduceParams<1>& p, int grid, int threads, const LaunchOpts& o);
+int launch_reduce_loopback(const ReduceParams<kMaxWorld>& p, int grid, int nranks, int threads, const LaunchOpts& o);
+int launch_rowpar(const RowparParams<1>& p, int grid, const LaunchOpts& o);
+int launch_rowpar_loopback(const RowparParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o);
+int rowpar_smem_bytes(int m, int stages);
+int rowpar_stages(int m);
+int rowpar_max_ctas_per_sm(int m);
+
+extern int g_last_cuda_error;
+extern long long g_launches;
+
+}  // namespace dlm

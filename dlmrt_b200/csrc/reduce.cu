@@ -1,0 +1,68 @@
+// Stand-alone fused tensor-parallel reduction of a given BF16 partial: push reduce-scatter, rank-ordered FP32 sum
+// (+ residual + RMSNorm), multicast all-gather, in-band arrival detection. One launch per call; every CTA pushes its
+// share of the partial, re-arms its share of the stale buffers, then owns rows r = block, block + grid, ...
+// Replaces reduce_kernel<NORM, RESIDUAL> of the reference (dlmrt/ops/csrc/tp_comm.cu:138-275) bit for bit.
+#include "kernels.cuh"
+
+namespace dlm {
+
+int g_last_cuda_error = 0;
+long long g_launches = 0;
+
+// NR = 1: one rank per GPU (production). NR = 8: up to eight ranks emulated by one launch on one GPU, rank slot =
+// blockIdx.y; the grid is launched cooperatively so that all ranks' CTAs are resident together.
+template <int NR>
+__global__ void __launch_bounds__(1024, 1) reduce_kernel(const __grid_constant__ ReduceParams<NR> p) {
+    const int slot = NR == 1 ? 0 : static_cast<int>(blockIdx.y);
+    const CommDev& c = p.c[slot];
+    __shared__ float scratch[32];
+    pdl_wait();
+    const CommCtx x = comm_begin(c, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
+    stamp(c, x, 0);
+    push_partial(c, x, p.partial[slot]);
+    stamp(c, x, 1);
+    rearm(c, x);
+    own_and_collect(c, x, scratch);
+    comm_end(c, x);
+    pdl_launch_dependents();
+}
+
+template <int NR>
+static int launch_impl(const ReduceParams<NR>& p, dim3 grid, int threads, const LaunchOpts& o) {
+    cudaLaunchConfig_t config{};
+    config.gridDim = grid;
+    config.blockDim = dim3(static_cast<unsigned>(threads));
+    config.stream = o.stream;
+    cudaLaunchAttribute attrs[2];
+    int n = 0;
+    if (o.pdl) {
+        attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (o.cooperative) {
+        attrs[n].id = cudaLaunchAttributeCooperative;
+        attrs[n].val.cooperative = 1;
+        ++n;
+    }
+    config.attrs = attrs;
+    config.numAttrs = n;
+    const cudaError_t err = cudaLaunchKernelEx(&config, reduce_kernel<NR>, p);
+    if (err != cudaSuccess) {
+        g_last_cuda_error = static_cast<int>(err);
+        (void)cudaGetLastError();
+        return -6;
+    }
+    ++g_launches;
+    return 0;
+}
+
+int launch_reduce(const ReduceParams<1>& p, int grid, int threads, const LaunchOpts& o) {
+    return launch_impl<1>(p, dim3(grid), threads, o);
+}
+
+int launch_reduce_loopback(const ReduceParams<kMaxWorld>& p, int grid, int nranks, int threads, const LaunchOpts& o) {
+    return launch_impl<kMaxWorld>(p, dim3(grid, nranks), threads, o);
+}
+
+}  // namespace dlm

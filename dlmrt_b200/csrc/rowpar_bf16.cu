@@ -1,0 +1,282 @@
+// Row-parallel BF16 projection fused with the tensor-parallel reduction that follows it, for sm_100a.
+//
+//   out[m, n] = sum over ranks of  x_r[m, k] * W_r[n, k]^T          (k = this rank's K shard)
+//
+// The shape of a denoise round is small-M (32, 64 or 256 block tokens) against a wide weight shard, so the kernel is a
+// weight streamer: weights sit on the 128-row M axis of the MMA and the tokens on its N axis (D[128 features, m
+// tokens] in tensor memory), every CTA pulls a disjoint [128 x K/splits] slab of W through a TMA ring, and the x
+// slab comes out of L2.
+//
+//   warp 0   TMA producer: W slab (evict-first) + x slab (evict-last) per 64-wide k-block into a ring of 128-byte
+//            swizzled stages. The first ring-full of weight loads is issued BEFORE griddepcontrol.wait: weights never
+//            depend on the previous kernel, only x does.
+//   warp 1   MMA issuer: four tcgen05.mma kind::f16 (K = 16) per k-block, FP32 accumulator in TMEM; tcgen05.commit
+//            frees the stage and finally signals the epilogue.
+//   warp 2   TMEM allocation / release.
+//   warps 4-11  epilogue: tcgen05.ld the accumulator and write this CTA's FP32 partial tile to the workspace.
+//   The last CTA to finish a feature tile (an arrival counter per tile) sums the `splits` partial tiles in split
+//   order, so the value does not depend on which CTA finishes last, rounds to BF16 and either stores the tile (plain
+//   GEMM) or pushes each token row's 256 bytes straight into the owner rank's receive slot over NVLink. Then every CTA
+//   runs the re-arm / own / collect phases of the reduction (comm.cuh).
+#include "kernels.cuh"
+
+namespace dlm {
+
+namespace {
+
+struct SmemLayout {
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
+    uint64_t acc_full;
+    uint32_t tmem_base;
+    int finisher;
+    float scratch[32];
+};
+
+constexpr int kTileBytesW = kBlockF * kBlockK * 2;  // 16 KB
+
+__device__ __forceinline__ uint32_t tmem_cols(int m) {
+    uint32_t c = 32;
+    while (c < static_cast<uint32_t>(m)) c <<= 1;
+    return c;
+}
+
+}  // namespace
+
+template <int NR>
+__global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_constant__ RowparParams<NR> p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const int slot = NR == 1 ? 0 : static_cast<int>(blockIdx.y);
+    const GemmDev& g = p.g[slot];
+    const CommDev& c = p.c[slot];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int block = static_cast<int>(blockIdx.x), blocks = static_cast<int>(gridDim.x);
+
+    // Tile and K range of this CTA.
+    const int f = block / g.splits, s = block - f * g.splits;
+    const int nkb = g.k / kBlockK;
+    const int kb0 = static_cast<int>(static_cast<long long>(s) * nkb / g.splits);
+    const int kb1 = static_cast<int>(static_cast<long long>(s + 1) * nkb / g.splits);
+    const int iters = kb1 - kb0;
+    const int stage_bytes = kTileBytesW + g.m * kBlockK * 2;
+
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    SmemLayout* sm = reinterpret_cast<SmemLayout*>(tiles + g.stages * stage_bytes);
+    const uint32_t cols = tmem_cols(g.m);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < g.stages; ++i) {
+            mbar_init(&sm->full[i], 1);
+            mbar_init(&sm->empty[i], 1);
+        }
+        mbar_init(&sm->acc_full, 1);
+        fence_barrier_init();
+        tma_prefetch_descriptor(&g.tm_w);
+        tma_prefetch_descriptor(&g.tm_x);
+    }
+    if (warp == 2) tmem_alloc(&sm->tmem_base, cols);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem = sm->tmem_base;
+    // Generous budget for the local pipeline; the cross-rank waits take theirs from the caller (comm_begin).
+    const long long pipeline_deadline = globaltimer() + (c.timeout_ns > 0 ? c.timeout_ns : 2000000000ll);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int pre = iters < g.stages ? iters : g.stages;
+            for (int it = 0; it < pre; ++it) {
+                mbar_expect_tx(&sm->full[it], static_cast<uint32_t>(stage_bytes));
+                tma_load_2d(tiles + it * stage_bytes, &g.tm_w, &sm->full[it], (kb0 + it) * kBlockK, f * kBlockF,
+                            kEvictFirst);
+            }
+            pdl_wait();
+            for (int it = 0; it < pre; ++it)
+                tma_load_2d(tiles + it * stage_bytes + kTileBytesW, &g.tm_x, &sm->full[it], (kb0 + it) * kBlockK, 0,
+                            kEvictLast);
+            for (int it = pre; it < iters; ++it) {
+                const int st = it % g.stages;
+                const uint32_t parity = ((it / g.stages) & 1) ^ 1;
+                if (!mbar_wait(&sm->empty[st], parity, pipeline_deadline)) {
+                    report(c.status, kErrTimeout, st, kPhasePipeline, 0);
+                    break;
+                }
+                mbar_expect_tx(&sm->full[st], static_cast<uint32_t>(stage_bytes));
+                tma_load_2d(tiles + st * stage_bytes, &g.tm_w, &sm->full[st], (kb0 + it) * kBlockK, f * kBlockF,
+                            kEvictFirst);
+                tma_load_2d(tiles + st * stage_bytes + kTileBytesW, &g.tm_x, &sm->full[st], (kb0 + it) * kBlockK, 0,
+                            kEvictLast);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_bf16(kBlockF, g.m);
+            for (int it = 0; it < iters; ++it) {
+                const int st = it % g.stages;
+                const uint32_t parity = (it / g.stages) & 1;
+                if (!mbar_wait(&sm->full[st], parity, pipeline_deadline)) {
+                    report(c.status, kErrTimeout, st, kPhasePipeline, 1);
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint64_t dw = umma_desc_k128(tiles + st * stage_bytes);
+                const uint64_t dx = umma_desc_k128(tiles + st * stage_bytes + kTileBytesW);
+#pragma unroll
+                for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+                    // Advancing 16 BF16 = 32 bytes inside the swizzled row: +2 in the descriptor's 16-byte units.
+                    umma_bf16(tmem, dw + 2 * kk, dx + 2 * kk, idesc, (it | kk) != 0);
+                }
+                umma_commit(&sm->empty[st]);
+            }
+            umma_commit(&sm->acc_full);
+        }
+    } else if (warp >= 4) {
+        // Epilogue: thread `lane` of a warp holds feature 32 * quarter + lane; 16 token columns per tcgen05.ld.
+        const int quarter = warp & 3, half = (warp - 4) >> 2;
+        float* tile = g.ws + (static_cast<size_t>(f) * g.splits + s) * g.m * kBlockF;
+        const int feature = quarter * 32 + lane;
+        bool ok = true;
+        if (iters > 0) {
+            ok = mbar_wait(&sm->acc_full, 0, pipeline_deadline);
+            if (!ok) report(c.status, kErrTimeout, 0, kPhasePipeline, 2);
+            tcgen05_fence_after();
+        }
+        pdl_wait();  // the workspace may still be read by the previous kernel of the chain
+        for (int chunk = half; chunk < g.m / 16; chunk += 2) {
+            uint32_t r[16];
+            if (iters > 0 && ok) {
+                tmem_load_16(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + chunk * 16, r);
+                tmem_load_wait();
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) r[j] = 0;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) tile[static_cast<size_t>(chunk * 16 + j) * kBlockF + feature] = __uint_as_float(r[j]);
+        }
+        tcgen05_fence_before();
+    }
+    pdl_wait();
+    __threadfence();
+    __syncthreads();
+    if (warp == 2) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem, cols);
+    }
+    if (threadIdx.x == 0) {
+        const int old = atomicAdd(&g.counters[f], 1);
+        const int last = old == g.splits - 1;
+        if (last) g.counters[f] = 0;  // nobody else touches it before the next launch
+        sm->finisher = last;
+    }
+    __syncthreads();
+
+    CommCtx x{};
+    if (p.fused) {
+        x = comm_begin(c, block, blocks);
+        stamp(c, x, 0);
+    }
+    if (sm->finisher) {
+        __threadfence();
+        const float* base = g.ws + static_cast<size_t>(f) * g.splits * g.m * kBlockF;
+        const size_t split_stride = static_cast<size_t>(g.m) * kBlockF;
+        for (int v = threadIdx.x; v < g.m * (kBlockF / kVec); v += kFusedThreads) {
+            const int token = v / (kBlockF / kVec), j = v - token * (kBlockF / kVec);
+            const float* src = base + static_cast<size_t>(token) * kBlockF + j * kVec;
+            float acc[kVec];
+            {
+                const float4 a = __ldcg(reinterpret_cast<const float4*>(src));
+                const float4 b = __ldcg(reinterpret_cast<const float4*>(src) + 1);
+                acc[0] = a.x, acc[1] = a.y, acc[2] = a.z, acc[3] = a.w;
+                acc[4] = b.x, acc[5] = b.y, acc[6] = b.z, acc[7] = b.w;
+            }
+            for (int sp = 1; sp < g.splits; ++sp) {
+                const float4 a = __ldcg(reinterpret_cast<const float4*>(src + sp * split_stride));
+                const float4 b = __ldcg(reinterpret_cast<const float4*>(src + sp * split_stride) + 1);
+                acc[0] += a.x, acc[1] += a.y, acc[2] += a.z, acc[3] += a.w;
+                acc[4] += b.x, acc[5] += b.y, acc[6] += b.z, acc[7] += b.w;
+            }
+            const uint4 packed = pack_bf16x8(acc);
+            const int col = f * kBlockF + j * kVec;
+            if (p.fused) {
+                store_v4(push_address(c, x, token, col), packed);
+            } else {
+                store_v4(g.out + static_cast<size_t>(token) * g.ldo + col, packed);
+            }
+        }
+    }
+    if (p.fused) {
+        stamp(c, x, 1);
+        rearm(c, x);
+        pdl_launch_dependents();
+        own_and_collect(c, x, sm->scratch);
+        comm_end(c, x);
+    } else {
+        pdl_launch_dependents();
+    }
+}
+
+int rowpar_stages(int m) {
+    const int stage = kTileBytesW + m * kBlockK * 2;
+    int stages = kSmemBudget / stage;
+    if (stages > kMaxStages) stages = kMaxStages;
+    return stages;
+}
+
+int rowpar_smem_bytes(int m, int stages) {
+    return stages * (kTileBytesW + m * kBlockK * 2) + static_cast<int>(sizeof(SmemLayout)) + 1024;
+}
+
+template <int NR>
+static int launch_impl(const RowparParams<NR>& p, dim3 grid, const LaunchOpts& o) {
+    const int smem = rowpar_smem_bytes(p.g[0].m, p.g[0].stages);
+    cudaError_t err = cudaFuncSetAttribute(rowpar_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err == cudaSuccess) {
+        cudaLaunchConfig_t config{};
+        config.gridDim = grid;
+        config.blockDim = dim3(kFusedThreads);
+        config.dynamicSmemBytes = static_cast<size_t>(smem);
+        config.stream = o.stream;
+        cudaLaunchAttribute attrs[2];
+        int n = 0;
+        if (o.pdl) {
+            attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attrs[n].val.programmaticStreamSerializationAllowed = 1;
+            ++n;
+        }
+        if (o.cooperative) {
+            attrs[n].id = cudaLaunchAttributeCooperative;
+            attrs[n].val.cooperative = 1;
+            ++n;
+        }
+        config.attrs = attrs;
+        config.numAttrs = n;
+        err = cudaLaunchKernelEx(&config, rowpar_kernel<NR>, p);
+    }
+    if (err != cudaSuccess) {
+        g_last_cuda_error = static_cast<int>(err);
+        (void)cudaGetLastError();
+        return -6;
+    }
+    ++g_launches;
+    return 0;
+}
+
+int launch_rowpar(const RowparParams<1>& p, int grid, const LaunchOpts& o) { return launch_impl<1>(p, dim3(grid), o); }
+
+int launch_rowpar_loopback(const RowparParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o) {
+    return launch_impl<kMaxWorld>(p, dim3(grid, nranks), o);
+}
+
+int rowpar_max_ctas_per_sm(int m) {
+    int n = 0;
+    const int smem = rowpar_smem_bytes(m, rowpar_stages(m));
+    if (cudaFuncSetAttribute(rowpar_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, rowpar_kernel<1>, kFusedThreads, smem) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 1;
+    }
+    return n < 1 ? 1 : n;
+}
+
+}  // namespace dlm

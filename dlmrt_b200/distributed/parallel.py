@@ -1,0 +1,315 @@
+"""Tensor parallelism over the GPUs of one NVSwitch node: the reduction entry point of the row-parallel hot path.
+
+Mirror of the reference's `dlmrt/distributed/parallel.py` (init :34-44, Group :47-180): same names, arguments, buffer
+discipline and error behaviour, so model code written against it runs unchanged. What differs is underneath:
+
+  * `Group.reduce` / `Group.reduce_norm` call libdlmrt_b200.so through its C ABI (dlm_reduce_bf16, or dlm_rowpar_bf16
+    when the partial's GEMM was deferred, see below) instead of the JIT-built tp_comm extension;
+  * the row-parallel GEMM that produces a partial is FUSED into the reduction: `Linear.__call__(x, out=partial)` on a
+    buffer obtained from `Group.partial` records the GEMM instead of running it, and the next `Group.reduce*` on that
+    buffer launches one kernel that streams the weight shard through tcgen05, pushes finished tiles into the owner
+    ranks' receive slots and reduces them (`Group.flush(partial)` materialises the partial if something else wants
+    to read it);
+  * NCCL is used only to create the process group torch symmetric memory rendezvouses over, as in the reference
+    (parallel.py:42-43,73); on a single GPU a `Group.local` (world 1) runs the same kernels over ordinary buffers.
+
+One process per GPU runs the same program; every reduction returns bitwise-identical values on all ranks.
+"""
+
+import ctypes as C
+import os
+
+import torch
+
+from .. import _lib
+from .._lib import DlmComm, DlmGemm, DlmStatus
+
+# CTAs' wait budget on the device; a rank that never pushes ends in a DLM_ERR_TIMEOUT status, not a hang.
+TIMEOUT_NS = int(os.environ.get("DLMRT_TP_TIMEOUT_NS", 2_000_000_000))
+PDL = os.environ.get("DLMRT_PDL", "1") != "0"
+
+
+def init():
+    """Join the torchrun process group; returns None when running on one GPU (parallel.py:34-44)."""
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if world == 1:
+        return None
+    rank = int(os.environ["RANK"])
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
+    torch.cuda.set_device(device)
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=device)
+    return Group(device)
+
+
+class Handle:
+    """What a rendezvous yields: every rank's address of the buffer and its NVLS multicast address (0 if none)."""
+
+    def __init__(self, buffer_ptrs, multicast_ptr=0):
+        self.buffer_ptrs = list(buffer_ptrs)
+        self.multicast_ptr = multicast_ptr
+
+
+class SymmetricAllocator:
+    """torch symmetric memory (CUDA VMM handles exchanged over the NCCL-bootstrapped group), parallel.py:61-79."""
+
+    def __init__(self, device, name):
+        self.device, self.name = device, name
+
+    def alloc(self, shape, dtype, armed):
+        import torch.distributed._symmetric_memory as symm
+
+        with torch.inference_mode(False):  # shared by graphs captured in and out of inference mode
+            t = symm.empty(*shape, device=self.device, dtype=dtype)
+        if armed:  # every rank finishes arming before the rendezvous lets any rank write into it
+            t.view(torch.int16).fill_(-1)
+            torch.cuda.synchronize(self.device)
+        h = symm.rendezvous(t, self.name)
+        return t, Handle(h.buffer_ptrs, h.multicast_ptr if h.multicast_ptr else 0)
+
+
+class LocalAllocator:
+    """World 1: the 'symmetric' buffer is an ordinary tensor and its only peer is itself."""
+
+    def __init__(self, device):
+        self.device = device
+
+    def alloc(self, shape, dtype, armed):
+        with torch.inference_mode(False):
+            t = torch.empty(*shape, device=self.device, dtype=dtype)
+        if armed:
+            t.view(torch.int16).fill_(-1)
+        return t, Handle([t.data_ptr()])
+
+
+class Group:
+    def __init__(self, device, rank=None, world=None, allocator=None, max_ctas=0):
+        if allocator is None:
+            import torch.distributed as dist
+
+            rank, world = dist.get_rank(), dist.get_world_size()
+            self.name = dist.group.WORLD.group_name
+            allocator = SymmetricAllocator(device, self.name)
+        else:
+            self.name = "local"
+        self.rank, self.world = rank, world
+        self.device = device
+        self.max_ctas = max_ctas  # cap on every launch's grid (calls on concurrent chains must fit together)
+        self._alloc = allocator
+        self._buffers = {}
+        self._handles = {}
+        self._recv = {}
+        self._out_peers = {}
+        self._last = {}      # per chain: the previous call's output buffer
+        self._pending = {}   # partial data_ptr -> (linear, x): GEMMs deferred into the next reduction
+        self._workspaces = {}
+        self.stamps = 0      # device address of a [grid, 4] int64 buffer to record kernel phase times
+        self.status = torch.zeros(_lib.STATUS_WORDS, device=device, dtype=torch.int32)
+        _lib.lib()  # fail now, not at the first reduction, when the library is missing
+
+    @classmethod
+    def local(cls, device):
+        """A world-1 group on one GPU: same kernels, receive slots and output buffers in local memory."""
+        return cls(torch.device(device), rank=0, world=1, allocator=LocalAllocator(torch.device(device)))
+
+    def symmetric(self, key, shape, dtype=torch.bfloat16, armed=False):
+        """A symmetric-memory tensor, allocated once per key (collectively, in the same order on every rank); every
+        later call with the key must ask for the same shape and dtype.
+
+        `armed`: filled with the arrival sentinel (every bf16 lane 0xFFFF) before any rank can write into it.
+        """
+        if key not in self._buffers:
+            self._buffers[key], self._handles[key] = self._alloc.alloc(tuple(shape), dtype, armed)
+        t = self._buffers[key]
+        if tuple(t.shape) != tuple(shape) or t.dtype != dtype:  # a larger request would write past it
+            raise ValueError(f"symmetric buffer {key}: {tuple(t.shape)} {t.dtype} allocated, {tuple(shape)} {dtype} "
+                             "requested")
+        return t
+
+    def _handle(self, t):
+        for key, buf in self._buffers.items():
+            base = buf.data_ptr()
+            if base <= t.data_ptr() < base + buf.numel() * buf.element_size():
+                return key, self._handles[key]
+        raise ValueError("not a symmetric tensor of this group")
+
+    def multicast(self, t):
+        """Multicast address of symmetric tensor `t` (stores reach every rank's copy), or 0 without NVLink multicast."""
+        handle = self._handle(t)[1]
+        if not handle.multicast_ptr:
+            return 0
+        return handle.multicast_ptr + (t.data_ptr() - handle.buffer_ptrs[self.rank])
+
+    def peer_addresses(self, t):
+        """The address of `t` in every rank's copy, as Python ints (what the C ABI takes by value)."""
+        handle = self._handle(t)[1]
+        offset = t.data_ptr() - handle.buffer_ptrs[self.rank]
+        return [p + offset for p in handle.buffer_ptrs]
+
+    def peers(self, t):
+        """[world] int64 device tensor: the address of `t` in every rank's copy (parallel.py:95-102)."""
+        key = self._handle(t)[0]
+        if (key, t.data_ptr()) not in self._out_peers:
+            self._out_peers[key, t.data_ptr()] = torch.tensor(self.peer_addresses(t), device=self.device,
+                                                              dtype=torch.int64)
+        return self._out_peers[key, t.data_ptr()]
+
+    def _receive(self, rows, n, chain):
+        """Triple-buffered receive slots (symmetric, armed), every rank's slot address, invocation counters."""
+        if (rows, n, chain) not in self._recv:
+            key = f"recv{rows}x{n}.{chain}"
+            self.symmetric(key, (3, self.world, rows // self.world, n), armed=True)
+            epochs = torch.zeros(_lib.EPOCH_SLOTS, device=self.device, dtype=torch.int32)
+            self._recv[rows, n, chain] = list(self._handles[key].buffer_ptrs), epochs
+        return self._recv[rows, n, chain]
+
+    def partial(self, site, shape):
+        """Where a row-parallel GEMM writes its partial product: one buffer shared by every call site (`site` is not
+        used), so every call passes the same shape (parallel.py:114-117)."""
+        return self.symmetric("partial", shape)
+
+    # -- deferred GEMMs ---------------------------------------------------------------------------------------------
+    def is_partial(self, t):
+        """True when `t` is (a leading-rows view of) this group's symmetric memory, i.e. a GEMM into it may be fused
+        into the reduction that follows."""
+        try:
+            self._handle(t)
+        except ValueError:
+            return False
+        return True
+
+    def defer(self, linear, x, out):
+        """Record `out = x @ linear.weight^T` instead of running it; the next reduce* of `out` runs it fused."""
+        self._pending[out.data_ptr()] = (linear, x, out)
+        return out
+
+    def flush(self, partial):
+        """Run a deferred GEMM on its own, for callers that read the partial before reducing it."""
+        pending = self._pending.pop(partial.data_ptr(), None)
+        if pending is not None:
+            linear, x, out = pending
+            linear.gemm(x, out)
+        return partial
+
+    def workspace(self, chain, nbytes):
+        """Split-K scratch of the fused GEMMs of one chain (FP32 partial tiles + tile counters), grown on demand."""
+        ws = self._workspaces.get(chain)
+        if ws is None or ws.numel() < nbytes:
+            with torch.inference_mode(False):
+                ws = torch.zeros(nbytes, device=self.device, dtype=torch.uint8)
+            self._workspaces[chain] = ws
+        return ws
+
+    # -- launches ---------------------------------------------------------------------------------------------------
+    def _comm(self, rows, n, site, chain, mode, h, weight, eps, scale):
+        """The DlmComm of one call and its output buffer (the bookkeeping of parallel.py:119-132)."""
+        out = self.symmetric(f"out:{site}", (rows, n), armed=True)
+        ptrs, epochs = self._receive(rows, n, chain)
+        last = self._last.get(chain)
+        if last is out:
+            raise ValueError(f"call site {site} ran twice in a row; its buffer would never be re-armed")
+        c = DlmComm()
+        c.rank, c.world, c.rows, c.n, c.mode = self.rank, self.world, rows, n, mode
+        c.eps, c.scale = eps, scale
+        peers = self.peer_addresses(out)
+        for s in range(self.world):
+            c.recv[s] = ptrs[s]
+            c.out_peers[s] = peers[s]
+        c.out = out.data_ptr()
+        c.out_mc = self.multicast(out) or None
+        # The previous call's output on this chain: its consumer has finished, so this call re-arms it.
+        if last is not None:
+            c.rearm, c.rearm_bytes = last.data_ptr(), last.numel() * last.element_size()
+        c.epochs = epochs.data_ptr()
+        c.h = h.data_ptr() if h is not None else None
+        c.weight = weight.data_ptr() if weight is not None else None
+        c.status = self.status.data_ptr()
+        c.stamps = self.stamps or None
+        c.timeout_ns = TIMEOUT_NS
+        c.pdl = int(PDL)
+        c.max_ctas = self.max_ctas
+        return c, out
+
+    def _gemm(self, linear, x, chain):
+        g = DlmGemm()
+        m, k = x.shape
+        if x.stride(1) != 1 or x.dtype != torch.bfloat16:
+            raise ValueError("row-parallel input must be BF16 with contiguous K")
+        nbytes = _lib.lib().dlm_workspace_bytes(m, linear.n, k)
+        ws = self.workspace(chain, nbytes)
+        g.x, g.w, g.m, g.n, g.k = x.data_ptr(), linear.weight.data_ptr(), m, linear.n, k
+        g.ldx, g.ldw = x.stride(0), linear.weight.stride(0)
+        g.workspace, g.workspace_bytes, g.splits = ws.data_ptr(), ws.numel(), 0
+        return g
+
+    def _launch(self, mode, partial, h, weight, site, eps=0.0, scale=1.0, chain=0):
+        rows, n = partial.shape
+        comm, out = self._comm(rows, n, site, chain, mode, h, weight, eps, scale)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        pending = self._pending.pop(partial.data_ptr(), None)
+        if pending is not None and n <= _lib.FUSED_MAX_N:
+            linear, x, _ = pending
+            gemm = self._gemm(linear, x, chain)
+            _lib.check(_lib.lib().dlm_rowpar_bf16(C.byref(gemm), C.byref(comm), stream), f"rowpar {site}")
+        else:
+            if pending is not None:
+                pending[0].gemm(pending[1], pending[2])
+            _lib.check(_lib.lib().dlm_reduce_bf16(partial.data_ptr(), C.byref(comm), stream), f"reduce {site}")
+        self._last[chain] = out
+        return out
+
+    def reduce_norm(self, partial, h, weight, eps, scale=1.0, *, site, chain=0):
+        """rmsnorm(h [+= sum of partial over ranks]) * weight * scale, on every rank (parallel.py:134-143).
+
+        With `h`, only this rank's rows of `h` are updated (the residual stream becomes sequence-parallel);
+        without it the reduced partial itself is normalized. The result lives in this call site's buffer
+        until the next call on the same `chain`, which re-arms it. Reductions that may run concurrently
+        (different streams) need different `chain`s; calls on one chain are ordered.
+        """
+        mode = _lib.REDUCE_NORM_RESIDUAL if h is not None else _lib.REDUCE_NORM
+        return self._launch(mode, partial, h, weight, site, eps, scale, chain)
+
+    def reduce(self, partial, *, site, chain=0):
+        """Sum over ranks of `partial`, on every rank, in this call site's buffer (parallel.py:145-147)."""
+        return self._launch(_lib.REDUCE, partial, None, None, site, chain=chain)
+
+    def shard(self, t, dim=0):
+        if t.shape[dim] % self.world:
+            raise ValueError(f"Dimension {dim} of {tuple(t.shape)} does not split over {self.world} ranks")
+        return t.chunk(self.world, dim)[self.rank].contiguous()
+
+    def check(self):
+        """Read and clear the device status words (synchronises the current stream); raises on a timed-out wait."""
+        st = DlmStatus()
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _lib.check(_lib.lib().dlm_status_read(self.status.data_ptr(), C.byref(st), stream), "status")
+        if st.code:
+            raise TimeoutError(f"rank {self.rank}: {_lib.lib().dlm_strerror(st.code).decode()} (block {st.block}, "
+                               f"rank slot {st.slot}, phase {st.phase}, invocation {st.epoch})")
+
+    def all_reduce_(self, x):
+        """In-place sum over ranks of a symmetric tensor; identical result on every rank (parallel.py:154-162).
+        Off the hot path: torch's symmetric-memory kernels, as in the reference."""
+        if self.world == 1:
+            return x
+        if self.multicast(x):
+            torch.ops.symm_mem.multimem_all_reduce_(x, "sum", self.name)
+        else:
+            torch.ops.symm_mem.two_shot_all_reduce_(x, "sum", self.name)
+        return x
+
+    def all_gather(self, x, key):
+        """[world, *x.shape]: every rank's `x`, stacked in rank order (parallel.py:164-180). Off the hot path."""
+        out = self.symmetric(key, (self.world, *x.shape), x.dtype)
+        if self.world == 1:
+            out[0].copy_(x)
+            return out
+        if self.multicast(out):
+            torch.ops.symm_mem.multimem_all_gather_out(x, self.name, out.view(-1, *x.shape[1:]))
+            return out
+        import torch.distributed as dist
+
+        dist.all_gather_into_tensor(out.view(-1, *x.shape[1:]), x.contiguous())
+        return out

@@ -1,0 +1,66 @@
+"""Linear layers of the row-parallel hot path on hand-written sm_100a kernels.
+
+Mirror of the reference's `dlmrt/layers/linear.py` (Linear :16-51): `Linear(weight, fp8, b200=False)`, `.n`, `.k`,
+`.weight`, `.fp8`, `.input(rows, device)`, `__call__(x, scales=None, out=None) -> out`. The reference runs BF16 on
+cuBLAS (`torch.mm`) on SM >= 10 (:28,47-48); here the GEMM is libdlmrt_b200's tcgen05 weight streamer, and when `out`
+is a tensor-parallel group's symmetric partial the GEMM is not run at all but deferred into the fused
+projection + reduction kernel launched by the following `Group.reduce*` (see dlmrt_b200.distributed.parallel).
+
+FP8 activations are outside this path (the reference forces the fused reduction off with FP8 GEMM inputs,
+dlmrt/models/sdar/model.py:62-64), so `fp8=True` is rejected.
+"""
+
+import ctypes as C
+
+import torch
+
+from .. import _lib
+from .._lib import DlmGemm
+
+
+class Linear:
+    """y = x @ W^T, BF16 in and out, FP32 accumulation in increasing K (K ranges summed in order when split)."""
+
+    def __init__(self, weight, fp8=False, b200=False, group=None):
+        if fp8:
+            raise NotImplementedError("FP8 linears are not part of the row-parallel BF16 path")
+        if weight.dtype != torch.bfloat16 or weight.dim() != 2:
+            raise ValueError("weight must be a BF16 [N, K] matrix")
+        self.n, self.k = weight.shape
+        self.fp8 = False
+        self.b200 = False  # the SM 12.x emulation switch of the reference has no meaning on a B200
+        self.weight = weight.contiguous()
+        self.group = group
+        self._workspace = None
+        _lib.lib()
+
+    def input(self, rows, device):
+        """Activation buffers this layer consumes: BF16 needs none (linear.py:34-39)."""
+        return None, None
+
+    def gemm(self, x, out, pdl=True):
+        """Run the GEMM now: out[m, n] = x[m, k] @ W[n, k]^T."""
+        m, k = x.shape
+        if k != self.k or tuple(out.shape) != (m, self.n) or out.dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
+            raise ValueError(f"Linear [{self.n}, {self.k}]: x {tuple(x.shape)} {x.dtype}, out {tuple(out.shape)}")
+        if x.stride(1) != 1 or out.stride(1) != 1:
+            raise ValueError("x and out must have a contiguous last dimension")
+        nbytes = _lib.lib().dlm_workspace_bytes(m, self.n, k)
+        if self._workspace is None or self._workspace.numel() < nbytes:
+            with torch.inference_mode(False):
+                self._workspace = torch.zeros(nbytes, device=x.device, dtype=torch.uint8)
+        g = DlmGemm()
+        g.x, g.w, g.m, g.n, g.k = x.data_ptr(), self.weight.data_ptr(), m, self.n, k
+        g.ldx, g.ldw = x.stride(0), self.weight.stride(0)
+        g.workspace, g.workspace_bytes, g.splits = self._workspace.data_ptr(), self._workspace.numel(), 0
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        _lib.check(_lib.lib().dlm_gemm_bf16(C.byref(g), out.data_ptr(), out.stride(0), int(pdl), stream),
+                   f"gemm [{m}, {self.n}, {k}]")
+        return out
+
+    def __call__(self, x, scales=None, out=None):
+        if out is None:
+            out = torch.empty(x.shape[0], self.n, device=x.device, dtype=torch.bfloat16)
+        elif self.group is not None and self.group.is_partial(out):
+            return self.group.defer(self, x, out)
+        return self.gemm(x, out)

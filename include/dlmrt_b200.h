@@ -1,0 +1,165 @@
+/* dlmrt_b200 -- C ABI of the B200-native tensor-parallel row-parallel hot path.
+ *
+ * One shared library (libdlmrt_b200.so, sm_100a only) replaces, for this path, what the reference engine binds
+ * through two interfaces:
+ *   - the pybind module of dlmrt/ops/csrc/tp_comm.cu:315-319 (`reduce`, `reduce_norm`, `reduce_norm_residual`,
+ *     17 positional arguments each, tp_comm.cu:278-280), called from dlmrt/distributed/parallel.py:119-132;
+ *   - the row-parallel GEMM that feeds it: `torch.mm(x, W.t(), out=partial)` in dlmrt/layers/linear.py:47-48
+ *     (cuBLAS on SM >= 10) and FlashInfer's `trtllm_fp4_block_scale_routed_moe` behind
+ *     dlmrt/quantization/nvfp4.py:280-306 for the NVFP4 expert down-projection.
+ *
+ * Conventions
+ *   - plain C types only: device addresses are `void*` / `const void*`, sizes are integers, the stream is the
+ *     CUstream / cudaStream_t handle passed as `void*` (NULL = the legacy default stream);
+ *   - every entry point returns 0 (DLM_OK) or a negative DLM_ERR_* code and never throws; dlm_strerror() names it,
+ *     dlm_last_cuda_error() gives the cudaError_t behind DLM_ERR_CUDA;
+ *   - nothing is allocated after dlm_* returns and no host state is kept that a CUDA-graph replay would bypass:
+ *     epochs, tile counters and the status words live in device memory owned by the caller (tp_comm.cu:178,211 keeps
+ *     its epochs the same way);
+ *   - device-side waits are bounded (timeout_ns, measured with %globaltimer). A wait that runs out records a code in
+ *     the caller's status words, stops waiting, finishes its bookkeeping and returns normally; it never traps
+ *     (the reference prints and traps after ~30 s, tp_comm.cu:67-70).
+ *
+ * All BF16 matrices are row-major with the hidden / K dimension contiguous, as in the reference.
+ */
+#ifndef DLMRT_B200_H
+#define DLMRT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define DLM_API __attribute__((visibility("default")))
+#else
+#define DLM_API
+#endif
+
+#define DLM_MAX_WORLD 8      /* tp_comm.cu:52 kMaxWorld */
+#define DLM_EPOCH_SLOTS 256  /* int32 invocation counters per receive buffer; every kernel keeps all of them equal */
+#define DLM_STATUS_WORDS 4   /* int32: [0] first error code, [1] block << 8 | slot, [2] phase, [3] epoch */
+#define DLM_MAX_N 8192       /* tp_comm.cu:282: hidden size a multiple of 256, at most 8192 */
+#define DLM_FUSED_MAX_N 3072 /* the fused GEMM+reduce kernels run 384 threads: hidden / 8 <= 384 */
+#define DLM_MAX_M 256        /* rows of one block forward (32, 64 or 256 in the reference's rounds) */
+
+enum {
+    DLM_OK = 0,
+    DLM_ERR_SHAPE = -1,     /* a size the kernels do not take (see each entry point) */
+    DLM_ERR_ALIGN = -2,     /* an address or leading dimension that is not 16-byte aligned */
+    DLM_ERR_WORLD = -3,     /* world outside 1..8, rank outside 0..world-1, rows % world != 0 */
+    DLM_ERR_NULL = -4,      /* a required pointer is NULL */
+    DLM_ERR_GRID = -5,      /* the grid cannot be co-resident on this GPU (ranks wait on each other) */
+    DLM_ERR_CUDA = -6,      /* a CUDA call failed: see dlm_last_cuda_error() */
+    DLM_ERR_WORKSPACE = -7, /* workspace smaller than dlm_workspace_bytes() */
+    DLM_ERR_TIMEOUT = -8,   /* device status: a bounded wait ran out (data from a rank never arrived) */
+    DLM_ERR_ARCH = -9       /* not an sm_100 device */
+};
+
+/* What follows the rank-ordered sum (tp_comm.cu:138 template <NORM, RESIDUAL>). */
+enum {
+    DLM_REDUCE = 0,               /* K1  tp_comm.cu:318  out = sum                                            */
+    DLM_REDUCE_NORM = 1,          /* K2  tp_comm.cu:317  out = rmsnorm(bf16(sum)) * weight * scale             */
+    DLM_REDUCE_NORM_RESIDUAL = 2  /* K3  tp_comm.cu:316  h[own rows] = bf16(bf16(sum) + h); out = rmsnorm(..)  */
+};
+
+/* The reduction half of a call: where partial rows are pushed, where the result lands, what is re-armed.
+ * Replaces arguments 2-17 of the reference's launch<> (tp_comm.cu:278-280); the address tables the reference
+ * passes as int64 device tensors (`recv`, `out_peers`, parallel.py:95-112) are passed by value here and travel in
+ * kernel parameter space. */
+typedef struct DlmComm {
+    int32_t rank, world;
+    int32_t rows, n;               /* the partial is [rows, n] BF16; rows % world == 0; n % 256 == 0, n <= 8192 */
+    int32_t mode;                  /* DLM_REDUCE* */
+    float eps, scale;              /* RMSNorm epsilon and output scale (modes 1, 2) */
+    void* recv[DLM_MAX_WORLD];     /* every rank's receive buffer [3][world][rows/world][n] BF16, armed (0xFFFF) */
+    void* out;                     /* this rank's copy of the call site's output [rows, n] BF16, armed */
+    void* out_mc;                  /* NVLS multicast address of `out`, or NULL: then one store per rank */
+    void* out_peers[DLM_MAX_WORLD];/* every rank's copy of `out` (used when out_mc is NULL) */
+    void* rearm;                   /* previous output on this chain (local) to re-arm, or NULL */
+    int64_t rearm_bytes;           /* its size; a multiple of 16 */
+    int32_t* epochs;               /* [DLM_EPOCH_SLOTS] int32, zero-initialised, one array per receive buffer */
+    void* h;                       /* [rows, n] BF16 residual stream (mode 2): own rows read and rewritten */
+    const void* weight;            /* [n] BF16 RMSNorm weight (modes 1, 2) */
+    int32_t* status;               /* [DLM_STATUS_WORDS] int32 device words, zero-initialised, or NULL */
+    int64_t* stamps;               /* [grid, 4] int64 %globaltimer phase stamps per CTA, or NULL (tp_comm.cu:121) */
+    int64_t timeout_ns;            /* budget of every device wait; 0 = 2 s */
+    int32_t pdl;                   /* launch as a programmatic dependent launch (tp_comm.cu:304-309) */
+    int32_t max_ctas;              /* cap on the grid, 0 = one CTA per SM. Calls that may run concurrently (different
+                                      chains on different streams) must together fit on the GPU. */
+} DlmComm;
+
+/* The GEMM half of a fused call: out[M, N] = x[M, K] * W[N, K]^T, this rank's K shard (linear.py:41-51). */
+typedef struct DlmGemm {
+    const void* x;   /* [m, k] BF16, leading dimension ldx elements */
+    const void* w;   /* [n, k] BF16, leading dimension ldw elements */
+    int32_t m, n, k; /* m % 16 == 0, 16 <= m <= 256; n % 128 == 0; k % 64 == 0 */
+    int64_t ldx, ldw;/* multiples of 8 */
+    void* workspace; /* dlm_workspace_bytes(m, n, k) bytes, zero-initialised once, 256-byte aligned; one per chain */
+    int64_t workspace_bytes;
+    int32_t splits;  /* K splits across CTAs, 0 = chosen by the library; FP32 partial tiles are summed in split
+                        order, so the result does not depend on scheduling */
+} DlmGemm;
+
+/* Device status read back by dlm_status_read(). */
+typedef struct DlmStatus {
+    int32_t code;   /* DLM_OK or DLM_ERR_TIMEOUT */
+    int32_t block;  /* CTA that gave up */
+    int32_t slot;   /* rank slot it was waiting for */
+    int32_t phase;  /* 1 = receive slots (reduce-scatter), 2 = own OUT copy (all-gather), 3 = GEMM pipeline */
+    int32_t epoch;
+} DlmStatus;
+
+typedef void* dlm_stream_t;
+
+/* Stand-alone fused reduction of a given BF16 partial [rows, n] (local memory): push reduce-scatter, rank-ordered
+ * FP32 sum (+ residual + RMSNorm), multicast all-gather, in-band arrival detection. Bit-exact with
+ * reduce_kernel<NORM, RESIDUAL> (tp_comm.cu:138-275), whose three pybind entry points it replaces. */
+DLM_API int dlm_reduce_bf16(const void* partial, const DlmComm* comm, dlm_stream_t stream);
+
+/* One launch that runs `nranks` ranks of the same reduction on ONE GPU (rank i = partial[i], comm[i]; every
+ * comm[i].recv / out_peers names buffers on this GPU; out_mc must be NULL). For testing the multi-rank protocol
+ * without several GPUs: kernels that wait on one another must not run as separate launches on one GPU.
+ * No counterpart in the reference. */
+DLM_API int dlm_reduce_bf16_loopback(const void* const* partial, const DlmComm* comm, int nranks, dlm_stream_t stream);
+
+/* Plain row-parallel-shaped GEMM without communication: out[m, n] BF16 (ldo elements) = x * W^T.
+ * Replaces Linear.__call__ on one GPU (linear.py:47-48, torch.mm on cuBLAS). */
+DLM_API int dlm_gemm_bf16(const DlmGemm* gemm, void* out, int64_t ldo, int pdl, dlm_stream_t stream);
+
+/* Fused row-parallel projection + reduction: the GEMM above whose finished BF16 tiles are pushed straight into the
+ * owner ranks' receive slots, followed in the same kernel by the reduction of dlm_reduce_bf16.
+ * Replaces the pair Linear.__call__(x, out=partial) -> Group.reduce / reduce_norm
+ * (dlmrt/models/sdar/model.py:237-243, llada2/model.py:435-439, diffusion_gemma/model.py:272-292).
+ * gemm->m == comm->rows, gemm->n == comm->n <= DLM_FUSED_MAX_N. */
+DLM_API int dlm_rowpar_bf16(const DlmGemm* gemm, const DlmComm* comm, dlm_stream_t stream);
+
+/* Single-GPU loopback of `nranks` ranks of dlm_rowpar_bf16 in one launch (see dlm_reduce_bf16_loopback). */
+DLM_API int dlm_rowpar_bf16_loopback(const DlmGemm* gemm, const DlmComm* comm, int nranks, dlm_stream_t stream);
+
+/* Bytes of workspace (FP32 split-K partial tiles + tile counters) a GEMM of this shape needs. */
+DLM_API size_t dlm_workspace_bytes(int m, int n, int k);
+
+/* Number of K splits the library would pick for this shape with `max_ctas` CTAs available (0 = all SMs). */
+DLM_API int dlm_choose_splits(int m, int n, int k, int max_ctas);
+
+/* Copies the device status words to the host (synchronises `stream`) and clears them on the device. */
+DLM_API int dlm_status_read(int32_t* device_status, DlmStatus* out, dlm_stream_t stream);
+
+/* Returns DLM_OK when the caller's struct sizes (a binding in another language) match the library's. */
+DLM_API int dlm_abi_check(size_t sizeof_comm, size_t sizeof_gemm, size_t sizeof_status);
+
+DLM_API const char* dlm_strerror(int code);
+DLM_API int dlm_last_cuda_error(void);
+/* Number of SMs of the current device, and 100 when it is an sm_100 part (0 otherwise). */
+DLM_API int dlm_device_sms(void);
+DLM_API int dlm_device_arch(void);
+/* Number of kernel launches this library has issued in this process (for the benchmark's gpu_launches). */
+DLM_API int64_t dlm_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DLMRT_B200_H */

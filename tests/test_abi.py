@@ -1,0 +1,112 @@
+"""The C-ABI library loads, exports every symbol include/dlmrt_b200.h declares, and rejects bad arguments with the
+documented codes before touching a GPU (host-side checks of tp_comm.cu:282-287 as return codes)."""
+
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+
+from dlmrt_b200 import _lib
+from dlmrt_b200._lib import DlmComm, DlmGemm
+
+HEADER = Path(__file__).resolve().parent.parent / "include" / "dlmrt_b200.h"
+
+
+def declared():
+    return re.findall(r"^DLM_API\s+[\w\s\*]+?\b(dlm_\w+)\(", HEADER.read_text(), flags=re.M)
+
+
+def test_every_declared_symbol_is_exported_and_bound():
+    names = declared()
+    assert len(names) >= 14
+    handle = C.CDLL(str(_lib.LIB_PATH))
+    for name in names:
+        assert hasattr(handle, name), name
+        assert name in _lib.SIGNATURES, f"{name} is not bound in dlmrt_b200._lib"
+    assert set(_lib.SIGNATURES) == set(names)
+
+
+def test_struct_layouts_match():
+    lib = _lib.lib()
+    assert lib.dlm_abi_check(C.sizeof(DlmComm), C.sizeof(DlmGemm), C.sizeof(_lib.DlmStatus)) == _lib.OK
+    assert lib.dlm_abi_check(C.sizeof(DlmComm) + 8, C.sizeof(DlmGemm), C.sizeof(_lib.DlmStatus)) == _lib.ERR_SHAPE
+
+
+def test_header_constants_match_binding():
+    text = HEADER.read_text()
+    for name, value in [("DLM_MAX_WORLD", _lib.MAX_WORLD), ("DLM_EPOCH_SLOTS", _lib.EPOCH_SLOTS),
+                        ("DLM_STATUS_WORDS", _lib.STATUS_WORDS), ("DLM_FUSED_MAX_N", _lib.FUSED_MAX_N)]:
+        assert int(re.search(rf"#define {name} (\d+)", text).group(1)) == value
+    for name, value in [("DLM_ERR_TIMEOUT", _lib.ERR_TIMEOUT), ("DLM_ERR_ARCH", _lib.ERR_ARCH),
+                        ("DLM_ERR_WORKSPACE", _lib.ERR_WORKSPACE)]:
+        assert int(re.search(rf"{name} = (-?\d+)", text).group(1)) == value
+
+
+def test_strerror_and_sizes():
+    lib = _lib.lib()
+    for code in range(0, -10, -1):
+        assert lib.dlm_strerror(code)
+    assert lib.dlm_strerror(-99) == b"unknown error"
+    assert lib.dlm_workspace_bytes(256, 2560, 9728) == 256 + 8 * 256 * 2560 * 4
+    assert lib.dlm_workspace_bytes(0, 2560, 64) == 0
+
+
+def comm(**kw):
+    c = DlmComm()
+    c.rank, c.world, c.rows, c.n, c.mode = 0, 1, 32, 256, _lib.REDUCE
+    c.recv[0], c.out, c.out_peers[0], c.epochs = 0x1000, 0x2000, 0x2000, 0x3000
+    for k, v in kw.items():
+        setattr(c, k, v)
+    return c
+
+
+@pytest.mark.parametrize("kw, code", [
+    (dict(n=100), _lib.ERR_SHAPE), (dict(n=8448), _lib.ERR_SHAPE), (dict(rows=33, world=2, rank=0), _lib.ERR_WORLD),
+    (dict(world=9), _lib.ERR_WORLD), (dict(rank=1), _lib.ERR_WORLD), (dict(out=None), _lib.ERR_NULL),
+    (dict(out=0x2008), _lib.ERR_ALIGN), (dict(mode=_lib.REDUCE_NORM), _lib.ERR_NULL),
+    (dict(mode=_lib.REDUCE_NORM_RESIDUAL, weight=0x4000), _lib.ERR_NULL), (dict(rearm_bytes=24, rearm=0x5000), _lib.ERR_ALIGN),
+    (dict(rearm_bytes=32), _lib.ERR_ALIGN), (dict(epochs=None), _lib.ERR_NULL), (dict(mode=7), _lib.ERR_SHAPE),
+])
+def test_reduce_rejects_bad_arguments(kw, code):
+    """No launch happens: the checks run before any CUDA call, as the reference's TORCH_CHECKs do."""
+    assert _lib.lib().dlm_reduce_bf16(0x8000, C.byref(comm(**kw)), None) == code
+
+
+def test_reduce_rejects_null_partial_and_missing_peer():
+    assert _lib.lib().dlm_reduce_bf16(None, C.byref(comm()), None) == _lib.ERR_NULL
+    c = comm(world=2, rows=32)
+    c.recv[1] = 0x1100
+    assert _lib.lib().dlm_reduce_bf16(0x8000, C.byref(c), None) == _lib.ERR_NULL  # out_peers[1] missing, no multicast
+
+
+def gemm(**kw):
+    g = DlmGemm()
+    g.x, g.w, g.m, g.n, g.k, g.ldx, g.ldw = 0x1000, 0x2000, 32, 256, 128, 128, 128
+    g.workspace, g.workspace_bytes = 0x10000, 1 << 24
+    for k, v in kw.items():
+        setattr(g, k, v)
+    return g
+
+
+@pytest.mark.parametrize("kw, code", [
+    (dict(m=8), _lib.ERR_SHAPE), (dict(m=272), _lib.ERR_SHAPE), (dict(m=40), _lib.ERR_SHAPE), (dict(n=192), _lib.ERR_SHAPE),
+    (dict(k=96), _lib.ERR_SHAPE), (dict(ldx=64), _lib.ERR_ALIGN), (dict(ldw=132), _lib.ERR_ALIGN),
+    (dict(x=0x1004), _lib.ERR_ALIGN), (dict(workspace=0x10010), _lib.ERR_ALIGN), (dict(w=None), _lib.ERR_NULL),
+    (dict(splits=9), _lib.ERR_SHAPE),
+])
+def test_gemm_rejects_bad_arguments(kw, code):
+    assert _lib.lib().dlm_gemm_bf16(C.byref(gemm(**kw)), 0x9000, 256, 0, None) == code
+
+
+def test_fused_requires_matching_shapes():
+    c = comm(rows=32, n=256)
+    assert _lib.lib().dlm_rowpar_bf16(C.byref(gemm(m=64)), C.byref(c), None) == _lib.ERR_SHAPE
+    assert _lib.lib().dlm_rowpar_bf16(C.byref(gemm(n=512)), C.byref(c), None) == _lib.ERR_SHAPE
+
+
+def test_missing_library_is_an_import_error(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "libdlmrt_b200.so")
+    with pytest.raises(ImportError, match="no CPU or PyTorch fallback"):
+        _lib.lib()

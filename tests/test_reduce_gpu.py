@@ -1,0 +1,165 @@
+"""The stand-alone fused reduction (dlm_reduce_bf16 / _loopback through the Group mirror) against the CPU oracle and
+against the reference's own kernel, bit for bit."""
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import assert_norm_close, assert_same_bits, bits, randn_bf16
+from oracle import reduce as red
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def short_timeouts(monkeypatch):
+    from dlmrt_b200.distributed import parallel
+
+    monkeypatch.setattr(parallel, "TIMEOUT_NS", 500_000_000)
+
+
+def run_sequence(world, rows, n, calls, seed=0):
+    """`calls` reductions alternating over two call sites and all three modes; returns nothing, asserts parity."""
+    from dlmrt_b200.distributed.loopback import LoopbackWorld
+
+    lw = LoopbackWorld(world)
+    weight = randn_bf16(n, seed=seed + 99, std=0.1) + 1
+    hs = [randn_bf16(rows, n, seed=seed + 50 + r) for r in range(world)]
+    for i in range(calls):
+        mode = i % 3
+        partials = [randn_bf16(rows, n, seed=seed + 1000 * i + r) for r in range(world)]
+        site = f"s{i % 2}.{mode}"
+        p_bits = np.stack([bits(p) for p in partials])
+        if mode == 0:
+            outs = lw.reduce(partials, site=site)
+            want = red.reduce(p_bits)
+        elif mode == 1:
+            outs = lw.reduce(partials, site=site, weight=weight, eps=1e-6, scale=1.5)
+            want, _ = red.reduce_norm(p_bits, bits(weight), 1e-6, 1.5)
+        else:
+            h_before = np.stack([bits(h) for h in hs])
+            outs = lw.reduce(partials, site=site, hs=hs, weight=weight, eps=1e-6, scale=1.0)
+            want, h_after = red.reduce_norm(p_bits, bits(weight), 1e-6, 1.0, h_before)
+        torch.cuda.synchronize()
+        lw.check()
+        got = [bits(o) for o in outs]
+        for r in range(1, world):
+            assert_same_bits(got[r], got[0], f"call {i}: rank {r} vs rank 0")
+        if mode == 0:
+            assert_same_bits(got[0], want, f"call {i} K1")
+        else:
+            assert_norm_close(got[0], want, f"call {i} mode {mode}")
+        if mode == 2:
+            for r in range(world):
+                assert_same_bits(bits(hs[r]), h_after[r], f"call {i}: residual of rank {r}")
+
+
+@pytest.mark.parametrize("world, rows, n", [(1, 32, 256), (1, 256, 2560), (2, 32, 2048), (2, 256, 2560),
+                                            (4, 64, 2816), (8, 32, 2048), (8, 256, 2560), (4, 16, 8192)])
+def test_loopback_sequences_match_oracle(world, rows, n):
+    run_sequence(world, rows, n, calls=7)
+
+
+def test_special_values_survive():
+    """-0.0 sums to +0.0, infinities and NaN propagate as canonical values, nothing is mistaken for the sentinel."""
+    from dlmrt_b200.distributed.loopback import LoopbackWorld
+
+    lw = LoopbackWorld(2)
+    rows, n = 4, 256
+    a = torch.zeros(rows, n, dtype=torch.bfloat16, device="cuda")
+    b = torch.zeros(rows, n, dtype=torch.bfloat16, device="cuda")
+    a[0], b[0] = -0.0, -0.0
+    a[1, :8], b[1, :8] = float("inf"), float("-inf")
+    a[2, 8:16] = float("nan")
+    a[3], b[3] = 3.0e38, 3.0e38
+    outs = lw.reduce([a, b], site="special")
+    torch.cuda.synchronize()
+    lw.check()
+    want = red.reduce(np.stack([bits(a), bits(b)]))
+    assert_same_bits(bits(outs[0]), want, "special values")
+    assert_same_bits(bits(outs[1]), want, "special values, rank 1")
+
+
+def test_group_local_world_one_matches_oracle_and_rejects_repeated_site():
+    from dlmrt_b200.distributed.parallel import Group
+
+    g = Group.local("cuda:0")
+    p = randn_bf16(32, 2048, seed=3)
+    out = g.reduce(p, site="a")
+    torch.cuda.synchronize()
+    g.check()
+    assert_same_bits(bits(out), red.reduce(bits(p)[None]), "world 1")
+    with pytest.raises(ValueError, match="twice in a row"):
+        g.reduce(p, site="a")
+    with pytest.raises(ValueError, match="allocated"):
+        g.symmetric("out:a", (64, 2048))
+
+
+def test_withheld_push_times_out_without_trapping():
+    """A rank whose pushes never reach their destination: the owners' bounded waits run out, the status words say
+    so on every rank, the kernel returns normally and the GPU stays usable."""
+    import ctypes as C
+
+    from dlmrt_b200 import _lib
+    from dlmrt_b200.distributed import parallel
+    from dlmrt_b200.distributed.loopback import LoopbackWorld
+
+    parallel.TIMEOUT_NS = 2_000_000  # 2 ms
+    lw = LoopbackWorld(2)
+    rows, n = 8, 256
+    partials = [randn_bf16(rows, n, seed=r) for r in range(2)]
+    comms, outs = lw._comms(rows, n, "lost", 0, None, None, 0.0, 1.0)
+    lost = torch.full((3, 2, rows // 2, n), -1, dtype=torch.int16, device="cuda")
+    comms[1].recv[0] = lost.data_ptr()  # rank 1's pushes to rank 0 land in a buffer nobody reads
+    ptrs = (C.c_void_p * 2)(*[p.data_ptr() for p in partials])
+    _lib.check(_lib.lib().dlm_reduce_bf16_loopback(ptrs, comms, 2, None), "loopback")
+    torch.cuda.synchronize()
+    for g in lw.groups:
+        with pytest.raises(TimeoutError, match="never arrived"):
+            g.check()
+    # the context is alive and a fresh world works
+    run_sequence(2, 8, 256, calls=3, seed=7)
+
+
+def test_reference_kernel_agrees_bit_for_bit():
+    """This library's kernel, the reference's own kernel (built from its sources into oracle/_ref) and the CPU
+    oracle on the same seeded inputs, world 1 (one GPU): all three modes, several invocations."""
+    from oracle.build_ref import load_built
+
+    ref = load_built()
+    if ref is None:
+        pytest.skip("oracle/_ref was not built (python oracle/build_ref.py <reference>)")
+    from dlmrt_b200.distributed.parallel import Group
+
+    rows, n = 64, 2560
+    g = Group.local("cuda:0")
+    dev = "cuda"
+    recv = torch.full((3, 1, rows, n), -1, dtype=torch.int16, device=dev).view(torch.bfloat16)
+    recv_ptrs = torch.tensor([recv.data_ptr()], dtype=torch.int64, device=dev)
+    epochs = torch.zeros(rows + 96, dtype=torch.int32, device=dev)
+    ref_outs = [torch.full((rows, n), -1, dtype=torch.int16, device=dev).view(torch.bfloat16) for _ in range(2)]
+    weight = randn_bf16(n, seed=11, std=0.1) + 1
+    h_mine, h_ref = randn_bf16(rows, n, seed=12), randn_bf16(rows, n, seed=12)
+    last = None
+    for i in range(6):
+        mode = i % 3
+        p = randn_bf16(rows, n, seed=100 + i)
+        out = ref_outs[i % 2]
+        peers = torch.tensor([out.data_ptr()], dtype=torch.int64, device=dev)
+        rearm, rearm_numel = (last.data_ptr(), last.numel()) if last is not None else (0, 0)
+        fn = [ref.reduce, ref.reduce_norm, ref.reduce_norm_residual][mode]
+        fn(p, recv_ptrs, h_ref if mode == 2 else p, weight if mode else p, out, 0, peers, rearm, rearm_numel, epochs, 0,
+           1, 1e-6, 1.25, 96, 0, False)
+        last = out
+        site = f"r{i % 2}"
+        if mode == 0:
+            mine = g.reduce(p, site=site)
+        else:
+            mine = g.reduce_norm(p, h_mine if mode == 2 else None, weight, 1e-6, 1.25, site=site)
+        torch.cuda.synchronize()
+        g.check()
+        assert_same_bits(bits(mine), bits(out), f"call {i} mode {mode}: this kernel vs the reference kernel")
+        if mode == 2:
+            assert_same_bits(bits(h_mine), bits(h_ref), f"call {i}: residual stream")
+        if mode == 0:
+            assert_same_bits(bits(out), red.reduce(bits(p)[None]), f"call {i}: reference kernel vs CPU oracle")

@@ -1,0 +1,185 @@
+"""The tcgen05 row-parallel GEMM (dlm_gemm_bf16) and the fused projection + reduction (dlm_rowpar_bf16 / _loopback)
+against the CPU oracle."""
+
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import assert_norm_close, assert_same_bits, bits, randn_bf16
+from oracle import reduce as red
+from oracle import rowpar
+from oracle.bf16 import f32_to_bf16
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def short_timeouts(monkeypatch):
+    from dlmrt_b200.distributed import parallel
+
+    monkeypatch.setattr(parallel, "TIMEOUT_NS", 500_000_000)
+
+
+def gemm(x, w, splits=0):
+    from dlmrt_b200 import _lib
+    from dlmrt_b200._lib import DlmGemm
+
+    m, k = x.shape
+    n = w.shape[0]
+    out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+    ws = torch.zeros(_lib.lib().dlm_workspace_bytes(m, n, k), dtype=torch.uint8, device=x.device)
+    g = DlmGemm()
+    g.x, g.w, g.m, g.n, g.k, g.ldx, g.ldw = x.data_ptr(), w.data_ptr(), m, n, k, x.stride(0), w.stride(0)
+    g.workspace, g.workspace_bytes, g.splits = ws.data_ptr(), ws.numel(), splits
+    _lib.check(_lib.lib().dlm_gemm_bf16(C.byref(g), out.data_ptr(), n, 0, None), "gemm")
+    torch.cuda.synchronize()
+    return out
+
+
+def integer_case(m, n, k, seed):
+    """Small-integer operands: every product and partial sum is exact in FP32, so the BF16 result is the same whatever
+    the summation order, and the comparison with the oracle is bit for bit at any size."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randint(-3, 4, (m, k), generator=g).to(torch.bfloat16).cuda()
+    w = torch.randint(-2, 3, (n, k), generator=g).to(torch.bfloat16).cuda()
+    return x, w
+
+
+SHAPES = [(16, 128, 64), (32, 2048, 2048), (64, 2816, 512), (256, 2560, 4096), (256, 2560, 9728), (48, 256, 1216),
+          (256, 2816, 2176), (32, 2048, 64)]
+
+
+@pytest.mark.parametrize("m, n, k", SHAPES)
+def test_gemm_exact_on_integer_operands(m, n, k):
+    x, w = integer_case(m, n, k, seed=m + n + k)
+    want = f32_to_bf16(rowpar.gemm_f32(bits(x), bits(w)))
+    assert_same_bits(bits(gemm(x, w)), want, f"gemm {m}x{n}x{k}")
+
+
+@pytest.mark.parametrize("m, n, k", SHAPES)
+def test_gemm_within_tolerance_on_gaussian_operands(m, n, k):
+    """Tolerance of the GEMM partial: per row max-abs <= 2 BF16 ulp of the row's largest magnitude and relative L2
+    <= 4e-3 against float64 (bounds of the reference's tests/test_sdar_kernels.py:30, test_llada_nvfp4.py:166)."""
+    x, w = randn_bf16(m, k, seed=1), randn_bf16(n, k, seed=2, std=0.02)
+    out = gemm(x, w)
+    truth = rowpar.gemm_f64(bits(x), bits(w))
+    max_abs, rel = rowpar.row_errors(bits(out), truth)
+    assert max_abs.max() <= rowpar.ULPS and rel.max() <= rowpar.REL_L2, (max_abs.max(), rel.max())
+    # and no further from the truth than cuBLAS on the same GPU
+    _, rel_cublas = rowpar.row_errors(bits(torch.mm(x, w.t())), truth)
+    assert rel.max() <= 2 * rel_cublas.max() + 1e-6
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 8])
+def test_gemm_split_k_is_deterministic_and_ordered(splits):
+    m, n, k = 64, 256, 2048
+    x, w = randn_bf16(m, k, seed=5), randn_bf16(n, k, seed=6)
+    a, b = gemm(x, w, splits), gemm(x, w, splits)
+    assert_same_bits(bits(a), bits(b), "two runs")
+    # the split result is the in-order FP32 sum of the per-range products (dlmrt/ops/triton/gemm.py:3-7)
+    nkb = k // 64
+    edges = [s * nkb // splits * 64 for s in range(splits + 1)]
+    parts = [x[:, lo:hi].float() @ w[:, lo:hi].float().t() for lo, hi in zip(edges[:-1], edges[1:])]
+    acc = parts[0]
+    for p in parts[1:]:
+        acc = acc + p
+    from oracle.bf16 import bf16_to_f32
+
+    want = acc.cpu().numpy()
+    diff = np.abs(bf16_to_f32(bits(a)) - want)
+    # inside a range the tensor core's own summation tree applies, so equality is up to FP32 rounding of the
+    # accumulation plus the final BF16 rounding: half a BF16 ulp of the value plus a little of the row's scale
+    assert (diff <= np.abs(want) * 2.0 ** -8 + np.abs(want).max(axis=1, keepdims=True) * 2.0 ** -16).all()
+
+
+def test_gemm_strided_operands():
+    m, n, k = 32, 256, 256
+    xs, ws = randn_bf16(m, 2 * k, seed=7), randn_bf16(n, 3 * k, seed=8)
+    x, w = xs[:, k:], ws[:, k:2 * k]
+    from dlmrt_b200.layers.linear import Linear
+
+    lin = Linear(w.contiguous())
+    out = lin(x)
+    torch.cuda.synchronize()
+    assert rowpar.within_tolerance(bits(out), rowpar.gemm_f64(bits(x.contiguous()), bits(w.contiguous())))
+
+
+@pytest.mark.parametrize("world, m, n, k, splits", [(1, 32, 2048, 2048, 0), (1, 256, 2560, 4096, 0), (2, 256, 2560, 9728, 3),
+                                                     (2, 32, 2048, 2048, 2), (4, 256, 2816, 4096, 1), (8, 32, 2048, 2048, 1),
+                                                     (8, 256, 2048, 9728, 1), (4, 64, 2560, 1024, 0)])
+def test_fused_rowpar_loopback_matches_oracle(world, m, n, k, splits):
+    """Fused projection + reduction over `world` emulated ranks: with exact (integer) operands the whole pipeline is
+    bit-exact against the oracle; with Gaussian operands the reduction of this kernel's own GEMM partials is."""
+    from dlmrt_b200.distributed.loopback import LoopbackWorld
+
+    lw = LoopbackWorld(world)
+    weight = randn_bf16(n, seed=9, std=0.1) + 1
+    hs = [randn_bf16(m, n, seed=20 + r) for r in range(world)]
+    for i, mode in enumerate([0, 2, 1, 0]):
+        if i % 2:
+            x, w = randn_bf16(m, k, seed=30 + i), randn_bf16(n, k, seed=40 + i, std=0.02)
+        else:
+            x, w = integer_case(m, n, k, seed=i)
+        xs = [t.contiguous() for t in x.chunk(world, 1)]
+        ws = [t.contiguous() for t in w.chunk(world, 1)]
+        sp = splits or 1
+        partial_bits = np.stack([bits(gemm(xs[r], ws[r], sp)) for r in range(world)])
+        if i % 2 == 0:
+            _, exact = rowpar.rowpar(bits(x), bits(w), world)
+            assert_same_bits(partial_bits, exact, "integer partials")
+        site = f"site{i}"
+        if mode == 0:
+            outs = lw.rowpar(xs, ws, site=site, splits=sp)
+            want = red.reduce(partial_bits)
+        elif mode == 1:
+            outs = lw.rowpar(xs, ws, site=site, weight=weight, eps=1e-6, scale=0.5, splits=sp)
+            want, _ = red.reduce_norm(partial_bits, bits(weight), 1e-6, 0.5)
+        else:
+            h_before = np.stack([bits(h) for h in hs])
+            outs = lw.rowpar(xs, ws, site=site, hs=hs, weight=weight, eps=1e-6, splits=sp)
+            want, h_after = red.reduce_norm(partial_bits, bits(weight), 1e-6, 1.0, h_before)
+        torch.cuda.synchronize()
+        lw.check()
+        got = [bits(o) for o in outs]
+        for r in range(1, world):
+            assert_same_bits(got[r], got[0], f"call {i}: rank {r} vs rank 0")
+        if mode == 0:
+            assert_same_bits(got[0], want, f"call {i}")
+        else:
+            assert_norm_close(got[0], want, f"call {i} mode {mode}")
+        if mode == 2:
+            for r in range(world):
+                assert_same_bits(bits(hs[r]), h_after[r], f"call {i}: residual of rank {r}")
+
+
+def test_linear_defers_into_group_reduce():
+    """The drop-in pair of the reference's call sites: Linear(x, out=group.partial(...)) then group.reduce_norm(...)
+    (dlmrt/models/sdar/model.py:237-243) runs as one fused launch and matches GEMM-then-reduce."""
+    from dlmrt_b200 import _lib
+    from dlmrt_b200.distributed.parallel import Group
+    from dlmrt_b200.layers.linear import Linear
+
+    g = Group.local("cuda:0")
+    m, n, k = 256, 2560, 4096
+    x, w = randn_bf16(m, k, seed=1), randn_bf16(n, k, seed=2, std=0.02)
+    weight, h = randn_bf16(n, seed=3, std=0.1) + 1, randn_bf16(m, n, seed=4)
+    lin = Linear(w, fp8=False, group=g)
+    before = _lib.lib().dlm_launch_count()
+    p = lin(x, out=g.partial("0.post", (m, n)))
+    assert _lib.lib().dlm_launch_count() == before  # deferred: nothing ran yet
+    h_before = bits(h)[None]
+    out = g.reduce_norm(p, h, weight, 1e-6, site="0.post")
+    assert _lib.lib().dlm_launch_count() == before + 1  # one fused kernel
+    torch.cuda.synchronize()
+    g.check()
+    partial_bits = bits(Linear(w).gemm(x, torch.empty(m, n, dtype=torch.bfloat16, device="cuda")))[None]
+    want, h_after = red.reduce_norm(partial_bits, bits(weight), 1e-6, 1.0, h_before)
+    assert_norm_close(bits(out), want, "fused reduce_norm")
+    assert_same_bits(bits(h), h_after[0], "residual stream")
+    # flush materialises a deferred partial instead
+    p2 = lin(x, out=g.partial("1.post", (m, n)))
+    g.flush(p2)
+    torch.cuda.synchronize()
+    assert_same_bits(bits(p2), partial_bits[0], "flushed partial")
