@@ -1,0 +1,385 @@
+"""Benchmark of the tensor-parallel row-parallel hot path (fused projection + reduction) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+
+Workload (BASELINE config 2, the Qwen3-style decoder layer): hidden 2560, o_proj K = 4096, down_proj K = 9728,
+one 256-token block, BF16, TP = N. One STEP is the row-parallel hot path of a 36-layer round: for each layer the two
+fused kernels `o_proj -> reduce + residual + RMSNorm` and `down_proj -> reduce + residual + RMSNorm`
+(dlmrt/models/sdar/model.py:237-243), 72 launches, each layer with its own weights (2.56 GB at TP = 1, far above the
+126 MB L2, so weights stream from HBM every step). Steps are captured once in a CUDA graph and replayed, as the
+reference measures a round (dlmrt/entrypoints/bench/common.py:68-80).
+
+  value      microseconds per decoder layer (o_proj + down_proj with their reductions), inputs resident in HBM
+  e2e        the same through host buffers: pinned-host -> device copy of the step's activations, the graph replay, and
+             the device -> host copy of the last reduced block, all inside the timed region
+  roofline   dominant kernel rowpar_kernel: algorithmic bytes = the weight shard N * K/w * 2 per launch (HBM) or, when
+             larger in time, the reduction's per-GPU NVLink ingress 2 * (w-1)/w * M * N * 2, over the average launch
+             duration measured here with CUDA events
+  cpu_baseline / --impl reference   the CPU restatement of the same path (torch CPU matmul per K shard, rank-order FP32
+             sum, residual, RMSNorm) on the host cores. The reference has no CPU implementation of this path, so this
+             port is what is timed (kind "port").
+
+Synthetic data: weights ~ N(0, 0.02), activations ~ N(0, 1), seeded; no dataset or checkpoint is read.
+"""
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+HIDDEN, K_O, K_DOWN, ROWS, LAYERS, EPS = 2560, 4096, 9728, 256, 36, 1e-6
+NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction on this pool (nominal 900)
+FALLBACK_HBM_GBS = 6650.0
+
+
+def peaks():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        return float(json.loads(f.read_text())["hbm_gbs"]), "measured"
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class Clocks:
+    """Samples nvidia-smi during the timed region."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.file,
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        self.proc.wait()
+        self.file.seek(0)
+        rows = [[c.strip() for c in line.split(",")] for line in self.file.read().splitlines() if line.count(",") >= 5]
+        self.file.close()
+        os.unlink(self.file.name)
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        mhz = sorted(int(r[0]) for r in rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i] == "Active" for r in rows)]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": int(rows[0][1]), "reasons": reasons, "samples": len(rows)}
+
+
+def weight_bytes(world):
+    return HIDDEN * (K_O // world) * 2, HIDDEN * (K_DOWN // world) * 2
+
+
+def reduction_bytes(world):
+    return 2 * (world - 1) * ROWS * HIDDEN * 2 // world
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# CPU restatement (the reference arm and the cpu_baseline leg)
+# ---------------------------------------------------------------------------------------------------------------------
+def cpu_layer_seconds(world, repeats):
+    """One decoder layer's hot path on the host: per K shard a BF16 torch.mm (dlmrt/layers/linear.py:47-48 on CPU
+    tensors), the rank-ordered FP32 sum, BF16 rounding, residual add and RMSNorm (oracle.reduce order of operations),
+    for o_proj and down_proj. Returns the median seconds per layer over `repeats`."""
+    import torch
+
+    g = torch.Generator().manual_seed(0)
+    h = torch.randn(ROWS, HIDDEN, generator=g).to(torch.bfloat16)
+    norm = (torch.randn(HIDDEN, generator=g) * 0.1 + 1).to(torch.bfloat16)
+    ops = []
+    for k in (K_O, K_DOWN):
+        x = torch.randn(ROWS, k, generator=g).to(torch.bfloat16)
+        w = (torch.randn(HIDDEN, k, generator=g) * 0.02).to(torch.bfloat16)
+        ops.append(([s.contiguous() for s in x.chunk(world, 1)], [s.contiguous() for s in w.chunk(world, 1)]))
+
+    def layer(h):
+        for xs, ws in ops:
+            acc = torch.zeros(ROWS, HIDDEN)
+            for x, w in zip(xs, ws):  # rank order
+                acc = acc + torch.mm(x, w.t()).float()
+            v = acc.to(torch.bfloat16).float() + h.float()
+            h = v.to(torch.bfloat16)
+            out = (v * torch.rsqrt((v * v).mean(-1, keepdim=True) + EPS) * norm.float()).to(torch.bfloat16)
+        return h, out
+
+    layer(h)
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        layer(h)
+        times.append(time.perf_counter() - t0)
+    times.sort()
+    return times[len(times) // 2], torch.get_num_threads()
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    world = args.gpus
+    for _ in range(max(args.warmup, 1) - 1):
+        cpu_layer_seconds(world, 1)
+    sec, cores = cpu_layer_seconds(world, max(args.steps, 3))
+    us = sec * 1e6
+    sample = f"one decoder layer (o_proj + down_proj, {ROWS} rows) per step on the host, median of {max(args.steps, 3)}"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": round(us, 1), "unit": "us", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3 * LAYERS, 3),
+        "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": config(world),
+        "cpu_baseline": {"value": round(us, 1), "unit": "us", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": round(us, 1), "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+METRIC = "fused row-parallel projection+reduction latency per decoder layer (o_proj + down_proj), denoise round"
+
+
+def config(world):
+    return {"workload": f"BASELINE config 2: Qwen3-style layer, hidden {HIDDEN}, o_proj K {K_O}, down_proj K {K_DOWN}, "
+                        f"{ROWS}-token block, BF16, TP={world}; a step = {LAYERS} layers x 2 fused "
+                        "projection+reduce+residual+RMSNorm launches with per-layer weights",
+            "tp": world, "rows": ROWS, "hidden": HIDDEN, "layers": LAYERS,
+            "l2": f"weights of a step ({sum(weight_bytes(world)) * LAYERS / 1e6:.0f} MB per GPU) exceed the 126 MB L2"
+                  if sum(weight_bytes(world)) * LAYERS > 130e6 else "L2 flushed by a 256 MB write between steps"}
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------------------------------
+def run_gpu(args, rank, world):
+    import torch
+
+    from dlmrt_b200 import _lib
+    from dlmrt_b200.distributed import parallel
+    from dlmrt_b200.layers.linear import Linear
+
+    if world > 1:
+        import torch.distributed as dist
+
+        group = parallel.init()
+        device = group.device
+    else:
+        device = torch.device("cuda", 0)
+        torch.cuda.set_device(device)
+        group = parallel.Group.local(device)
+    lib = _lib.lib()
+    if lib.dlm_device_arch() != 100:
+        raise RuntimeError("bench.py needs an sm_100 GPU: there is no fallback path")
+
+    g = torch.Generator().manual_seed(1 + rank)
+    ko, kd = K_O // world, K_DOWN // world
+    lin_o = [Linear((torch.randn(HIDDEN, ko, generator=g) * 0.02).to(torch.bfloat16).to(device), group=group)
+             for _ in range(LAYERS)]
+    lin_d = [Linear((torch.randn(HIDDEN, kd, generator=g) * 0.02).to(torch.bfloat16).to(device), group=group)
+             for _ in range(LAYERS)]
+    gs = torch.Generator().manual_seed(7)  # identical on every rank
+    norms = [(torch.randn(HIDDEN, generator=gs) * 0.1 + 1).to(torch.bfloat16).to(device) for _ in range(2 * LAYERS)]
+    h0 = torch.randn(ROWS, HIDDEN, generator=gs).to(torch.bfloat16)
+    h = h0.to(device)
+    host_xo = torch.randn(ROWS, ko, generator=g).to(torch.bfloat16).pin_memory()
+    host_xd = torch.randn(ROWS, kd, generator=g).to(torch.bfloat16).pin_memory()
+    x_o, x_d = host_xo.to(device), host_xd.to(device)
+    host_out = torch.empty(ROWS, HIDDEN, dtype=torch.bfloat16).pin_memory()
+    flush = None
+    if sum(weight_bytes(world)) * LAYERS <= 130e6:
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+    def step():
+        out = None
+        for i in range(LAYERS):
+            p = lin_o[i](x_o, out=group.partial(f"{i}.o", (ROWS, HIDDEN)))
+            group.reduce_norm(p, h, norms[2 * i], EPS, site=f"{i}.post")
+            p = lin_d[i](x_d, out=group.partial(f"{i}.down", (ROWS, HIDDEN)))
+            out = group.reduce_norm(p, h, norms[2 * i + 1], EPS, site=f"{i + 1}.input")
+        return out
+
+    stream = torch.cuda.Stream(device)
+    with torch.cuda.stream(stream):
+        for _ in range(2):  # eager: allocates every symmetric buffer, in the same order on every rank
+            out = step()
+        stream.synchronize()
+        group.check()
+        before = lib.dlm_launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            out = step()
+        launches_per_step = lib.dlm_launch_count() - before
+
+    def barrier():
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(device)
+
+    def timed(fn, steps):
+        """Total milliseconds of `steps` calls on `stream`, CUDA events, max over ranks."""
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        with torch.cuda.stream(stream):
+            start.record(stream)
+            for _ in range(steps):
+                fn()
+            stop.record(stream)
+        barrier()
+        ms = torch.tensor([start.elapsed_time(stop)], device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    def device_step():
+        if flush is not None:
+            flush.fill_(1)
+        graph.replay()
+
+    def e2e_step():
+        x_o.copy_(host_xo, non_blocking=True)
+        x_d.copy_(host_xd, non_blocking=True)
+        if flush is not None:
+            flush.fill_(1)
+        graph.replay()
+        host_out.copy_(out, non_blocking=True)
+
+    flush_ms = 0.0
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            device_step()
+    if flush is not None:
+        flush_ms = timed(lambda: flush.fill_(1), args.steps) / args.steps
+    clocks = Clocks(device.index) if rank == 0 else None
+    ms = timed(device_step, args.steps) / args.steps - flush_ms
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            e2e_step()
+    e2e_ms = timed(e2e_step, args.steps) / args.steps - flush_ms
+    clock_report = clocks.stop() if clocks else None
+    group.check()
+
+    # The reference's own GPU building blocks on the same box: cuBLAS torch.mm into the partial, then the reference's
+    # reduce_norm_residual kernel built from its sources (oracle/_ref). Informational; absent when it was not built.
+    ref_gpu = reference_gpu_path(torch, group, lin_o, lin_d, norms, x_o, x_d, h0.to(device), stream, timed, args, world)
+
+    if rank != 0:
+        return
+    hbm, which = peaks()
+    wo, wd = weight_bytes(world)
+    launches = 2 * LAYERS
+    avg_launch_s = ms * 1e-3 / launches
+    t_hbm = (wo + wd) / 2 / (hbm * 1e9)
+    t_link = reduction_bytes(world) / (NVLINK_GBS * 1e9)
+    if t_hbm >= t_link:
+        roof = {"bound": "hbm", "achieved": round((wo + wd) / 2 / avg_launch_s / 1e9, 1), "peak": hbm, "unit": "GB/s"}
+    else:
+        roof = {"bound": "nvlink", "achieved": round(reduction_bytes(world) / avg_launch_s / 1e9, 1), "peak": NVLINK_GBS,
+                "unit": "GB/s"}
+    roof["frac"] = round(roof["achieved"] / roof["peak"], 4)
+    roof["peak_source"] = f"of {which}"
+    roof["kernel"] = "rowpar_kernel"
+    roof["algorithmic_bytes_per_launch"] = (wo + wd) // 2 if roof["bound"] == "hbm" else reduction_bytes(world)
+    roof["avg_launch_us"] = round(avg_launch_s * 1e6, 2)
+    traffic = ROOT / "profiles" / "rowpar_kernel_traffic.json"
+    roof["traffic"] = json.loads(traffic.read_text()).get(f"tp{world}") if traffic.exists() else None
+
+    cpu_sec, cores = cpu_layer_seconds(world, 5) if world == 1 else (None, None)
+    line = {
+        "metric": METRIC, "value": round(ms * 1e3 / LAYERS, 2), "unit": "us", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config(world),
+        "e2e": {"value": round(e2e_ms * 1e3 / LAYERS, 2), "unit": "us",
+                "h2d_bytes_per_step": host_xo.numel() * 2 + host_xd.numel() * 2, "d2h_bytes_per_step": host_out.numel() * 2},
+        "gpu_launches": int(launches_per_step * args.steps), "roofline": roof, "clocks": clock_report,
+        "timing": "CUDA events on the launching stream around K graph replays, max over ranks",
+    }
+    if cpu_sec is not None:
+        line["cpu_baseline"] = {"value": round(cpu_sec * 1e6, 1), "unit": "us", "cores": cores, "kind": "port",
+                                "sample": "one decoder layer (o_proj + down_proj) on the host, median of 5"}
+    if ref_gpu is not None:
+        line["reference_gpu_path"] = ref_gpu
+    print(json.dumps(line))
+
+
+def reference_gpu_path(torch, group, lin_o, lin_d, norms, x_o, x_d, h, stream, timed, args, world):
+    """torch.mm (cuBLAS) into the symmetric partial followed by the reference's own reduce_norm_residual kernel, the
+    same 72 operations, captured in a graph and timed the same way. Returns None when oracle/_ref is not present."""
+    try:
+        from oracle.build_ref import load_built
+
+        ref = load_built()
+    except Exception:  # noqa: BLE001
+        ref = None
+    if ref is None:
+        return None
+    device = group.device
+    R = ROWS // world
+    recv = group.symmetric("ref.recv", (3, world, R, HIDDEN), armed=True)
+    recv_ptrs = torch.tensor(group.peer_addresses(recv), dtype=torch.int64, device=device)
+    epochs = torch.zeros(R + 96, dtype=torch.int32, device=device)
+    partial = group.symmetric("ref.partial", (ROWS, HIDDEN))
+    outs = [group.symmetric(f"ref.out{i}", (ROWS, HIDDEN), armed=True) for i in range(2 * LAYERS)]
+    peers = [group.peers(o) for o in outs]
+    mcs = [group.multicast(o) for o in outs]
+    state = {"last": None}
+
+    def step():
+        for i in range(2 * LAYERS):
+            lin, x = (lin_o[i // 2], x_o) if i % 2 == 0 else (lin_d[i // 2], x_d)
+            torch.mm(x, lin.weight.t(), out=partial)
+            last = state["last"]
+            rearm, numel = (last.data_ptr(), last.numel()) if last is not None else (0, 0)
+            ref.reduce_norm_residual(partial, recv_ptrs, h, norms[i], outs[i], mcs[i], peers[i], rearm, numel, epochs,
+                                     group.rank, world, EPS, 1.0, 96, 0, True)
+            state["last"] = outs[i]
+
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            step()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+        for _ in range(3):
+            graph.replay()
+    ms = timed(graph.replay, args.steps) / args.steps
+    return {"value": round(ms * 1e3 / LAYERS, 2), "unit": "us",
+            "what": "torch.mm (cuBLAS) + the reference's tp_comm reduce_norm_residual kernel, same 72 ops in a CUDA graph"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (torchrun --nproc-per-node {args.gpus}); "
+                         f"WORLD_SIZE is {world}")
+    run_gpu(args, rank, world)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -230,7 +230,16 @@ int rowpar_smem_bytes(int m, int stages) {
 template <int NR>
 static int launch_impl(const RowparParams<NR>& p, dim3 grid, const LaunchOpts& o) {
     const int smem = rowpar_smem_bytes(p.g[0].m, p.g[0].stages);
-    cudaError_t err = cudaFuncSetAttribute(rowpar_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    // Raised once per device to the largest configuration (not a stream operation, but kept out of graph captures).
+    static bool raised[64] = {};
+    cudaError_t err = cudaSuccess;
+    int dev = 0;
+    (void)cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !raised[dev]) {
+        err = cudaFuncSetAttribute(rowpar_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   rowpar_smem_bytes(256, rowpar_stages(256)));
+        raised[dev] = err == cudaSuccess;
+    }
     if (err == cudaSuccess) {
         cudaLaunchConfig_t config{};
         config.gridDim = grid;
