@@ -28,7 +28,7 @@ class DlmComm(C.Structure):
 class DlmGemm(C.Structure):
     _fields_ = [("x", C.c_void_p), ("w", C.c_void_p), ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
                 ("ldx", C.c_int64), ("ldw", C.c_int64), ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
-                ("splits", C.c_int32)]
+                ("splits", C.c_int32), ("token_tiles", C.c_int32)]
 
 
 class DlmStatus(C.Structure):
@@ -54,7 +54,7 @@ SIGNATURES = {
     "dlm_rowpar_bf16": (C.c_int, [C.POINTER(DlmGemm), C.POINTER(DlmComm), C.c_void_p]),
     "dlm_rowpar_bf16_loopback": (C.c_int, [C.POINTER(DlmGemm), C.POINTER(DlmComm), C.c_int, C.c_void_p]),
     "dlm_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
-    "dlm_choose_splits": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int]),
+    "dlm_choose_tiling": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "dlm_status_read": (C.c_int, [C.c_void_p, C.POINTER(DlmStatus), C.c_void_p]),
     "dlm_abi_check": (C.c_int, [C.c_size_t, C.c_size_t, C.c_size_t]),
     "dlm_strerror": (C.c_char_p, [C.c_int]),

@@ -126,16 +126,35 @@ int make_map(CUtensorMap* map, const void* base, int rows, int cols, long long l
     return DLM_OK;
 }
 
-int choose_splits(int m, int n, int k, int max_ctas, int sms) {
-    (void)m;
-    const int avail = max_ctas > 0 && max_ctas < sms ? max_ctas : sms;
-    const int tiles = n / kBlockF, nkb = k / kBlockK;
-    int s = avail / tiles;
-    const int by_k = nkb / 4 > 0 ? nkb / 4 : 1;  // at least four k-blocks per CTA: below that the partial tiles cost more than they save
-    if (s > by_k) s = by_k;
-    if (s > kMaxSplits) s = kMaxSplits;
-    if (s < 1) s = 1;
-    return s;
+// Picks (token tiles, K splits) for a [m, n, k] GEMM on `avail` CTAs with a small cost model, in microseconds:
+// a CTA streams ceil(nkb / S) k-blocks of (16 KB of W + tokens-per-tile x 128 B of x) at what one SM pulls from L2,
+// never faster than the whole weight shard streams from HBM; several splits add the partial-tile round trip through L2
+// and the rendezvous. Token tiles re-read W from L2 but need no rendezvous, which wins for short K (high TP degrees);
+// K splits win for long K (TP = 1).
+void choose_tiling(int m, int n, int k, int avail, int* tiles_out, int* splits_out) {
+    const double sm_bytes_per_us = 120e3, hbm_bytes_per_us = 6.0e6, rendezvous_us = 3.0;
+    const int feature_tiles = n / kBlockF, nkb = k / kBlockK;
+    double best = 1e30;
+    *tiles_out = 1;
+    *splits_out = 1;
+    for (int t = 1; t <= 8; t *= 2) {
+        if (m % (16 * t)) break;
+        const int mt = m / t;
+        if (feature_tiles * t > avail || feature_tiles * t > kMaxTiles) break;
+        for (int sp = 1; sp <= kMaxSplits && sp <= nkb; ++sp) {
+            if (feature_tiles * t * sp > avail) break;
+            const int kb = (nkb + sp - 1) / sp;
+            double us = kb * (16384.0 + mt * 128.0) / sm_bytes_per_us;
+            const double hbm = static_cast<double>(n) * k * 2 / hbm_bytes_per_us;
+            if (us < hbm) us = hbm;
+            if (sp > 1) us += rendezvous_us + 2.0 * mt * kBlockF * 4 / sm_bytes_per_us;
+            if (us < best - 1e-9) {
+                best = us;
+                *tiles_out = t;
+                *splits_out = sp;
+            }
+        }
+    }
 }
 
 int check_gemm(const DlmGemm* g) {
@@ -147,29 +166,47 @@ int check_gemm(const DlmGemm* g) {
     if (g->ldx < g->k || g->ldw < g->k || g->ldx % 8 || g->ldw % 8) return DLM_ERR_ALIGN;
     if (!aligned16(g->x) || !aligned16(g->w) || (reinterpret_cast<uintptr_t>(g->workspace) & 255)) return DLM_ERR_ALIGN;
     if (g->splits < 0 || g->splits > kMaxSplits) return DLM_ERR_SHAPE;
+    if (g->token_tiles < 0 || (g->token_tiles > 0 && (g->m % (16 * g->token_tiles) || g->token_tiles > 16)))
+        return DLM_ERR_SHAPE;
     return DLM_OK;
 }
 
 // Fills the device-side GEMM block; returns the per-rank grid in *grid.
 int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid) {
     std::memset(d, 0, sizeof(*d));
-    int rc = make_map(&d->tm_w, g->w, g->n, g->k, g->ldw, kBlockF);
-    if (rc == DLM_OK) rc = make_map(&d->tm_x, g->x, g->m, g->k, g->ldx, g->m);
-    if (rc != DLM_OK) return rc;
-    const int tiles = g->n / kBlockF, nkb = g->k / kBlockK;
-    int splits = g->splits > 0 ? g->splits : choose_splits(g->m, g->n, g->k, max_ctas, sms);
-    if (splits > nkb) splits = nkb;
     const int avail = max_ctas > 0 && max_ctas < sms ? max_ctas : sms;
-    if (tiles * splits > avail) return DLM_ERR_GRID;
-    const size_t need = 256 + static_cast<size_t>(splits) * g->m * g->n * sizeof(float);
+    const int feature_tiles = g->n / kBlockF, nkb = g->k / kBlockK;
+    int token_tiles = g->token_tiles, splits = g->splits;
+    if (token_tiles == 0 || splits == 0) {
+        int t = 1, sp = 1;
+        choose_tiling(g->m, g->n, g->k, avail, &t, &sp);
+        if (token_tiles == 0 && splits == 0) {
+            token_tiles = t;
+            splits = sp;
+        } else if (token_tiles == 0) {
+            token_tiles = 1;
+        } else {
+            splits = 1;
+        }
+    }
+    if (splits > nkb) splits = nkb;
+    const int tiles = feature_tiles * token_tiles;
+    if (tiles > kMaxTiles || tiles * splits > avail) return DLM_ERR_GRID;
+    const int mt = g->m / token_tiles;
+    int rc = make_map(&d->tm_w, g->w, g->n, g->k, g->ldw, kBlockF);
+    if (rc == DLM_OK) rc = make_map(&d->tm_x, g->x, g->m, g->k, g->ldx, mt);
+    if (rc != DLM_OK) return rc;
+    const size_t need = kWorkspaceHeader + (splits > 1 ? static_cast<size_t>(splits) * g->m * g->n * sizeof(float) : 0);
     if (g->workspace_bytes < static_cast<int64_t>(need)) return DLM_ERR_WORKSPACE;
-    d->counters = static_cast<int*>(g->workspace);
-    d->ws = reinterpret_cast<float*>(static_cast<char*>(g->workspace) + 256);
+    d->gen = static_cast<int*>(g->workspace);
+    d->counters = d->gen + kEpochSlots;
+    d->ws = reinterpret_cast<float*>(static_cast<char*>(g->workspace) + kWorkspaceHeader);
     d->m = g->m;
     d->n = g->n;
     d->k = g->k;
     d->splits = splits;
-    d->stages = rowpar_stages(g->m);
+    d->token_tiles = token_tiles;
+    d->stages = rowpar_stages(mt);
     *grid = tiles * splits;
     return DLM_OK;
 }
@@ -278,9 +315,7 @@ int dlm_rowpar_bf16_loopback(const DlmGemm* gemm, const DlmComm* comm, int nrank
         if (gemm[i].m != gemm[0].m || gemm[i].n != gemm[0].n || gemm[i].k != gemm[0].k) return DLM_ERR_SHAPE;
         int cap = comm[0].max_ctas > 0 && comm[0].max_ctas < per_rank ? comm[0].max_ctas : per_rank;
         int gi = 0;
-        DlmGemm gg = gemm[i];
-        if (gg.splits == 0) gg.splits = choose_splits(gg.m, gg.n, gg.k, cap, per_rank);
-        rc = fill_gemm(&p.g[i], &gg, cap, per_rank, &gi);
+        rc = fill_gemm(&p.g[i], &gemm[i], cap, per_rank, &gi);
         if (rc != DLM_OK) return rc;
         if (i > 0 && gi != grid) return DLM_ERR_SHAPE;
         grid = gi;
@@ -293,17 +328,19 @@ int dlm_rowpar_bf16_loopback(const DlmGemm* gemm, const DlmComm* comm, int nrank
 size_t dlm_workspace_bytes(int m, int n, int k) {
     (void)k;
     if (m <= 0 || n <= 0) return 0;
-    return 256 + static_cast<size_t>(kMaxSplits) * static_cast<size_t>(m) * static_cast<size_t>(n) * sizeof(float);
+    return kWorkspaceHeader +
+           static_cast<size_t>(kMaxSplits) * static_cast<size_t>(m) * static_cast<size_t>(n) * sizeof(float);
 }
 
-int dlm_choose_splits(int m, int n, int k, int max_ctas) {
+int dlm_choose_tiling(int m, int n, int k, int max_ctas, int* token_tiles, int* splits) {
+    if (token_tiles == nullptr || splits == nullptr) return DLM_ERR_NULL;
+    if (m < 16 || m > DLM_MAX_M || m % 16 || n < kBlockF || n % kBlockF || k < kBlockK || k % kBlockK)
+        return DLM_ERR_SHAPE;
     DeviceInfo info;
     int sms = 148;
     if (device_info(&info) == DLM_OK) sms = info.sms;
-    if (n < kBlockF || n % kBlockF || k < kBlockK || k % kBlockK) return DLM_ERR_SHAPE;
-    int s = choose_splits(m, n, k, max_ctas, sms);
-    const int nkb = k / kBlockK;
-    return s > nkb ? nkb : s;
+    choose_tiling(m, n, k, max_ctas > 0 && max_ctas < sms ? max_ctas : sms, token_tiles, splits);
+    return DLM_OK;
 }
 
 int dlm_status_read(int32_t* device_status, DlmStatus* out, dlm_stream_t stream) {

@@ -24,6 +24,8 @@ namespace dlm {
 
 constexpr int kMaxWorld = 8;
 constexpr int kEpochSlots = 256;
+constexpr int kStampSlots = 8;  // %globaltimer stamps per CTA: 0 start, 1 pushed, 2 owned rows broadcast, 3 collected;
+                                // fused kernels add 4 accumulator ready, 5 partial tile written, 6 tile summed and pushed
 
 enum Mode { kReduce = 0, kReduceNorm = 1, kReduceNormResidual = 2 };
 
@@ -53,7 +55,7 @@ struct CommCtx {
 };
 
 __device__ __forceinline__ void stamp(const CommDev& c, const CommCtx& x, int phase) {
-    if (c.stamps && threadIdx.x == 0) c.stamps[x.block * 4 + phase] = globaltimer();
+    if (c.stamps && threadIdx.x == 0) c.stamps[x.block * kStampSlots + phase] = globaltimer();
 }
 
 __device__ __forceinline__ CommCtx comm_begin(const CommDev& c, int block, int blocks) {
@@ -199,8 +201,9 @@ __device__ __forceinline__ void own_and_collect(const CommDev& c, const CommCtx&
         }
     }
     stamp(c, x, 2);
-    // Collect: rows s * R + r of this rank's OUT copy, from every owner s.
-    if (active) {
+    // Collect: rows s * R + r of this rank's OUT copy, from every owner s. With one rank every row of OUT was stored
+    // by this very grid, so it is complete when the kernel ends and there is nothing to wait for.
+    if (active && c.world > 1) {
         for (int r = x.block; r < c.R; r += x.blocks)
             if (!poll_all(c.out + static_cast<size_t>(r) * c.n + col, x.slot_elems, c.world, slots, c, x, kPhaseOut)) break;
     }

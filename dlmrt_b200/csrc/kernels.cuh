@@ -12,18 +12,21 @@ constexpr int kBlockF = 128;        // weight rows (output features) per tile: t
 constexpr int kBlockK = 64;         // BF16 per k-block: one 128-byte swizzled row
 constexpr int kUmmaK = 16;          // K of one tcgen05.mma kind::f16
 constexpr int kMaxSplits = 8;
+constexpr int kMaxTiles = 128;      // (feature tiles) x (token tiles) of one GEMM
+constexpr int kWorkspaceHeader = 2048;  // int32 gen[256] then int32 counters[2][128]
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 200 * 1024;
 
 // The GEMM half of one rank. `out` is used by the plain GEMM (no communication) only.
 struct alignas(64) GemmDev {
     CUtensorMap tm_w;  // W [n, k] BF16, box 64 x 128, 128-byte swizzle
-    CUtensorMap tm_x;  // x [m, k] BF16, box 64 x m, 128-byte swizzle
-    float* ws;         // FP32 partial tiles [n / 128][splits][m][128]
-    int* counters;     // [n / 128] arrivals per feature tile, self-resetting
+    CUtensorMap tm_x;  // x [m, k] BF16, box 64 x (m / token_tiles), 128-byte swizzle
+    float* ws;         // FP32 partial tiles [tile][split][tokens per tile][128]
+    int* gen;          // [256] launch generation of this workspace, every entry kept equal (like the epochs)
+    int* counters;     // [2][kMaxTiles] split-K arrivals per tile, banked by generation parity
     __nv_bfloat16* out;
     long long ldo;
-    int m, n, k, splits, stages;
+    int m, n, k, splits, token_tiles, stages;
 };
 
 template <int NR>

@@ -13,11 +13,13 @@
 //   warp 1   MMA issuer: four tcgen05.mma kind::f16 (K = 16) per k-block, FP32 accumulator in TMEM; tcgen05.commit
 //            frees the stage and finally signals the epilogue.
 //   warp 2   TMEM allocation / release.
-//   warps 4-11  epilogue: tcgen05.ld the accumulator and write this CTA's FP32 partial tile to the workspace.
-//   The last CTA to finish a feature tile (an arrival counter per tile) sums the `splits` partial tiles in split
-//   order, so the value does not depend on which CTA finishes last, rounds to BF16 and either stores the tile (plain
-//   GEMM) or pushes each token row's 256 bytes straight into the owner rank's receive slot over NVLink. Then every CTA
-//   runs the re-arm / own / collect phases of the reduction (comm.cuh).
+//   warps 4-11  epilogue: tcgen05.ld the accumulator.
+//   The grid is (feature tiles) x (token tiles) x (K splits), at most one CTA per SM. With one split the BF16 tile is
+//   staged in shared memory and goes straight out. With several, every CTA writes its FP32 partial tile to the
+//   workspace, the CTAs of a tile meet on an arrival counter, and each then sums its share of the tile's tokens over
+//   the splits in split order (the value never depends on timing). Either way each token row's 256 bytes are stored
+//   (plain GEMM) or pushed straight into the owner rank's receive slot over NVLink, and every CTA goes on to the
+//   re-arm / own / collect phases of the reduction (comm.cuh).
 #include "kernels.cuh"
 
 namespace dlm {
@@ -29,7 +31,6 @@ struct SmemLayout {
     uint64_t empty[kMaxStages];
     uint64_t acc_full;
     uint32_t tmem_base;
-    int finisher;
     float scratch[32];
 };
 
@@ -51,18 +52,23 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
     const CommDev& c = p.c[slot];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int block = static_cast<int>(blockIdx.x), blocks = static_cast<int>(gridDim.x);
+    if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 7] = globaltimer();
 
-    // Tile and K range of this CTA.
-    const int f = block / g.splits, s = block - f * g.splits;
+    // This CTA's output tile (feature tile f, token tile t) and K range (split s).
+    const int s = block % g.splits;
+    const int tile = block / g.splits;  // f * token_tiles + t
+    const int f = tile / g.token_tiles, t = tile - f * g.token_tiles;
+    const int mt = g.m / g.token_tiles;  // tokens of this tile: the MMA's N
+    const int token0 = t * mt;
     const int nkb = g.k / kBlockK;
     const int kb0 = static_cast<int>(static_cast<long long>(s) * nkb / g.splits);
     const int kb1 = static_cast<int>(static_cast<long long>(s + 1) * nkb / g.splits);
     const int iters = kb1 - kb0;
-    const int stage_bytes = kTileBytesW + g.m * kBlockK * 2;
+    const int stage_bytes = kTileBytesW + mt * kBlockK * 2;
 
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     SmemLayout* sm = reinterpret_cast<SmemLayout*>(tiles + g.stages * stage_bytes);
-    const uint32_t cols = tmem_cols(g.m);
+    const uint32_t cols = tmem_cols(mt);
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < g.stages; ++i) {
@@ -79,7 +85,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem = sm->tmem_base;
-    // Generous budget for the local pipeline; the cross-rank waits take theirs from the caller (comm_begin).
+    // Budget of the local pipeline and of the split-K rendezvous; the cross-rank waits take theirs in comm_begin.
     const long long pipeline_deadline = globaltimer() + (c.timeout_ns > 0 ? c.timeout_ns : 2000000000ll);
 
     if (warp == 0) {
@@ -92,8 +98,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
             }
             pdl_wait();
             for (int it = 0; it < pre; ++it)
-                tma_load_2d(tiles + it * stage_bytes + kTileBytesW, &g.tm_x, &sm->full[it], (kb0 + it) * kBlockK, 0,
-                            kEvictLast);
+                tma_load_2d(tiles + it * stage_bytes + kTileBytesW, &g.tm_x, &sm->full[it], (kb0 + it) * kBlockK,
+                            token0, kEvictLast);
             for (int it = pre; it < iters; ++it) {
                 const int st = it % g.stages;
                 const uint32_t parity = ((it / g.stages) & 1) ^ 1;
@@ -104,13 +110,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
                 mbar_expect_tx(&sm->full[st], static_cast<uint32_t>(stage_bytes));
                 tma_load_2d(tiles + st * stage_bytes, &g.tm_w, &sm->full[st], (kb0 + it) * kBlockK, f * kBlockF,
                             kEvictFirst);
-                tma_load_2d(tiles + st * stage_bytes + kTileBytesW, &g.tm_x, &sm->full[st], (kb0 + it) * kBlockK, 0,
-                            kEvictLast);
+                tma_load_2d(tiles + st * stage_bytes + kTileBytesW, &g.tm_x, &sm->full[st], (kb0 + it) * kBlockK,
+                            token0, kEvictLast);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc_bf16(kBlockF, g.m);
+            const uint32_t idesc = umma_idesc_bf16(kBlockF, mt);
             for (int it = 0; it < iters; ++it) {
                 const int st = it % g.stages;
                 const uint32_t parity = (it / g.stages) & 1;
@@ -133,7 +139,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
     } else if (warp >= 4) {
         // Epilogue: thread `lane` of a warp holds feature 32 * quarter + lane; 16 token columns per tcgen05.ld.
         const int quarter = warp & 3, half = (warp - 4) >> 2;
-        float* tile = g.ws + (static_cast<size_t>(f) * g.splits + s) * g.m * kBlockF;
         const int feature = quarter * 32 + lane;
         bool ok = true;
         if (iters > 0) {
@@ -141,8 +146,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
             if (!ok) report(c.status, kErrTimeout, 0, kPhasePipeline, 2);
             tcgen05_fence_after();
         }
-        pdl_wait();  // the workspace may still be read by the previous kernel of the chain
-        for (int chunk = half; chunk < g.m / 16; chunk += 2) {
+        if (c.stamps && threadIdx.x == 128) c.stamps[block * kStampSlots + 4] = globaltimer();
+        // One K split: the BF16 tile is staged in shared memory, token-major, over the drained pipeline stages.
+        // Several: this CTA's FP32 partial tile goes to the workspace (which the previous kernel of the chain may
+        // still be reading, hence the wait).
+        float* part = g.ws + (static_cast<size_t>(tile) * g.splits + s) * mt * kBlockF;
+        __nv_bfloat16* staged = reinterpret_cast<__nv_bfloat16*>(tiles);
+        if (g.splits > 1) pdl_wait();
+        for (int chunk = half; chunk < mt / 16; chunk += 2) {
             uint32_t r[16];
             if (iters > 0 && ok) {
                 tmem_load_16(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + chunk * 16, r);
@@ -151,63 +162,101 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
 #pragma unroll
                 for (int j = 0; j < 16; ++j) r[j] = 0;
             }
+            if (g.splits > 1) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) tile[static_cast<size_t>(chunk * 16 + j) * kBlockF + feature] = __uint_as_float(r[j]);
+                for (int j = 0; j < 16; ++j)
+                    part[static_cast<size_t>(chunk * 16 + j) * kBlockF + feature] = __uint_as_float(r[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    staged[(chunk * 16 + j) * kBlockF + feature] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            }
         }
         tcgen05_fence_before();
     }
     pdl_wait();
-    __threadfence();
+    if (g.splits > 1) __threadfence();
     __syncthreads();
+    if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 5] = globaltimer();
     if (warp == 2) {
         tcgen05_fence_after();
         tmem_dealloc(tmem, cols);
     }
-    if (threadIdx.x == 0) {
-        const int old = atomicAdd(&g.counters[f], 1);
-        const int last = old == g.splits - 1;
-        if (last) g.counters[f] = 0;  // nobody else touches it before the next launch
-        sm->finisher = last;
-    }
-    __syncthreads();
 
     CommCtx x{};
     if (p.fused) {
         x = comm_begin(c, block, blocks);
         stamp(c, x, 0);
     }
-    if (sm->finisher) {
-        __threadfence();
-        const float* base = g.ws + static_cast<size_t>(f) * g.splits * g.m * kBlockF;
-        const size_t split_stride = static_cast<size_t>(g.m) * kBlockF;
-        for (int v = threadIdx.x; v < g.m * (kBlockF / kVec); v += kFusedThreads) {
-            const int token = v / (kBlockF / kVec), j = v - token * (kBlockF / kVec);
+    if (g.splits > 1) {
+        // Split-K rendezvous: every CTA of the tile announces its partial, waits for the others, then sums ITS share of
+        // the tile's tokens over the splits in split order (so the value never depends on timing) and pushes it.
+        // Arrival counters alternate between two banks by launch generation; this launch clears the other bank.
+        const int gen = g.gen[block] + 1;
+        int* counter = g.counters + (gen & 1) * kMaxTiles + tile;
+        if (threadIdx.x == 0) {
+            if (s == 0) g.counters[((gen + 1) & 1) * kMaxTiles + tile] = 0;
+            atomicAdd(counter, 1);
+            int seen;
+            do {
+                asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+                if (seen >= g.splits) break;
+                if (globaltimer() > pipeline_deadline) {
+                    report(c.status, kErrTimeout, s, kPhasePipeline, 3);
+                    break;
+                }
+            } while (true);
+            for (int j = block; j < kEpochSlots; j += blocks) g.gen[j] = gen;
+        }
+        __syncthreads();
+        const int tok_lo = static_cast<int>(static_cast<long long>(s) * mt / g.splits);
+        const int tok_hi = static_cast<int>(static_cast<long long>(s + 1) * mt / g.splits);
+        const float* base = g.ws + static_cast<size_t>(tile) * g.splits * mt * kBlockF;
+        const size_t split_stride = static_cast<size_t>(mt) * kBlockF;
+        for (int v = threadIdx.x; v < (tok_hi - tok_lo) * (kBlockF / kVec); v += kFusedThreads) {
+            const int token = tok_lo + v / (kBlockF / kVec), j = v % (kBlockF / kVec);
             const float* src = base + static_cast<size_t>(token) * kBlockF + j * kVec;
-            float acc[kVec];
-            {
-                const float4 a = __ldcg(reinterpret_cast<const float4*>(src));
-                const float4 b = __ldcg(reinterpret_cast<const float4*>(src) + 1);
-                acc[0] = a.x, acc[1] = a.y, acc[2] = a.z, acc[3] = a.w;
-                acc[4] = b.x, acc[5] = b.y, acc[6] = b.z, acc[7] = b.w;
+            float4 a[kMaxSplits], b[kMaxSplits];
+#pragma unroll
+            for (int sp = 0; sp < kMaxSplits; ++sp) {
+                if (sp < g.splits) {
+                    a[sp] = __ldcg(reinterpret_cast<const float4*>(src + sp * split_stride));
+                    b[sp] = __ldcg(reinterpret_cast<const float4*>(src + sp * split_stride) + 1);
+                }
             }
-            for (int sp = 1; sp < g.splits; ++sp) {
-                const float4 a = __ldcg(reinterpret_cast<const float4*>(src + sp * split_stride));
-                const float4 b = __ldcg(reinterpret_cast<const float4*>(src + sp * split_stride) + 1);
-                acc[0] += a.x, acc[1] += a.y, acc[2] += a.z, acc[3] += a.w;
-                acc[4] += b.x, acc[5] += b.y, acc[6] += b.z, acc[7] += b.w;
+            float acc[kVec] = {a[0].x, a[0].y, a[0].z, a[0].w, b[0].x, b[0].y, b[0].z, b[0].w};
+#pragma unroll
+            for (int sp = 1; sp < kMaxSplits; ++sp) {
+                if (sp < g.splits) {
+                    acc[0] += a[sp].x, acc[1] += a[sp].y, acc[2] += a[sp].z, acc[3] += a[sp].w;
+                    acc[4] += b[sp].x, acc[5] += b[sp].y, acc[6] += b[sp].z, acc[7] += b[sp].w;
+                }
             }
             const uint4 packed = pack_bf16x8(acc);
             const int col = f * kBlockF + j * kVec;
             if (p.fused) {
-                store_v4(push_address(c, x, token, col), packed);
+                store_v4(push_address(c, x, token0 + token, col), packed);
             } else {
-                store_v4(g.out + static_cast<size_t>(token) * g.ldo + col, packed);
+                store_v4(g.out + static_cast<size_t>(token0 + token) * g.ldo + col, packed);
+            }
+        }
+    } else {
+        const uint4* staged = reinterpret_cast<const uint4*>(tiles);
+        for (int v = threadIdx.x; v < mt * (kBlockF / kVec); v += kFusedThreads) {
+            const int token = v / (kBlockF / kVec), j = v % (kBlockF / kVec);
+            const uint4 packed = staged[v];
+            const int col = f * kBlockF + j * kVec;
+            if (p.fused) {
+                store_v4(push_address(c, x, token0 + token, col), packed);
+            } else {
+                store_v4(g.out + static_cast<size_t>(token0 + token) * g.ldo + col, packed);
             }
         }
     }
     if (p.fused) {
-        stamp(c, x, 1);
+        if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 6] = globaltimer();
         rearm(c, x);
+        stamp(c, x, 1);
         pdl_launch_dependents();
         own_and_collect(c, x, sm->scratch);
         comm_end(c, x);
@@ -216,7 +265,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
     }
 }
 
-int rowpar_stages(int m) {
+int rowpar_stages(int m) {  // m: tokens per tile
     const int stage = kTileBytesW + m * kBlockK * 2;
     int stages = kSmemBudget / stage;
     if (stages > kMaxStages) stages = kMaxStages;
@@ -229,7 +278,7 @@ int rowpar_smem_bytes(int m, int stages) {
 
 template <int NR>
 static int launch_impl(const RowparParams<NR>& p, dim3 grid, const LaunchOpts& o) {
-    const int smem = rowpar_smem_bytes(p.g[0].m, p.g[0].stages);
+    const int smem = rowpar_smem_bytes(p.g[0].m / p.g[0].token_tiles, p.g[0].stages);
     // Raised once per device to the largest configuration (not a stream operation, but kept out of graph captures).
     static bool raised[64] = {};
     cudaError_t err = cudaSuccess;

@@ -89,7 +89,7 @@ class LoopbackWorld:
         self._done(chain, outs)
         return outs
 
-    def rowpar(self, xs, ws, *, site, chain=0, hs=None, weight=None, eps=0.0, scale=1.0, splits=0):
+    def rowpar(self, xs, ws, *, site, chain=0, hs=None, weight=None, eps=0.0, scale=1.0, splits=0, token_tiles=0):
         """All ranks of the fused projection + reduction in one launch: xs[r] [m, k_r], ws[r] [n, k_r]."""
         m, n = xs[0].shape[0], ws[0].shape[0]
         comms, outs = self._comms(m, n, site, chain, hs, weight, eps, scale)
@@ -102,6 +102,7 @@ class LoopbackWorld:
             gm.x, gm.w, gm.m, gm.n, gm.k = x.data_ptr(), w.data_ptr(), m, n, x.shape[1]
             gm.ldx, gm.ldw = x.stride(0), w.stride(0)
             gm.workspace, gm.workspace_bytes, gm.splits = scratch.data_ptr(), scratch.numel(), splits
+            gm.token_tiles = token_tiles
             gemms[r] = gm
         stream = torch.cuda.current_stream(self.device).cuda_stream
         _lib.check(_lib.lib().dlm_rowpar_bf16_loopback(gemms, comms, self.world, stream), f"loopback rowpar {site}")

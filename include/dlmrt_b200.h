@@ -40,6 +40,7 @@ extern "C" {
 
 #define DLM_MAX_WORLD 8      /* tp_comm.cu:52 kMaxWorld */
 #define DLM_EPOCH_SLOTS 256  /* int32 invocation counters per receive buffer; every kernel keeps all of them equal */
+#define DLM_STAMP_SLOTS 8
 #define DLM_STATUS_WORDS 4   /* int32: [0] first error code, [1] block << 8 | slot, [2] phase, [3] epoch */
 #define DLM_MAX_N 8192       /* tp_comm.cu:282: hidden size a multiple of 256, at most 8192 */
 #define DLM_FUSED_MAX_N 3072 /* the fused GEMM+reduce kernels run 384 threads: hidden / 8 <= 384 */
@@ -84,7 +85,10 @@ typedef struct DlmComm {
     void* h;                       /* [rows, n] BF16 residual stream (mode 2): own rows read and rewritten */
     const void* weight;            /* [n] BF16 RMSNorm weight (modes 1, 2) */
     int32_t* status;               /* [DLM_STATUS_WORDS] int32 device words, zero-initialised, or NULL */
-    int64_t* stamps;               /* [grid, 4] int64 %globaltimer phase stamps per CTA, or NULL (tp_comm.cu:121) */
+    int64_t* stamps;               /* [grid, DLM_STAMP_SLOTS] int64 %globaltimer phase stamps per CTA, or NULL
+                                      (tp_comm.cu:121): 0 start, 1 pushed, 2 owned rows broadcast, 3 collected; fused
+                                      kernels also 4 accumulator ready, 5 partial tile written, 6 tile summed+pushed,
+                                      7 kernel entry */
     int64_t timeout_ns;            /* budget of every device wait; 0 = 2 s */
     int32_t pdl;                   /* launch as a programmatic dependent launch (tp_comm.cu:304-309) */
     int32_t max_ctas;              /* cap on the grid, 0 = one CTA per SM. Calls that may run concurrently (different
@@ -97,10 +101,12 @@ typedef struct DlmGemm {
     const void* w;   /* [n, k] BF16, leading dimension ldw elements */
     int32_t m, n, k; /* m % 16 == 0, 16 <= m <= 256; n % 128 == 0; k % 64 == 0 */
     int64_t ldx, ldw;/* multiples of 8 */
-    void* workspace; /* dlm_workspace_bytes(m, n, k) bytes, zero-initialised once, 256-byte aligned; one per chain */
+    void* workspace; /* dlm_workspace_bytes(m, n, k) bytes, zero-initialised once, 256-byte aligned; one per chain
+                        (split-K partial tiles, arrival counters and a launch generation live in it) */
     int64_t workspace_bytes;
     int32_t splits;  /* K splits across CTAs, 0 = chosen by the library; FP32 partial tiles are summed in split
                         order, so the result does not depend on scheduling */
+    int32_t token_tiles; /* tiles along m (each m / token_tiles tokens, a multiple of 16), 0 = chosen by the library */
 } DlmGemm;
 
 /* Device status read back by dlm_status_read(). */
@@ -142,8 +148,8 @@ DLM_API int dlm_rowpar_bf16_loopback(const DlmGemm* gemm, const DlmComm* comm, i
 /* Bytes of workspace (FP32 split-K partial tiles + tile counters) a GEMM of this shape needs. */
 DLM_API size_t dlm_workspace_bytes(int m, int n, int k);
 
-/* Number of K splits the library would pick for this shape with `max_ctas` CTAs available (0 = all SMs). */
-DLM_API int dlm_choose_splits(int m, int n, int k, int max_ctas);
+/* The (token tiles, K splits) the library would pick for this shape with `max_ctas` CTAs available (0 = all SMs). */
+DLM_API int dlm_choose_tiling(int m, int n, int k, int max_ctas, int* token_tiles, int* splits);
 
 /* Copies the device status words to the host (synchronises `stream`) and clears them on the device. */
 DLM_API int dlm_status_read(int32_t* device_status, DlmStatus* out, dlm_stream_t stream);

@@ -48,7 +48,7 @@ def test_strerror_and_sizes():
     for code in range(0, -10, -1):
         assert lib.dlm_strerror(code)
     assert lib.dlm_strerror(-99) == b"unknown error"
-    assert lib.dlm_workspace_bytes(256, 2560, 9728) == 256 + 8 * 256 * 2560 * 4
+    assert lib.dlm_workspace_bytes(256, 2560, 9728) == 2048 + 8 * 256 * 2560 * 4
     assert lib.dlm_workspace_bytes(0, 2560, 64) == 0
 
 
@@ -93,7 +93,7 @@ def gemm(**kw):
     (dict(m=8), _lib.ERR_SHAPE), (dict(m=272), _lib.ERR_SHAPE), (dict(m=40), _lib.ERR_SHAPE), (dict(n=192), _lib.ERR_SHAPE),
     (dict(k=96), _lib.ERR_SHAPE), (dict(ldx=64), _lib.ERR_ALIGN), (dict(ldw=132), _lib.ERR_ALIGN),
     (dict(x=0x1004), _lib.ERR_ALIGN), (dict(workspace=0x10010), _lib.ERR_ALIGN), (dict(w=None), _lib.ERR_NULL),
-    (dict(splits=9), _lib.ERR_SHAPE),
+    (dict(splits=9), _lib.ERR_SHAPE), (dict(token_tiles=3), _lib.ERR_SHAPE), (dict(m=48, token_tiles=2), _lib.ERR_SHAPE),
 ])
 def test_gemm_rejects_bad_arguments(kw, code):
     assert _lib.lib().dlm_gemm_bf16(C.byref(gemm(**kw)), 0x9000, 256, 0, None) == code
@@ -110,3 +110,16 @@ def test_missing_library_is_an_import_error(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "libdlmrt_b200.so")
     with pytest.raises(ImportError, match="no CPU or PyTorch fallback"):
         _lib.lib()
+
+
+def test_tiling_choice_follows_the_shape():
+    """Long K (TP = 1) is split along K over all SMs; short K (TP = 8) is tiled along the tokens with no split."""
+    lib = _lib.lib()
+    t, sp = C.c_int(), C.c_int()
+    assert lib.dlm_choose_tiling(256, 2560, 9728, 148, C.byref(t), C.byref(sp)) == _lib.OK
+    assert (t.value, sp.value) == (1, 7)
+    assert lib.dlm_choose_tiling(256, 2560, 1216, 148, C.byref(t), C.byref(sp)) == _lib.OK
+    assert sp.value == 1 and t.value >= 2
+    assert lib.dlm_choose_tiling(256, 2560, 9728, 20, C.byref(t), C.byref(sp)) == _lib.OK
+    assert (t.value, sp.value) == (1, 1)
+    assert lib.dlm_choose_tiling(250, 2560, 9728, 148, C.byref(t), C.byref(sp)) == _lib.ERR_SHAPE
