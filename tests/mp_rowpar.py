@@ -1,0 +1,88 @@
+"""One rank of the real multi-GPU parity run (launched by tests/test_multigpu.py through torch.distributed.run):
+stand-alone reductions and fused projections over symmetric memory, checked bit for bit against the CPU oracle fed
+with the all-gathered inputs, and for identity across ranks."""
+
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "tests"))
+
+from gpu_util import assert_norm_close, assert_same_bits, bits, randn_bf16  # noqa: E402
+from oracle import reduce as red  # noqa: E402
+
+
+def gather(t):
+    out = [torch.empty_like(t) for _ in range(dist.get_world_size())]
+    dist.all_gather(out, t.contiguous())
+    return out
+
+
+def main():
+    from dlmrt_b200.distributed import parallel
+    from dlmrt_b200.layers.linear import Linear
+
+    parallel.TIMEOUT_NS = 2_000_000_000
+    group = parallel.init()
+    rank, world, dev = group.rank, group.world, group.device
+    report = {"multicast": bool(group.multicast(group.symmetric("probe", (8, 256), armed=True)))}
+    rows, n = 256, 2560
+    weight = randn_bf16(n, seed=5, std=0.1, device=dev) + 1
+    h = randn_bf16(rows, n, seed=6, device=dev)  # same start on every rank; each rank updates its own rows
+    for i in range(9):
+        mode = i % 3
+        p = randn_bf16(rows, n, seed=100 * i + rank, device=dev)
+        all_p = np.stack([bits(t) for t in gather(p)])
+        h_all = np.stack([bits(t) for t in gather(h)])
+        site = f"s{i % 2}.{mode}"
+        if mode == 0:
+            out = group.reduce(p, site=site)
+            want = red.reduce(all_p)
+        elif mode == 1:
+            out = group.reduce_norm(p, None, weight, 1e-6, 0.75, site=site)
+            want, _ = red.reduce_norm(all_p, bits(weight), 1e-6, 0.75)
+        else:
+            out = group.reduce_norm(p, h, weight, 1e-6, site=site)
+            want, h_after = red.reduce_norm(all_p, bits(weight), 1e-6, 1.0, h_all)
+        torch.cuda.synchronize()
+        group.check()
+        got = bits(out)
+        for r, other in enumerate(gather(out)):
+            assert_same_bits(bits(other), got, f"reduce {i}: rank {r} vs rank {rank}")
+        (assert_same_bits if mode == 0 else assert_norm_close)(got, want, f"reduce {i} mode {mode}")
+        if mode == 2:
+            assert_same_bits(bits(h), h_after[rank], f"reduce {i}: residual")
+    # fused projection + reduction, integer operands: exact end to end
+    for i, (m, k_total) in enumerate([(256, 4096), (256, 9728 // 8 * 8), (32, 2048)]):
+        g = torch.Generator().manual_seed(7 + i)
+        x = torch.randint(-3, 4, (m, k_total), generator=g).to(torch.bfloat16)
+        w = torch.randint(-2, 3, (n, k_total), generator=g).to(torch.bfloat16)
+        if k_total % (64 * world):
+            continue
+        xs, ws = group.shard(x, 1).to(dev), group.shard(w, 1).to(dev)
+        lin = Linear(ws, group=group)
+        for rep in range(3):
+            p = lin(xs, out=group.symmetric(f"partial{m}", (m, n)))
+            out = group.reduce(p, site=f"f{i}.{rep % 2}", chain=m)
+            torch.cuda.synchronize()
+            group.check()
+            want = (x.float() @ w.float().t())
+            parts = [x.chunk(world, 1)[r].float() @ w.chunk(world, 1)[r].float().t() for r in range(world)]
+            want = red.reduce(np.stack([bits(t.to(torch.bfloat16)) for t in parts]))
+            assert_same_bits(bits(out), want, f"fused {i}.{rep}")
+            for r, other in enumerate(gather(out)):
+                assert_same_bits(bits(other), bits(out), f"fused {i}.{rep}: rank {r} vs rank {rank}")
+    dist.barrier()
+    if rank == 0:
+        print(f"MULTIGPU_OK world={world} multicast={report['multicast']}")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
