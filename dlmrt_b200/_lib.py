@@ -8,9 +8,10 @@ MAX_WORLD = 8
 EPOCH_SLOTS = 256
 STATUS_WORDS = 4
 FUSED_MAX_N = 3072
+NOALLOC_SCRATCH_BYTES = 8 << 20
 
-OK, ERR_SHAPE, ERR_ALIGN, ERR_WORLD, ERR_NULL, ERR_GRID, ERR_CUDA, ERR_WORKSPACE, ERR_TIMEOUT, ERR_ARCH = \
-    0, -1, -2, -3, -4, -5, -6, -7, -8, -9
+OK, ERR_SHAPE, ERR_ALIGN, ERR_WORLD, ERR_NULL, ERR_GRID, ERR_CUDA, ERR_WORKSPACE, ERR_TIMEOUT, ERR_ARCH, \
+    ERR_SCRATCH = 0, -1, -2, -3, -4, -5, -6, -7, -8, -9, -10
 REDUCE, REDUCE_NORM, REDUCE_NORM_RESIDUAL = 0, 1, 2
 
 LIB_PATH = Path(__file__).resolve().parent / "libdlmrt_b200.so"
@@ -51,6 +52,8 @@ SIGNATURES = {
     "dlm_reduce_bf16": (C.c_int, [C.c_void_p, C.POINTER(DlmComm), C.c_void_p]),
     "dlm_reduce_bf16_loopback": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(DlmComm), C.c_int, C.c_void_p]),
     "dlm_gemm_bf16": (C.c_int, [C.POINTER(DlmGemm), C.c_void_p, C.c_int64, C.c_int, C.c_void_p]),
+    "dlm_gemm_bf16_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int64,
+                                        C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "dlm_rowpar_bf16": (C.c_int, [C.POINTER(DlmGemm), C.POINTER(DlmComm), C.c_void_p]),
     "dlm_rowpar_bf16_loopback": (C.c_int, [C.POINTER(DlmGemm), C.POINTER(DlmComm), C.c_int, C.c_void_p]),
     "dlm_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),

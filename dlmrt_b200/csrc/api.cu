@@ -274,6 +274,78 @@ int dlm_gemm_bf16(const DlmGemm* gemm, void* out, int64_t ldo, int pdl, dlm_stre
     return launch_rowpar(p, grid, {static_cast<cudaStream_t>(stream), pdl != 0, false});
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// The entry point that allocates nothing.
+//
+// Its split-K scratch is this file-scope device array: DLM_NOALLOC_SCRATCH_BYTES of global memory that every GPU which
+// loads the library holds until the process exits. In host code `g_noalloc_scratch` is only a stand-in for the symbol,
+// not a device address; the address a kernel may use comes from cudaGetSymbolAddress, asked once per device with that
+// device current (first call of the entry point on that device).
+// ---------------------------------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_noalloc_scratch[DLM_NOALLOC_SCRATCH_BYTES];
+
+static int noalloc_scratch(void** ptr) {
+    static void* cached[64] = {};
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return cuda_fail(err);
+    if (dev < 0 || dev >= 64) return DLM_ERR_ARCH;
+    if (cached[dev] == nullptr) {
+        void* p = nullptr;
+        err = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (err != cudaSuccess) return cuda_fail(err);
+        cached[dev] = p;
+    }
+    *ptr = cached[dev];
+    return DLM_OK;
+}
+
+int dlm_gemm_bf16_noalloc(const void* x, const void* w, void* out, int m, int n, int k, int64_t ldx, int64_t ldw,
+                          int64_t ldo, int splits, int token_tiles, int pdl, dlm_stream_t stream) {
+    DlmGemm g;
+    std::memset(&g, 0, sizeof(g));
+    g.x = x, g.w = w, g.m = m, g.n = n, g.k = k, g.ldx = ldx, g.ldw = ldw;
+    g.splits = splits, g.token_tiles = token_tiles;
+    g.workspace = reinterpret_cast<void*>(uintptr_t(256));  // placeholder for the argument checks only
+    g.workspace_bytes = DLM_NOALLOC_SCRATCH_BYTES;
+    int rc = check_gemm(&g);
+    if (rc != DLM_OK) return rc;
+    if (out == nullptr) return DLM_ERR_NULL;
+    if (!aligned16(out) || ldo < n || ldo % 8) return DLM_ERR_ALIGN;
+    const size_t per_split = static_cast<size_t>(m) * n * sizeof(float);
+    // An explicit request that does not fit is refused; splits the library picks are capped to what fits
+    // (one split needs no partial tiles at all).
+    if (splits > 1 && kWorkspaceHeader + splits * per_split > DLM_NOALLOC_SCRATCH_BYTES) return DLM_ERR_SCRATCH;
+    DeviceInfo info;
+    rc = device_info(&info);
+    if (rc != DLM_OK) return rc;
+    void* scratch = nullptr;
+    rc = noalloc_scratch(&scratch);
+    if (rc != DLM_OK) return rc;
+    g.workspace = scratch;
+    if (g.splits == 0 || g.token_tiles == 0) {
+        int t = 1, sp = 1;
+        choose_tiling(m, n, k, info.sms, &t, &sp);
+        if (g.token_tiles == 0) g.token_tiles = g.splits == 0 ? t : 1;
+        if (g.splits == 0) g.splits = token_tiles == 0 ? sp : 1;
+        while (g.splits > 1 && kWorkspaceHeader + g.splits * per_split > DLM_NOALLOC_SCRATCH_BYTES) --g.splits;
+    }
+    RowparParams<1> p;
+    std::memset(&p, 0, sizeof(p));
+    int grid = 0;
+    rc = fill_gemm(&p.g[0], &g, 0, info.sms, &grid);
+    if (rc != DLM_OK) return rc;
+    p.g[0].out = static_cast<__nv_bfloat16*>(out);
+    p.g[0].ldo = ldo;
+    p.fused = 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // The array keeps whatever the last call left. The only part that must start at zero is the header (launch
+    // generation and arrival counters); the partial tiles are fully rewritten before they are read.
+    const cudaError_t err = cudaMemsetAsync(scratch, 0, kWorkspaceHeader, s);
+    if (err != cudaSuccess) return cuda_fail(err);
+    return launch_rowpar(p, grid, {s, pdl != 0, false});
+}
+
 static int check_pair(const DlmGemm* gemm, const DlmComm* comm) {
     int rc = check_gemm(gemm);
     if (rc == DLM_OK) rc = check_comm(comm);
@@ -377,6 +449,7 @@ const char* dlm_strerror(int code) {
         case DLM_ERR_WORKSPACE: return "workspace too small (dlm_workspace_bytes)";
         case DLM_ERR_TIMEOUT: return "device wait ran out: data from a rank never arrived";
         case DLM_ERR_ARCH: return "not an sm_100 device";
+        case DLM_ERR_SCRATCH: return "requested K splits need more than the library's built-in scratch (DLM_NOALLOC_SCRATCH_BYTES)";
         default: return "unknown error";
     }
 }

@@ -44,6 +44,7 @@ extern "C" {
 #define DLM_STATUS_WORDS 4   /* int32: [0] first error code, [1] block << 8 | slot, [2] phase, [3] epoch */
 #define DLM_MAX_N 8192       /* tp_comm.cu:282: hidden size a multiple of 256, at most 8192 */
 #define DLM_FUSED_MAX_N 3072 /* the fused GEMM+reduce kernels run 384 threads: hidden / 8 <= 384 */
+#define DLM_NOALLOC_SCRATCH_BYTES (8u << 20) /* built-in scratch of dlm_gemm_bf16_noalloc, held by every GPU in use */
 #define DLM_MAX_M 256        /* rows of one block forward (32, 64 or 256 in the reference's rounds) */
 
 enum {
@@ -56,7 +57,8 @@ enum {
     DLM_ERR_CUDA = -6,      /* a CUDA call failed: see dlm_last_cuda_error() */
     DLM_ERR_WORKSPACE = -7, /* workspace smaller than dlm_workspace_bytes() */
     DLM_ERR_TIMEOUT = -8,   /* device status: a bounded wait ran out (data from a rank never arrived) */
-    DLM_ERR_ARCH = -9       /* not an sm_100 device */
+    DLM_ERR_ARCH = -9,      /* not an sm_100 device */
+    DLM_ERR_SCRATCH = -10   /* dlm_gemm_bf16_noalloc: the requested K splits do not fit the built-in scratch */
 };
 
 /* What follows the rank-ordered sum (tp_comm.cu:138 template <NORM, RESIDUAL>). */
@@ -134,6 +136,28 @@ DLM_API int dlm_reduce_bf16_loopback(const void* const* partial, const DlmComm* 
 /* Plain row-parallel-shaped GEMM without communication: out[m, n] BF16 (ldo elements) = x * W^T.
  * Replaces Linear.__call__ on one GPU (linear.py:47-48, torch.mm on cuBLAS). */
 DLM_API int dlm_gemm_bf16(const DlmGemm* gemm, void* out, int64_t ldo, int pdl, dlm_stream_t stream);
+
+/* dlm_gemm_bf16 for callers that cannot allocate device memory. No counterpart in the reference.
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits -- inside a CUDA-graph capture of someone else's
+ * stream, in a plugin whose host forbids allocations after start-up, or in a process whose memory pool is owned by
+ * another runtime -- cannot provide the workspace dlm_gemm_bf16 asks for. Here the split-K scratch (FP32 partial
+ * tiles, arrival counters) is a fixed array of DLM_NOALLOC_SCRATCH_BYTES (8 MiB) inside the library, which every GPU
+ * that uses the library keeps until the process ends. The caller passes only inputs and the output; the call issues
+ * no cudaMalloc / cudaFree and no allocating library routine.
+ *
+ * Limits and rules:
+ *   - m, n, k, ld* as for dlm_gemm_bf16. `splits` > 1 needs 2 KiB + splits * m * n * 4 bytes of scratch; an explicit
+ *     request beyond 8 MiB returns DLM_ERR_SCRATCH. With splits = 0 the library picks a tiling and lowers the number
+ *     of splits until it fits (a single split needs no partial tiles), so every legal shape runs, if slower;
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress with that device
+ *     current); make that first call before any stream capture starts;
+ *   - all calls on a GPU share the one array. Each call clears the small header it depends on (stream-ordered
+ *     memset) and rewrites the partial tiles before reading them, so calls that follow each other on one stream are
+ *     safe; calls that overlap on the GPU (different streams, different host threads) race on it and give wrong
+ *     results. */
+DLM_API int dlm_gemm_bf16_noalloc(const void* x, const void* w, void* out, int m, int n, int k, int64_t ldx,
+                                  int64_t ldw, int64_t ldo, int splits, int token_tiles, int pdl, dlm_stream_t stream);
 
 /* Fused row-parallel projection + reduction: the GEMM above whose finished BF16 tiles are pushed straight into the
  * owner ranks' receive slots, followed in the same kernel by the reduction of dlm_reduce_bf16.
