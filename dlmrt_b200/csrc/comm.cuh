@@ -58,11 +58,12 @@ __device__ __forceinline__ void stamp(const CommDev& c, const CommCtx& x, int ph
     if (c.stamps && threadIdx.x == 0) c.stamps[x.block * kStampSlots + phase] = globaltimer();
 }
 
-__device__ __forceinline__ CommCtx comm_begin(const CommDev& c, int block, int blocks) {
+// `previous` is epochs[block] as read after the previous kernel completed (callers may have fetched it early).
+__device__ __forceinline__ CommCtx comm_begin(const CommDev& c, int block, int blocks, int previous) {
     CommCtx x;
     x.block = block;
     x.blocks = blocks;
-    x.e = c.epochs[block] + 1;
+    x.e = previous + 1;
     x.buf = x.e % 3;
     x.deadline = globaltimer() + c.timeout_ns;
     x.slot_elems = static_cast<size_t>(c.R) * c.n;
@@ -94,10 +95,11 @@ __device__ __forceinline__ void push_partial(const CommDev& c, const CommCtx& x,
 
 // Re-arm the receive buffer peers write in invocation e + 2 and the previous call site's output (over that output's
 // own size: calls on one chain may differ in rows, tp_comm.cu:201-208).
-__device__ __forceinline__ void rearm(const CommDev& c, const CommCtx& x) {
+// The work is spread over `parts` CTAs of which this one is number `part`.
+__device__ __forceinline__ void rearm(const CommDev& c, const CommCtx& x, int part, int parts) {
     const uint4 sentinel = make_uint4(kSentinel, kSentinel, kSentinel, kSentinel);
-    const int stride = x.blocks * blockDim.x;
-    const int first = x.block * blockDim.x + threadIdx.x;
+    const int stride = parts * blockDim.x;
+    const int first = part * blockDim.x + threadIdx.x;
     __nv_bfloat16* stale = c.recv[c.rank] + ((x.e + 2) % 3) * x.buf_elems;
     const int total = static_cast<int>(x.buf_elems / kVec);
     for (int i = first; i < total; i += stride) store_v4(stale + static_cast<size_t>(i) * kVec, sentinel);
@@ -214,6 +216,16 @@ __device__ __forceinline__ void own_and_collect(const CommDev& c, const CommCtx&
     if (c.mode == kReduce) own_and_collect<kReduce>(c, x, scratch);
     else if (c.mode == kReduceNorm) own_and_collect<kReduceNorm>(c, x, scratch);
     else own_and_collect<kReduceNormResidual>(c, x, scratch);
+}
+
+// Nothing waits for the re-arm inside this launch, but the owners' sums are on the critical path of every rank. So
+// CTAs that own no row (block >= R) re-arm at once, on behalf of everyone; only when every CTA owns rows does each
+// re-arm its share, and then after its own and collect phases.
+__device__ __forceinline__ void rearm_early(const CommDev& c, const CommCtx& x) {
+    if (x.blocks > c.R && x.block >= c.R) rearm(c, x, x.block - c.R, x.blocks - c.R);
+}
+__device__ __forceinline__ void rearm_late(const CommDev& c, const CommCtx& x) {
+    if (x.blocks <= c.R) rearm(c, x, x.block, x.blocks);
 }
 
 // Advance the invocation counters: every entry of the table ends equal to e, whatever the grid size.

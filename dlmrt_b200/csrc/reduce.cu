@@ -17,12 +17,13 @@ __global__ void __launch_bounds__(1024, 1) reduce_kernel(const __grid_constant__
     const CommDev& c = p.c[slot];
     __shared__ float scratch[32];
     pdl_wait();
-    const CommCtx x = comm_begin(c, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
+    const CommCtx x = comm_begin(c, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), c.epochs[blockIdx.x]);
     stamp(c, x, 0);
     push_partial(c, x, p.partial[slot]);
     stamp(c, x, 1);
-    rearm(c, x);
+    rearm_early(c, x);
     own_and_collect(c, x, scratch);
+    rearm_late(c, x);
     comm_end(c, x);
     pdl_launch_dependents();
 }

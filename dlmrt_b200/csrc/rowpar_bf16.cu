@@ -31,6 +31,7 @@ struct SmemLayout {
     uint64_t empty[kMaxStages];
     uint64_t acc_full;
     uint32_t tmem_base;
+    int epoch, gen;  // epochs[block] and gen[block], fetched by a spare warp while the pipeline runs
     float scratch[32];
 };
 
@@ -136,6 +137,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
             }
             umma_commit(&sm->acc_full);
         }
+    } else if (warp == 3) {
+        if (lane == 0) {
+            pdl_wait();
+            if (p.fused) sm->epoch = c.epochs[block];
+            if (g.splits > 1) sm->gen = g.gen[block];
+        }
     } else if (warp >= 4) {
         // Epilogue: thread `lane` of a warp holds feature 32 * quarter + lane; 16 token columns per tcgen05.ld.
         const int quarter = warp & 3, half = (warp - 4) >> 2;
@@ -185,14 +192,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
 
     CommCtx x{};
     if (p.fused) {
-        x = comm_begin(c, block, blocks);
+        x = comm_begin(c, block, blocks, sm->epoch);
         stamp(c, x, 0);
     }
     if (g.splits > 1) {
         // Split-K rendezvous: every CTA of the tile announces its partial, waits for the others, then sums ITS share of
         // the tile's tokens over the splits in split order (so the value never depends on timing) and pushes it.
         // Arrival counters alternate between two banks by launch generation; this launch clears the other bank.
-        const int gen = g.gen[block] + 1;
+        const int gen = sm->gen + 1;
         int* counter = g.counters + (gen & 1) * kMaxTiles + tile;
         if (threadIdx.x == 0) {
             if (s == 0) g.counters[((gen + 1) & 1) * kMaxTiles + tile] = 0;
@@ -255,10 +262,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
     }
     if (p.fused) {
         if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 6] = globaltimer();
-        rearm(c, x);
         stamp(c, x, 1);
         pdl_launch_dependents();
+        rearm_early(c, x);
         own_and_collect(c, x, sm->scratch);
+        rearm_late(c, x);
         comm_end(c, x);
     } else {
         pdl_launch_dependents();
