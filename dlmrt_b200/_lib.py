@@ -32,6 +32,14 @@ class DlmGemm(C.Structure):
                 ("splits", C.c_int32), ("token_tiles", C.c_int32)]
 
 
+class DlmMoe(C.Structure):
+    _fields_ = [("act_codes", C.c_void_p), ("act_scales", C.c_void_p), ("amap", C.c_void_p), ("counts", C.c_void_p),
+                ("w_codes", C.c_void_p), ("w_scales", C.c_void_p), ("g2", C.c_void_p), ("ids", C.c_void_p),
+                ("weights", C.c_void_p), ("shared", C.c_void_p), ("m", C.c_int32), ("n", C.c_int32), ("f", C.c_int32),
+                ("top_k", C.c_int32), ("m_max", C.c_int32), ("lo", C.c_int32), ("e_local", C.c_int32),
+                ("e_total", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64)]
+
+
 class DlmStatus(C.Structure):
     _fields_ = [("code", C.c_int32), ("block", C.c_int32), ("slot", C.c_int32), ("phase", C.c_int32),
                 ("epoch", C.c_int32)]
@@ -56,6 +64,11 @@ SIGNATURES = {
                                         C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "dlm_rowpar_bf16": (C.c_int, [C.POINTER(DlmGemm), C.POINTER(DlmComm), C.c_void_p]),
     "dlm_rowpar_bf16_loopback": (C.c_int, [C.POINTER(DlmGemm), C.POINTER(DlmComm), C.c_int, C.c_void_p]),
+    "dlm_moe_nvfp4": (C.c_int, [C.POINTER(DlmMoe), C.c_void_p, C.c_int64, C.c_int, C.c_void_p]),
+    "dlm_rowpar_nvfp4_moe": (C.c_int, [C.POINTER(DlmMoe), C.POINTER(DlmComm), C.c_void_p]),
+    "dlm_rowpar_nvfp4_moe_loopback": (C.c_int, [C.POINTER(DlmMoe), C.POINTER(DlmComm), C.c_int, C.c_void_p]),
+    "dlm_moe_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
+    "dlm_abi_check_moe": (C.c_int, [C.c_size_t]),
     "dlm_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "dlm_choose_tiling": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "dlm_status_read": (C.c_int, [C.c_void_p, C.POINTER(DlmStatus), C.c_void_p]),
@@ -79,7 +92,8 @@ def lib():
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(handle, name)
             fn.restype, fn.argtypes = res, args
-        if handle.dlm_abi_check(C.sizeof(DlmComm), C.sizeof(DlmGemm), C.sizeof(DlmStatus)) != OK:
+        if handle.dlm_abi_check(C.sizeof(DlmComm), C.sizeof(DlmGemm), C.sizeof(DlmStatus)) != OK or \
+                handle.dlm_abi_check_moe(C.sizeof(DlmMoe)) != OK:
             raise ImportError(f"{LIB_PATH}: struct layout differs from this binding; rebuild the library")
         _lib = handle
     return _lib

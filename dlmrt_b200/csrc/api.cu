@@ -370,6 +370,128 @@ int dlm_rowpar_bf16(const DlmGemm* gemm, const DlmComm* comm, dlm_stream_t strea
     return launch_rowpar(p, grid, {static_cast<cudaStream_t>(stream), comm->pdl != 0, false});
 }
 
+static int check_moe(const DlmMoe* m) {
+    if (m == nullptr) return DLM_ERR_NULL;
+    if (!m->act_codes || !m->act_scales || !m->amap || !m->counts || !m->w_codes || !m->w_scales || !m->g2 || !m->ids ||
+        !m->weights || !m->workspace)
+        return DLM_ERR_NULL;
+    if (m->m < 1 || m->m > DLM_MAX_M || m->n < kBlockF || m->n % 256 || m->n > DLM_FUSED_MAX_N) return DLM_ERR_SHAPE;
+    if (m->f < 64 || m->f % 64 || m->f > 4096 || m->top_k < 1 || m->top_k > 16) return DLM_ERR_SHAPE;
+    if (m->m_max < 1 || m->m_max > 256 || m->e_local < 1 || m->e_local > 256) return DLM_ERR_SHAPE;
+    if (m->lo < 0 || m->lo + m->e_local > m->e_total) return DLM_ERR_SHAPE;
+    if (!aligned16(m->act_codes) || !aligned16(m->w_codes) || !aligned16(m->w_scales) || !aligned16(m->shared) ||
+        (reinterpret_cast<uintptr_t>(m->act_scales) & 3) || (reinterpret_cast<uintptr_t>(m->workspace) & 255))
+        return DLM_ERR_ALIGN;
+    if (static_cast<size_t>(m->workspace_bytes) < dlm_moe_workspace_bytes(m->m, m->n, m->top_k)) return DLM_ERR_WORKSPACE;
+    return DLM_OK;
+}
+
+static int make_map_u8(CUtensorMap* map, const void* base, long long rows, int row_bytes, int box_rows) {
+    EncodeTiled fn = encode_tiled();
+    if (fn == nullptr) return DLM_ERR_CUDA;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_bytes)};
+    const cuuint32_t box[2] = {128, static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        g_last_cuda_error = 100000 + static_cast<int>(r);
+        return DLM_ERR_CUDA;
+    }
+    return DLM_OK;
+}
+
+static int fill_moe(MoeDev* d, const DlmMoe* m) {
+    std::memset(d, 0, sizeof(*d));
+    int rc = make_map_u8(&d->tm_w, m->w_codes, static_cast<long long>(m->e_local) * m->n, m->f / 2, kBlockF);
+    if (rc == DLM_OK) rc = make_map_u8(&d->tm_a, m->act_codes, static_cast<long long>(m->e_local) * m->m_max, m->f / 2, 32);
+    if (rc != DLM_OK) return rc;
+    d->a_scales = static_cast<const uint8_t*>(m->act_scales);
+    d->w_scales = static_cast<const uint8_t*>(m->w_scales);
+    d->amap = m->amap, d->counts = m->counts, d->g2 = m->g2, d->ids = m->ids, d->weights = m->weights;
+    d->shared = static_cast<const __nv_bfloat16*>(m->shared);
+    d->gen = static_cast<int*>(m->workspace);
+    d->counters = d->gen + kEpochSlots;
+    d->y = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(m->workspace) + kWorkspaceHeader);
+    d->m = m->m, d->n = m->n, d->f = m->f, d->top_k = m->top_k, d->m_max = m->m_max;
+    d->lo = m->lo, d->e_local = m->e_local, d->e_total = m->e_total;
+    d->rows_cap = (m->m_max + 31) / 32 * 32;
+    d->stages = moe_stages(d->rows_cap);
+    return DLM_OK;
+}
+
+size_t dlm_moe_workspace_bytes(int m, int n, int top_k) {
+    if (m <= 0 || n <= 0 || top_k <= 0) return 0;
+    return kWorkspaceHeader + static_cast<size_t>(m) * top_k * n * 2;
+}
+
+int dlm_moe_nvfp4(const DlmMoe* moe, void* out, int64_t ldo, int pdl, dlm_stream_t stream) {
+    int rc = check_moe(moe);
+    if (rc != DLM_OK) return rc;
+    if (out == nullptr) return DLM_ERR_NULL;
+    if (!aligned16(out) || ldo < moe->n || ldo % 8) return DLM_ERR_ALIGN;
+    DeviceInfo info;
+    rc = device_info(&info);
+    if (rc != DLM_OK) return rc;
+    MoeParams<1> p;
+    std::memset(&p, 0, sizeof(p));
+    rc = fill_moe(&p.g[0], moe);
+    if (rc != DLM_OK) return rc;
+    p.g[0].out = static_cast<__nv_bfloat16*>(out);
+    p.g[0].ldo = ldo;
+    p.fused = 0;
+    return launch_moe(p, info.sms, {static_cast<cudaStream_t>(stream), pdl != 0, false});
+}
+
+int dlm_rowpar_nvfp4_moe(const DlmMoe* moe, const DlmComm* comm, dlm_stream_t stream) {
+    int rc = check_moe(moe);
+    if (rc == DLM_OK) rc = check_comm(comm);
+    if (rc != DLM_OK) return rc;
+    if (moe->m != comm->rows || moe->n != comm->n) return DLM_ERR_SHAPE;
+    DeviceInfo info;
+    rc = device_info(&info);
+    if (rc != DLM_OK) return rc;
+    MoeParams<1> p;
+    std::memset(&p, 0, sizeof(p));
+    rc = fill_moe(&p.g[0], moe);
+    if (rc != DLM_OK) return rc;
+    fill_comm(&p.c[0], comm);
+    p.fused = 1;
+    const int grid = comm->max_ctas > 0 && comm->max_ctas < info.sms ? comm->max_ctas : info.sms;
+    return launch_moe(p, grid, {static_cast<cudaStream_t>(stream), comm->pdl != 0, false});
+}
+
+int dlm_rowpar_nvfp4_moe_loopback(const DlmMoe* moe, const DlmComm* comm, int nranks, dlm_stream_t stream) {
+    if (moe == nullptr || comm == nullptr) return DLM_ERR_NULL;
+    if (nranks < 1 || nranks > DLM_MAX_WORLD) return DLM_ERR_WORLD;
+    MoeParams<kMaxWorld> p;
+    std::memset(&p, 0, sizeof(p));
+    for (int i = 0; i < nranks; ++i) {
+        int rc = check_moe(&moe[i]);
+        if (rc == DLM_OK) rc = check_comm(&comm[i]);
+        if (rc != DLM_OK) return rc;
+        if (comm[i].world != nranks || comm[i].rank != i || comm[i].out_mc != nullptr) return DLM_ERR_WORLD;
+        if (moe[i].m != comm[i].rows || moe[i].n != comm[i].n || moe[i].m != moe[0].m || moe[i].n != moe[0].n ||
+            moe[i].m_max != moe[0].m_max)
+            return DLM_ERR_SHAPE;
+    }
+    DeviceInfo info;
+    int rc = device_info(&info);
+    if (rc != DLM_OK) return rc;
+    for (int i = 0; i < nranks; ++i) {
+        rc = fill_moe(&p.g[i], &moe[i]);
+        if (rc != DLM_OK) return rc;
+        fill_comm(&p.c[i], &comm[i]);
+    }
+    p.fused = 1;
+    int grid = info.sms / nranks;
+    if (comm[0].max_ctas > 0 && comm[0].max_ctas < grid) grid = comm[0].max_ctas;
+    if (grid < 1) return DLM_ERR_GRID;
+    return launch_moe_loopback(p, grid, nranks, {static_cast<cudaStream_t>(stream), false, true});
+}
+
 int dlm_rowpar_bf16_loopback(const DlmGemm* gemm, const DlmComm* comm, int nranks, dlm_stream_t stream) {
     DeviceInfo info;
     int rc = device_info(&info);
@@ -436,6 +558,8 @@ int dlm_abi_check(size_t sizeof_comm, size_t sizeof_gemm, size_t sizeof_status) 
                ? DLM_OK
                : DLM_ERR_SHAPE;
 }
+
+int dlm_abi_check_moe(size_t sizeof_moe) { return sizeof_moe == sizeof(DlmMoe) ? DLM_OK : DLM_ERR_SHAPE; }
 
 const char* dlm_strerror(int code) {
     switch (code) {

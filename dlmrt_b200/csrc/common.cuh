@@ -233,6 +233,45 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
         : "memory");
 }
 
+// ---- block-scaled FP4 (NVFP4: E2M1 values, one UE4M3 scale per 16 elements along K) --------------------------------
+// Instruction descriptor of kind::mxf4nvf4: bits [7,10) A format 1 = E2M1, [10,13) B format 1 = E2M1, 15/16 majors 0 = K,
+// [17,23) n >> 3, bit 23 scale format 0 = UE4M3, [24,29) m >> 4, bit 31 = 0: K = 64 per instruction. The scale-factor
+// ids at [4,6) and [29,31) stay 0: with four scales per row (scale_vec::4X) the whole 32-bit TMEM word is used.
+__host__ __device__ constexpr uint32_t umma_idesc_nvfp4(int m, int n) {
+    return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// D[tmem] (+)= (A * SFA)[smem] * (B * SFB)[smem]^T, K = 64 FP4 elements (32 bytes of each K-major row). The scale
+// factors are read from tensor memory: row r of the operand finds its four bytes at lane r % 32, column r / 32 of the
+// given address (each 32-lane quarter holds a copy), which is what utccp_128x4() below writes.
+__device__ __forceinline__ void umma_nvfp4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                           uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n"
+        "}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+        : "memory");
+}
+
+// Descriptor of one 512-byte scale-factor atom in shared memory: 32 rows of 16 bytes, unswizzled, 8-row groups 128
+// bytes apart. Byte (r % 32) * 16 + (r / 32) * 4 + j of the atom is scale j (0..3) of operand row r (0..127).
+__device__ __forceinline__ uint64_t utccp_desc(const void* smem_atom) {
+    const uint32_t addr = smem_u32(smem_atom);
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((addr & 0x3FFFF) >> 4);
+    d |= static_cast<uint64_t>(128 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    return d;
+}
+
+// Copies one such atom into four TMEM columns starting at `taddr`, replicated into all four 32-lane quarters.
+__device__ __forceinline__ void utccp_128x4(uint32_t taddr, uint64_t desc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+
 // Arrives on `bar` once every MMA issued so far by this thread has completed (implies fence::before_thread_sync).
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))

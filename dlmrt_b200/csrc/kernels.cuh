@@ -42,6 +42,33 @@ struct alignas(64) RowparParams {
     int fused;  // 0: plain GEMM into g.out; 1: push + reduce
 };
 
+// The NVFP4 expert down-projection of one rank (GEMM2 of the routed experts + the weighted combine).
+struct alignas(64) MoeDev {
+    CUtensorMap tm_w;         // W2 codes as bytes [e_local * n, f / 2], box 128 B x 128 rows, 128-byte swizzle
+    CUtensorMap tm_a;         // activation codes [e_local * m_max, f / 2], box 128 B x 32 rows, 128-byte swizzle
+    const uint8_t* a_scales;  // [e_local * m_max, f / 16] E4M3, linear
+    const uint8_t* w_scales;  // [e_local][n / 128][f / 64][512] E4M3 in 128 x 4 atoms
+    const int* amap;          // [e_total, m_max] pair index (token * top_k + k) of each expert's slots
+    const int* counts;        // [e_total]
+    const float* g2;          // [e_local]
+    const int* ids;           // [m, top_k] global expert ids
+    const float* weights;     // [m, top_k]
+    const __nv_bfloat16* shared;  // [m, n] or null
+    __nv_bfloat16* y;         // [m * top_k, n] per-(token, expert) outputs (workspace)
+    int* gen;                 // workspace header: launch generation [256]
+    int* counters;            //                   arrival counters [2][kMaxTiles]
+    __nv_bfloat16* out;       // plain (unfused) output [m, n]
+    long long ldo;
+    int m, n, f, top_k, m_max, lo, e_local, e_total, stages, rows_cap;
+};
+
+template <int NR>
+struct alignas(64) MoeParams {
+    MoeDev g[NR];
+    CommDev c[NR];
+    int fused;
+};
+
 struct LaunchOpts {
     cudaStream_t stream;
     bool pdl;
@@ -52,6 +79,10 @@ int launch_reduce(const ReduceParams<1>& p, int grid, int threads, const LaunchO
 int launch_reduce_loopback(const ReduceParams<kMaxWorld>& p, int grid, int nranks, int threads, const LaunchOpts& o);
 int launch_rowpar(const RowparParams<1>& p, int grid, const LaunchOpts& o);
 int launch_rowpar_loopback(const RowparParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o);
+int launch_moe(const MoeParams<1>& p, int grid, const LaunchOpts& o);
+int launch_moe_loopback(const MoeParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o);
+int moe_stage_bytes(int rows_cap);
+int moe_stages(int rows_cap);
 int rowpar_smem_bytes(int m, int stages);
 int rowpar_stages(int m);
 int rowpar_max_ctas_per_sm(int m);

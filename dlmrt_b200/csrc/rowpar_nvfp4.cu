@@ -1,0 +1,382 @@
+// NVFP4 MoE expert down-projection (GEMM2 of the routed experts), the weighted top-k combine, and the tensor-parallel
+// reduction that follows, in one kernel for sm_100a.
+//
+//   y[token, k]   = bf16( (sum over f of act[slot, f] * W2[e, :, f]) * g2[e] )        e = ids[token, k] local to the rank
+//   out[token]    = bf16( sum over k in list order of weight[token, k] * y[token, k] )  (+ shared -> bf16)
+//   then out is this rank's partial of the all-reduce (experts are split whole across ranks).
+//
+// Arithmetic follows the reference's statement of the TRT-LLM-gen MoE roundings, dlmrt/ops/triton/nvfp4_moe.py:107-150
+// (FP32 dot of E2M1 x E4M3-per-16 operands, times g2, BF16 per (token, expert); FP32 combine in list order); the entry
+// point replaces dlmrt/quantization/nvfp4.py:280-306 (`trtllm_moe`) plus the add and reduce of
+// dlmrt/models/llada2/model.py:354-362,437-438.
+//
+// Work item = (active local expert, 128 output features): W2's [128 x F] slab sits on the MMA's M axis, the expert's
+// rows (tokens routed to it, padded to 16) on its N axis. Persistent CTAs take items round-robin:
+//   warp 0   TMA: per 256-element k-block the 16 KB code slab of W2 and the expert's activation rows (boxes of 32 rows)
+//   warp 3   scale loader: W2's pre-interleaved 128 x 4 scale atoms and the activation rows' linear E4M3 scales,
+//            rewritten into the same atom layout, into the stage
+//   warp 1   per k-block: tcgen05.cp the scale atoms into tensor memory, then up to four
+//            tcgen05.mma.kind::mxf4nvf4.block_scale (K = 64) into the FP32 accumulator
+//   warps 4-11  per item: tcgen05.ld, times g2, BF16, scatter rows to Y[pair] through the expert's slot map
+// When all CTAs are through their items (arrival counter), rows of the output are combined from Y in FP32 and pushed
+// into the owner ranks' receive slots, and the reduction phases of comm.cuh follow.
+#include "kernels.cuh"
+
+namespace dlm {
+
+namespace {
+
+constexpr int kMoeThreads = kFusedThreads;
+constexpr int kCodeTileW = 128 * 128;  // 128 rows x 128 bytes (256 FP4) of W2 codes
+constexpr int kBoxRows = 32;           // activation rows per TMA box
+constexpr int kAtom = 512;             // one 128-row x 4-scale atom
+constexpr int kStepsPerBlock = 4;      // K = 64 instructions per 256-element k-block
+constexpr int kTmemAcc = 0, kTmemSfa = 256, kTmemSfb = 272, kTmemCols = 512;
+constexpr int kMaxLocalExperts = 256;
+
+struct MoeSmem {
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
+    uint64_t acc_full;
+    uint64_t acc_empty;
+    uint32_t tmem_base;
+    int n_active, epoch, gen;
+    int warp_count[8];
+    float scratch[32];
+    short active[kMaxLocalExperts];
+};
+
+}  // namespace
+
+int moe_stage_bytes(int rows_cap) {
+    return kCodeTileW + rows_cap * 128 + kStepsPerBlock * kAtom + kStepsPerBlock * ((rows_cap + 127) / 128) * kAtom;
+}
+
+int moe_stages(int rows_cap) {
+    int s = kSmemBudget / moe_stage_bytes(rows_cap);
+    return s > kMaxStages ? kMaxStages : s;
+}
+
+template <int NR>
+__global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_constant__ MoeParams<NR> p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const int slot = NR == 1 ? 0 : static_cast<int>(blockIdx.y);
+    const MoeDev& g = p.g[slot];
+    const CommDev& c = p.c[slot];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int block = static_cast<int>(blockIdx.x), blocks = static_cast<int>(gridDim.x);
+
+    const int atoms = (g.rows_cap + 127) / 128;  // activation scale atoms per K = 64 step
+    const int stage_bytes = kCodeTileW + g.rows_cap * 128 + kStepsPerBlock * kAtom + kStepsPerBlock * atoms * kAtom;
+    const int off_a = kCodeTileW, off_sfa = off_a + g.rows_cap * 128, off_sfb = off_sfa + kStepsPerBlock * kAtom;
+    const int feature_tiles = g.n / kBlockF;
+    const int steps = g.f / 64;                  // K = 64 instructions per item
+    const int nkb = (steps + kStepsPerBlock - 1) / kStepsPerBlock;
+    const int scale_row = g.f / 16;              // bytes of scales per activation row
+
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    MoeSmem* sm = reinterpret_cast<MoeSmem*>(tiles + g.stages * stage_bytes);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < g.stages; ++i) {
+            mbar_init(&sm->full[i], 2);  // the TMA producer's expect_tx arrival and the scale loader's arrival
+            mbar_init(&sm->empty[i], 1);
+        }
+        mbar_init(&sm->acc_full, 1);
+        mbar_init(&sm->acc_empty, 8);    // one arrival per epilogue warp
+        fence_barrier_init();
+        tma_prefetch_descriptor(&g.tm_w);
+        tma_prefetch_descriptor(&g.tm_a);
+    }
+    if (warp == 2) tmem_alloc(&sm->tmem_base, kTmemCols);
+    // Routing (counts, slots, activations) comes from the previous kernels of the stream: nothing of it may be read
+    // before they are complete.
+    pdl_wait();
+    // Compact list of this rank's experts that have rows, in expert order.
+    {
+        const int e = threadIdx.x;
+        const bool has = e < g.e_local && g.counts[g.lo + e] > 0;
+        const unsigned ballot = __ballot_sync(0xffffffff, has);
+        if (warp < 8 && lane == 0) sm->warp_count[warp] = __popc(ballot);
+        tcgen05_fence_before();
+        __syncthreads();
+        tcgen05_fence_after();
+        if (warp < 8) {
+            int base = 0;
+            for (int wv = 0; wv < warp; ++wv) base += sm->warp_count[wv];
+            if (has) sm->active[base + __popc(ballot & ((1u << lane) - 1))] = static_cast<short>(e);
+            if (threadIdx.x == 0) {
+                int total = 0;
+                for (int wv = 0; wv < 8; ++wv) total += sm->warp_count[wv];
+                sm->n_active = total;
+            }
+        }
+        if (threadIdx.x == 96) {
+            if (p.fused) sm->epoch = c.epochs[block];
+            sm->gen = g.gen[block];
+        }
+        __syncthreads();
+    }
+    const uint32_t tmem = sm->tmem_base;
+    const int n_items = sm->n_active * feature_tiles;
+    const long long deadline = globaltimer() + (c.timeout_ns > 0 ? c.timeout_ns : 2000000000ll);
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            for (int i = block; i < n_items; i += blocks) {
+                const int e = sm->active[i / feature_tiles], ft = i % feature_tiles;
+                const int cnt = min(g.counts[g.lo + e], g.rows_cap);
+                const int boxes = (cnt + kBoxRows - 1) / kBoxRows;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int st = it % g.stages;
+                    if (it >= g.stages && !mbar_wait(&sm->empty[st], ((it / g.stages) & 1) ^ 1, deadline)) {
+                        report(c.status, kErrTimeout, st, kPhasePipeline, 0);
+                        i = n_items;
+                        break;
+                    }
+                    uint8_t* stage = tiles + st * stage_bytes;
+                    mbar_expect_tx(&sm->full[st], static_cast<uint32_t>(kCodeTileW + boxes * kBoxRows * 128));
+                    tma_load_2d(stage, &g.tm_w, &sm->full[st], kb * 128, e * g.n + ft * kBlockF, kEvictFirst);
+                    for (int b = 0; b < boxes; ++b)
+                        tma_load_2d(stage + off_a + b * kBoxRows * 128, &g.tm_a, &sm->full[st], kb * 128,
+                                    e * g.m_max + b * kBoxRows, kEvictLast);
+                }
+            }
+        }
+    } else if (warp == 3) {
+        // Scale loader. Atom byte (r % 32) * 16 + ((r % 128) / 32) * 4 + j holds scale j of row r.
+        const int total_slots = g.e_local * g.m_max;
+        int it = 0;
+        for (int i = block; i < n_items; i += blocks) {
+            const int e = sm->active[i / feature_tiles], ft = i % feature_tiles;
+            const int cnt = min(g.counts[g.lo + e], g.rows_cap);
+            const int rows = ((cnt + kBoxRows - 1) / kBoxRows) * kBoxRows;
+            bool alive = true;
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int st = it % g.stages;
+                if (it >= g.stages && !mbar_wait(&sm->empty[st], ((it / g.stages) & 1) ^ 1, deadline)) {
+                    alive = false;
+                    break;
+                }
+                uint8_t* stage = tiles + st * stage_bytes;
+                const int nsteps = min(kStepsPerBlock, steps - kb * kStepsPerBlock);
+                const uint4* wsrc = reinterpret_cast<const uint4*>(
+                    g.w_scales + (static_cast<size_t>(e * feature_tiles + ft) * steps + kb * kStepsPerBlock) * kAtom);
+                uint4* wdst = reinterpret_cast<uint4*>(stage + off_sfa);
+                for (int v = lane; v < nsteps * (kAtom / 16); v += 32) wdst[v] = __ldg(wsrc + v);
+                for (int r = lane; r < rows; r += 32) {
+                    const int srow = e * g.m_max + r;
+                    const uint32_t* src = reinterpret_cast<const uint32_t*>(
+                        g.a_scales + static_cast<size_t>(srow) * scale_row + kb * kStepsPerBlock * 4);
+                    uint8_t* dst = stage + off_sfb + (r / 128) * kAtom + (r % 32) * 16 + ((r % 128) / 32) * 4;
+                    for (int s = 0; s < nsteps; ++s)
+                        *reinterpret_cast<uint32_t*>(dst + s * atoms * kAtom) = srow < total_slots ? __ldcg(src + s) : 0u;
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm->full[st]);
+            }
+            if (!alive) break;
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int it = 0, item = 0;
+            for (int i = block; i < n_items; i += blocks, ++item) {
+                const int e = sm->active[i / feature_tiles];
+                const int cnt = min(g.counts[g.lo + e], g.rows_cap);
+                const int n_mma = max(16, (cnt + 15) & ~15);
+                const uint32_t idesc = umma_idesc_nvfp4(kBlockF, n_mma);
+                bool alive = true;
+                // The accumulator of the previous item must have been read out.
+                if (item > 0 && !mbar_wait(&sm->acc_empty, (item - 1) & 1, deadline)) {
+                    report(c.status, kErrTimeout, 0, kPhasePipeline, 4);
+                    break;
+                }
+                tcgen05_fence_after();
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int st = it % g.stages;
+                    if (!mbar_wait(&sm->full[st], (it / g.stages) & 1, deadline)) {
+                        report(c.status, kErrTimeout, st, kPhasePipeline, 1);
+                        alive = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    uint8_t* stage = tiles + st * stage_bytes;
+                    const int nsteps = min(kStepsPerBlock, steps - kb * kStepsPerBlock);
+                    for (int s = 0; s < nsteps; ++s) {
+                        utccp_128x4(tmem + kTmemSfa + 4 * s, utccp_desc(stage + off_sfa + s * kAtom));
+                        for (int a = 0; a * 128 < n_mma; ++a)
+                            utccp_128x4(tmem + kTmemSfb + 8 * s + 4 * a, utccp_desc(stage + off_sfb + (s * atoms + a) * kAtom));
+                    }
+                    const uint64_t dw = umma_desc_k128(stage), da = umma_desc_k128(stage + off_a);
+                    for (int s = 0; s < nsteps; ++s)
+                        umma_nvfp4(tmem + kTmemAcc, dw + 2 * s, da + 2 * s, idesc, tmem + kTmemSfa + 4 * s,
+                                   tmem + kTmemSfb + 8 * s, (kb | s) != 0);
+                    umma_commit(&sm->empty[st]);
+                }
+                umma_commit(&sm->acc_full);
+                if (!alive) break;
+            }
+        }
+    } else if (warp >= 4) {
+        // Epilogue: lane = output feature of the tile, registers = the expert's rows. Scatter through the slot map.
+        const int quarter = warp & 3, half = (warp - 4) >> 2;
+        int item = 0;
+        for (int i = block; i < n_items; i += blocks, ++item) {
+            const int e = sm->active[i / feature_tiles], ft = i % feature_tiles;
+            const int cnt = min(g.counts[g.lo + e], g.rows_cap);
+            const int n_mma = max(16, (cnt + 15) & ~15);
+            const float g2 = g.g2[e];
+            const int* slots = g.amap + static_cast<size_t>(g.lo + e) * g.m_max;
+            const bool ok = mbar_wait(&sm->acc_full, item & 1, deadline);
+            if (!ok) report(c.status, kErrTimeout, 0, kPhasePipeline, 2);
+            tcgen05_fence_after();
+            const int col = ft * kBlockF + quarter * 32 + lane;
+            for (int chunk = half; chunk < n_mma / 16 && ok; chunk += 2) {
+                uint32_t r[16];
+                tmem_load_16(tmem + kTmemAcc + (static_cast<uint32_t>(quarter * 32) << 16) + chunk * 16, r);
+                tmem_load_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int row = chunk * 16 + j;
+                    if (row < cnt)
+                        g.y[static_cast<size_t>(slots[row]) * g.n + col] = __float2bfloat16_rn(__uint_as_float(r[j]) * g2);
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm->acc_empty);
+            if (!ok) break;
+        }
+    }
+    // Every Y row this CTA produced is written; announce it and wait for the rest of the grid (the combine reads rows
+    // written by other CTAs). Counters are banked by launch generation as in the BF16 kernel.
+    __threadfence();
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+    CommCtx x{};
+    if (p.fused) x = comm_begin(c, block, blocks, sm->epoch);
+    {
+        const int gen = sm->gen + 1;
+        int* counter = g.counters + (gen & 1) * kMaxTiles;
+        if (threadIdx.x == 0) {
+            if (block == 0) g.counters[((gen + 1) & 1) * kMaxTiles] = 0;
+            atomicAdd(counter, 1);
+            int seen;
+            do {
+                asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+                if (seen >= blocks) break;
+                if (globaltimer() > deadline) {
+                    report(c.status, kErrTimeout, 0, kPhasePipeline, 3);
+                    break;
+                }
+            } while (true);
+            for (int j = block; j < kEpochSlots; j += blocks) g.gen[j] = gen;
+        }
+        __syncthreads();
+    }
+    // Combine: out[row] = bf16(sum over k in list order of w_k * y_k), experts of other ranks contribute 0 * 0.
+    {
+        const int t = threadIdx.x, threads = g.n / kVec;
+        for (int row = block; row < g.m; row += blocks) {
+            if (t < threads) {
+                float acc[kVec] = {};
+                for (int k = 0; k < g.top_k; ++k) {
+                    const int e = g.ids[row * g.top_k + k] - g.lo;
+                    const bool local = e >= 0 && e < g.e_local;
+                    uint4 raw = make_uint4(0, 0, 0, 0);
+                    float w = 0.f;
+                    if (local) {
+                        w = g.weights[row * g.top_k + k];
+                        raw = __ldcg(reinterpret_cast<const uint4*>(g.y + static_cast<size_t>(row * g.top_k + k) * g.n) + t);
+                    }
+                    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = __bfloat1622float2(b[i]);
+                        acc[2 * i] = fmaf(w, f.x, acc[2 * i]);
+                        acc[2 * i + 1] = fmaf(w, f.y, acc[2 * i + 1]);
+                    }
+                }
+                uint4 packed = pack_bf16x8(acc);
+                if (g.shared) {
+                    float v[kVec] = {};
+                    add_bf16x8(v, packed);
+                    add_bf16x8(v, *(reinterpret_cast<const uint4*>(g.shared + static_cast<size_t>(row) * g.n) + t));
+                    packed = pack_bf16x8(v);
+                }
+                if (p.fused) {
+                    store_v4(push_address(c, x, row, t * kVec), packed);
+                } else {
+                    store_v4(g.out + static_cast<size_t>(row) * g.ldo + t * kVec, packed);
+                }
+            }
+        }
+    }
+    if (p.fused) {
+        stamp(c, x, 1);
+        pdl_launch_dependents();
+        rearm_early(c, x);
+        own_and_collect(c, x, sm->scratch);
+        rearm_late(c, x);
+        comm_end(c, x);
+    } else {
+        pdl_launch_dependents();
+    }
+}
+
+template <int NR>
+static int launch_impl(const MoeParams<NR>& p, dim3 grid, const LaunchOpts& o) {
+    const int smem = p.g[0].stages * moe_stage_bytes(p.g[0].rows_cap) + static_cast<int>(sizeof(MoeSmem)) + 1024;
+    static bool raised[64] = {};
+    cudaError_t err = cudaSuccess;
+    int dev = 0;
+    (void)cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !raised[dev]) {
+        err = cudaFuncSetAttribute(moe_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   kSmemBudget + static_cast<int>(sizeof(MoeSmem)) + 1024);
+        raised[dev] = err == cudaSuccess;
+    }
+    if (err == cudaSuccess) {
+        cudaLaunchConfig_t config{};
+        config.gridDim = grid;
+        config.blockDim = dim3(kMoeThreads);
+        config.dynamicSmemBytes = static_cast<size_t>(smem);
+        config.stream = o.stream;
+        cudaLaunchAttribute attrs[2];
+        int n = 0;
+        if (o.pdl) {
+            attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attrs[n].val.programmaticStreamSerializationAllowed = 1;
+            ++n;
+        }
+        if (o.cooperative) {
+            attrs[n].id = cudaLaunchAttributeCooperative;
+            attrs[n].val.cooperative = 1;
+            ++n;
+        }
+        config.attrs = attrs;
+        config.numAttrs = n;
+        err = cudaLaunchKernelEx(&config, moe_kernel<NR>, p);
+    }
+    if (err != cudaSuccess) {
+        g_last_cuda_error = static_cast<int>(err);
+        (void)cudaGetLastError();
+        return -6;
+    }
+    ++g_launches;
+    return 0;
+}
+
+int launch_moe(const MoeParams<1>& p, int grid, const LaunchOpts& o) { return launch_impl<1>(p, dim3(grid), o); }
+
+int launch_moe_loopback(const MoeParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o) {
+    return launch_impl<kMaxWorld>(p, dim3(grid, nranks), o);
+}
+
+}  // namespace dlm

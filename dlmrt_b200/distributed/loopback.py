@@ -12,7 +12,7 @@ import ctypes as C
 import torch
 
 from .. import _lib
-from .._lib import DlmComm, DlmGemm
+from .._lib import DlmComm, DlmGemm, DlmMoe
 from .parallel import Group, Handle
 
 
@@ -106,6 +106,16 @@ class LoopbackWorld:
             gemms[r] = gm
         stream = torch.cuda.current_stream(self.device).cuda_stream
         _lib.check(_lib.lib().dlm_rowpar_bf16_loopback(gemms, comms, self.world, stream), f"loopback rowpar {site}")
+        self._done(chain, outs)
+        return outs
+
+    def moe(self, descriptors, *, site, chain=0):
+        """All ranks of the fused NVFP4 expert down-projection + reduction in one launch; descriptors[r] is rank r's
+        DlmMoe (dlmrt_b200.quantization.nvfp4.descriptor)."""
+        comms, outs = self._comms(descriptors[0].m, descriptors[0].n, site, chain, None, None, 0.0, 1.0)
+        moes = (DlmMoe * self.world)(*descriptors)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _lib.check(_lib.lib().dlm_rowpar_nvfp4_moe_loopback(moes, comms, self.world, stream), f"loopback moe {site}")
         self._done(chain, outs)
         return outs
 

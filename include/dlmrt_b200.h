@@ -111,6 +111,32 @@ typedef struct DlmGemm {
     int32_t token_tiles; /* tiles along m (each m / token_tiles tokens, a multiple of 16), 0 = chosen by the library */
 } DlmGemm;
 
+/* The NVFP4 expert half of a fused call: GEMM2 (down-projection) of this rank's routed experts and the weighted top-k
+ * combine. Formats follow the reference: E2M1 codes two per byte with the even element in the low nibble, one FP8
+ * E4M3 scale per 16 input elements, FP32 per-expert output scale g2 = input scale x weight scale
+ * (dlmrt/quantization/nvfp4.py:1-12,117-121); expert-major activation slots and slot map as in
+ * dlmrt/ops/triton/nvfp4_moe.py:11-12,107-150. Weight scales are NOT linear: they are pre-arranged once, when the
+ * experts are loaded, into 128-row x 4-scale atoms ([e_local][n / 128][f / 64][512] bytes, byte (r % 32) * 16 +
+ * (r / 32) * 4 + j = scale j of row r), as the reference pre-arranges them for its own B200 back-end
+ * (nvfp4.py:108-112). */
+typedef struct DlmMoe {
+    const void* act_codes;   /* [e_local * m_max, f / 2] uint8: GEMM2 input rows, slot e * m_max + j */
+    const void* act_scales;  /* [e_local * m_max, f / 16] E4M3, linear */
+    const int32_t* amap;     /* [e_total, m_max] int32: token * top_k + k of the j-th row routed to expert e */
+    const int32_t* counts;   /* [e_total] int32 rows per expert */
+    const void* w_codes;     /* [e_local, n, f / 2] uint8 */
+    const void* w_scales;    /* [e_local, n / 128, f / 64, 512] E4M3 atoms */
+    const float* g2;         /* [e_local] */
+    const int32_t* ids;      /* [m, top_k] int32 global expert ids, in the order the combine sums them */
+    const float* weights;    /* [m, top_k] FP32 routing weights (BF16-representable in the reference) */
+    const void* shared;      /* [m, n] BF16 added after the combine (shared expert), or NULL */
+    int32_t m, n, f, top_k;  /* m <= 256; n % 128 == 0, n <= 3072; f % 64 == 0; top_k <= 16 */
+    int32_t m_max;           /* rows reserved per expert (<= 256) */
+    int32_t lo, e_local, e_total; /* this rank's experts are [lo, lo + e_local), e_local <= 256 */
+    void* workspace;         /* dlm_moe_workspace_bytes(m, n, top_k) bytes, zero-initialised once, 256-byte aligned */
+    int64_t workspace_bytes;
+} DlmMoe;
+
 /* Device status read back by dlm_status_read(). */
 typedef struct DlmStatus {
     int32_t code;   /* DLM_OK or DLM_ERR_TIMEOUT */
@@ -166,6 +192,18 @@ DLM_API int dlm_gemm_bf16_noalloc(const void* x, const void* w, void* out, int m
  * gemm->m == comm->rows, gemm->n == comm->n <= DLM_FUSED_MAX_N. */
 DLM_API int dlm_rowpar_bf16(const DlmGemm* gemm, const DlmComm* comm, dlm_stream_t stream);
 
+/* NVFP4 routed experts on one GPU: out[m, n] BF16 (ldo elements) = combine(GEMM2). Replaces the GEMM2 + finalize
+ * half of nvfp4.trtllm_moe (dlmrt/quantization/nvfp4.py:280-306) and the `torch.add(routed, shared)` that follows it
+ * (dlmrt/models/llada2/model.py:360-362). */
+DLM_API int dlm_moe_nvfp4(const DlmMoe* moe, void* out, int64_t ldo, int pdl, dlm_stream_t stream);
+
+/* The same fused with the reduction over ranks (experts are split whole across ranks): replaces
+ * trtllm_moe -> [add shared] -> Group.reduce (llada2/model.py:354-362,437-438; diffusion_gemma/model.py:281-292).
+ * moe->m == comm->rows, moe->n == comm->n. */
+DLM_API int dlm_rowpar_nvfp4_moe(const DlmMoe* moe, const DlmComm* comm, dlm_stream_t stream);
+DLM_API int dlm_rowpar_nvfp4_moe_loopback(const DlmMoe* moe, const DlmComm* comm, int nranks, dlm_stream_t stream);
+DLM_API size_t dlm_moe_workspace_bytes(int m, int n, int top_k);
+
 /* Single-GPU loopback of `nranks` ranks of dlm_rowpar_bf16 in one launch (see dlm_reduce_bf16_loopback). */
 DLM_API int dlm_rowpar_bf16_loopback(const DlmGemm* gemm, const DlmComm* comm, int nranks, dlm_stream_t stream);
 
@@ -180,6 +218,7 @@ DLM_API int dlm_status_read(int32_t* device_status, DlmStatus* out, dlm_stream_t
 
 /* Returns DLM_OK when the caller's struct sizes (a binding in another language) match the library's. */
 DLM_API int dlm_abi_check(size_t sizeof_comm, size_t sizeof_gemm, size_t sizeof_status);
+DLM_API int dlm_abi_check_moe(size_t sizeof_moe);
 
 DLM_API const char* dlm_strerror(int code);
 DLM_API int dlm_last_cuda_error(void);

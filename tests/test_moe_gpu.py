@@ -1,0 +1,136 @@
+"""The NVFP4 expert down-projection kernel (dlm_moe_nvfp4, dlm_rowpar_nvfp4_moe[_loopback]) against the CPU oracle."""
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import assert_same_bits, bits
+from oracle import nvfp4 as onv
+from oracle import reduce as red
+from oracle.bf16 import bf16_to_f32, f32_to_bf16, to_torch
+
+pytestmark = pytest.mark.gpu
+
+
+def make_case(rows, hidden, f, e_total, top_k, seed, exact=False, skew=False):
+    """Routed inputs of one MoE layer call as numpy arrays in the layouts the kernel takes.
+
+    exact: codes and power-of-two scales chosen so that every product and partial sum is exact in FP32; the kernel must
+    then match the oracle bit for bit whatever its summation order, which also pins the scale-factor layout."""
+    rng = np.random.default_rng(seed)
+    if skew:
+        p = 1.0 / np.arange(1, e_total + 1) ** 1.2
+        p /= p.sum()
+        ids = np.stack([np.sort(rng.choice(e_total, top_k, replace=False, p=p)) for _ in range(rows)]).astype(np.int32)
+    else:
+        ids = np.stack([np.sort(rng.permutation(e_total)[:top_k]) for _ in range(rows)]).astype(np.int32)
+    weights = rng.random((rows, top_k), dtype=np.float32)
+    weights = bf16_to_f32(f32_to_bf16(weights / weights.sum(-1, keepdims=True) * 2.5))
+    amap, counts = onv.route_slots(ids, e_total)
+    m_max = rows
+    if exact:
+        w_codes = rng.integers(0, 256, (e_total, hidden, f // 2), dtype=np.uint8)
+        a_codes = rng.integers(0, 256, (e_total * m_max, f // 2), dtype=np.uint8)
+        pow2 = np.array([0x30, 0x38, 0x40, 0x48], dtype=np.uint8)  # E4M3 0.5, 1, 2, 4
+        w_scales = pow2[rng.integers(0, 4, (e_total, hidden, f // 16))]
+        a_scales = pow2[rng.integers(0, 4, (e_total * m_max, f // 16))]
+        g2 = np.full(e_total, 2.0 ** -6, dtype=np.float32)
+        weights = np.ones_like(weights) * 0.5
+    else:
+        w = rng.standard_normal((e_total, hidden, f)).astype(np.float32) * 0.02
+        s2 = np.float32(np.abs(w).max() / 2688)
+        q = [onv.quantize(w[e], s2) for e in range(e_total)]
+        w_codes, w_scales = np.stack([c for c, _ in q]), np.stack([s for _, s in q])
+        act = rng.standard_normal((e_total * m_max, f)).astype(np.float32) * 0.3
+        a2 = np.float32(np.abs(act).max() / 2688)
+        a_codes, a_scales = onv.quantize(act, a2)
+        g2 = np.full(e_total, a2 * s2, dtype=np.float32)
+    return dict(ids=ids, weights=weights.astype(np.float32), amap=amap, counts=counts, m_max=m_max, w_codes=w_codes,
+                w_scales=w_scales, a_codes=a_codes, a_scales=a_scales, g2=g2, rows=rows, hidden=hidden, f=f,
+                e_total=e_total, top_k=top_k)
+
+
+def oracle_out(case, lo, e_local, shared=None):
+    m_max = case["m_max"]
+    y = onv.moe_down(case["a_codes"][lo * m_max:(lo + e_local) * m_max], case["a_scales"][lo * m_max:(lo + e_local) * m_max],
+                     case["amap"], case["counts"], case["w_codes"][lo:lo + e_local], case["w_scales"][lo:lo + e_local],
+                     case["g2"][lo:lo + e_local], lo, case["rows"] * case["top_k"], accumulate=np.float64)
+    return onv.combine(y, case["ids"], case["weights"], lo, e_local, shared), y
+
+
+def device_args(case, lo, e_local, dev="cuda"):
+    from dlmrt_b200.quantization import nvfp4
+
+    m_max = case["m_max"]
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)  # noqa: E731
+    experts = {"lo": lo, "w2": t(case["w_codes"][lo:lo + e_local]),
+               "s2": nvfp4.interleave_scales(t(case["w_scales"][lo:lo + e_local])), "g2": t(case["g2"][lo:lo + e_local])}
+    buffers = nvfp4.Buffers(case["rows"], case["hidden"], case["top_k"], dev)
+    args = dict(act_codes=t(case["a_codes"][lo * m_max:(lo + e_local) * m_max]),
+                act_scales=t(case["a_scales"][lo * m_max:(lo + e_local) * m_max]), amap=t(case["amap"]),
+                counts=t(case["counts"]), experts=experts, ids=t(case["ids"]), weights=t(case["weights"]),
+                buffers=buffers, num_experts=case["e_total"])
+    return args
+
+
+def run_single(case, shared=None):
+    from dlmrt_b200.quantization import nvfp4
+
+    args = device_args(case, 0, case["e_total"])
+    out = torch.empty(case["rows"], case["hidden"], dtype=torch.bfloat16, device="cuda")
+    sh = to_torch(shared).cuda() if shared is not None else None
+    for _ in range(2):  # twice on one workspace: the rendezvous counters must re-arm themselves
+        nvfp4.moe_down(out=out, shared=sh, **args)
+    torch.cuda.synchronize()
+    return bits(out)
+
+
+@pytest.mark.parametrize("rows, hidden, f, e_total, top_k", [(32, 2048, 512, 16, 4), (32, 2048, 512, 256, 8),
+                                                            (64, 256, 704, 8, 2), (256, 2816, 704, 32, 8)])
+def test_exact_operands_match_bit_for_bit(rows, hidden, f, e_total, top_k):
+    case = make_case(rows, hidden, f, e_total, top_k, seed=rows + f, exact=True)
+    want, _ = oracle_out(case, 0, e_total)
+    assert_same_bits(run_single(case), want, "exact NVFP4 expert down-projection")
+
+
+@pytest.mark.parametrize("rows, hidden, f, e_total, top_k, skew", [(32, 2048, 512, 64, 8, False), (32, 2048, 512, 64, 8, True),
+                                                                  (256, 2816, 704, 16, 8, False)])
+def test_gaussian_operands_within_tolerance(rows, hidden, f, e_total, top_k, skew):
+    """Per output row relative L2 <= 1e-2 against the W4A4 oracle on identical quantised inputs; with a shared-expert
+    addend as well."""
+    case = make_case(rows, hidden, f, e_total, top_k, seed=7, skew=skew)
+    rng = np.random.default_rng(1)
+    shared = f32_to_bf16(rng.standard_normal((rows, hidden)).astype(np.float32) * 0.05)
+    for sh in (None, shared):
+        want, _ = oracle_out(case, 0, e_total, sh)
+        got = bf16_to_f32(run_single(case, sh)).astype(np.float64)
+        ref = bf16_to_f32(want).astype(np.float64)
+        rel = np.linalg.norm(got - ref, axis=1) / np.maximum(np.linalg.norm(ref, axis=1), 1e-30)
+        assert rel.max() <= onv.GEMM2_REL_L2, rel.max()
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_expert_parallel_loopback_matches_oracle(world):
+    """Experts split whole across emulated ranks; each rank's partial is exact (integer-like operands), so the fused
+    reduction must equal the oracle's rank-ordered sum of the per-rank combines bit for bit, on every rank."""
+    from dlmrt_b200.distributed.loopback import LoopbackWorld
+    from dlmrt_b200.quantization import nvfp4
+
+    rows, hidden, f, e_total, top_k = 32, 2048, 512, 64, 8
+    case = make_case(rows, hidden, f, e_total, top_k, seed=world, exact=True)
+    e_local = e_total // world
+    lw = LoopbackWorld(world)
+    keep = []
+    for rep in range(2):
+        descs, partials = [], []
+        for r in range(world):
+            args = device_args(case, r * e_local, e_local)
+            keep.append(args)
+            descs.append(nvfp4.descriptor(**args))
+            partials.append(oracle_out(case, r * e_local, e_local)[0])
+        outs = lw.moe(descs, site=f"moe{rep}")
+        torch.cuda.synchronize()
+        lw.check()
+        want = red.reduce(np.stack(partials))
+        for r, out in enumerate(outs):
+            assert_same_bits(bits(out), want, f"rep {rep} rank {r}")
