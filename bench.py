@@ -312,6 +312,125 @@ def run_gpu(args, rank, world):
     print(json.dumps(line))
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# NVFP4 expert workloads (BASELINE configs 4 and 5): not the default bench line, run with --workload c4 | c5
+# ---------------------------------------------------------------------------------------------------------------------
+MOE_SHAPES = {"c4": dict(hidden=2048, f=512, experts=256, top_k=8, rows=32, layers=20,
+                         name="BASELINE config 4: LLaDA2.1-mini-shape MoE, 256 experts top-8, F=512, 32-token block"),
+              "c5": dict(hidden=2816, f=704, experts=128, top_k=8, rows=256, layers=30,
+                         name="BASELINE config 5: DiffusionGemma-shape MoE, 128 experts top-8, F=704, 256-token canvas")}
+
+
+def run_gpu_moe(args, rank, world):
+    """A step = `layers` fused launches of the NVFP4 expert down-projection + combine + reduction (one per layer, each
+    layer with its own expert weights; random codes and scales, seeded routing, uniform or Zipf(1.2))."""
+    import numpy as np
+    import torch
+
+    from dlmrt_b200 import _lib
+    from dlmrt_b200.distributed import parallel
+    from dlmrt_b200.quantization import nvfp4
+
+    shape = MOE_SHAPES[args.workload]
+    hidden, f, experts, top_k, rows = (shape[k] for k in ("hidden", "f", "experts", "top_k", "rows"))
+    layers = min(args.layers, shape["layers"])
+    if world > 1:
+        import torch.distributed as dist
+
+        group = parallel.init()
+        device = group.device
+    else:
+        device = torch.device("cuda", 0)
+        torch.cuda.set_device(device)
+        group = parallel.Group.local(device)
+    e_local, lo = experts // world, rank * (experts // world)
+    rng = np.random.default_rng(5)  # routing identical on every rank
+    if args.routing == "zipf":
+        p = 1.0 / np.arange(1, experts + 1) ** 1.2
+        p = (p / p.sum())[rng.permutation(experts)]
+        ids = np.stack([np.sort(rng.choice(experts, top_k, replace=False, p=p)) for _ in range(rows)])
+    else:
+        ids = np.stack([np.sort(rng.permutation(experts)[:top_k]) for _ in range(rows)])
+    ids = ids.astype(np.int32)
+    amap = np.zeros((experts, rows), dtype=np.int32)
+    counts = np.zeros(experts, dtype=np.int32)
+    for pair, e in enumerate(ids.reshape(-1).tolist()):
+        amap[e, counts[e]] = pair
+        counts[e] += 1
+    active_local = int((counts[lo:lo + e_local] > 0).sum())
+    g = torch.Generator(device=device).manual_seed(1 + rank)
+    u8 = dict(device=device, dtype=torch.uint8, generator=g)
+    layer_experts = []
+    for _ in range(layers):
+        s2 = torch.randint(0x28, 0x48, (e_local, hidden, f // 16), **u8)  # E4M3 scales between 0.25 and 4
+        layer_experts.append({"lo": lo, "w2": torch.randint(0, 256, (e_local, hidden, f // 2), **u8),
+                              "s2": nvfp4.interleave_scales(s2), "g2": torch.full((e_local,), 1e-4, device=device)})
+    act_codes = torch.randint(0, 256, (e_local * rows, f // 2), **u8)
+    act_scales = torch.randint(0x28, 0x48, (e_local * rows, f // 16), **u8)
+    t = lambda a: torch.from_numpy(a).to(device)  # noqa: E731
+    common = dict(act_codes=act_codes, act_scales=act_scales, amap=t(amap), counts=t(counts), ids=t(ids),
+                  weights=torch.full((rows, top_k), 2.5 / top_k, device=device), num_experts=experts,
+                  buffers=nvfp4.Buffers(rows, hidden, top_k, device))
+
+    def step():
+        out = None
+        for i in range(layers):
+            out = nvfp4.moe_down(experts=layer_experts[i], out=None, group=group, site=f"{i}.moe", chain=rows, **common)
+        return out
+
+    stream = torch.cuda.Stream(device)
+    lib = _lib.lib()
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            step()
+        stream.synchronize()
+        group.check()
+        before = lib.dlm_launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+        launches_per_step = lib.dlm_launch_count() - before
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(device)
+    if world > 1:
+        dist.barrier()
+    clocks = Clocks(device.index) if rank == 0 else None
+    with torch.cuda.stream(stream):
+        start.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        stop.record(stream)
+    torch.cuda.synchronize(device)
+    ms = torch.tensor([start.elapsed_time(stop) / args.steps], device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    clock_report = clocks.stop() if clocks else None
+    group.check()
+    if rank != 0:
+        return
+    hbm, which = peaks()
+    weight = active_local * hidden * f * 9 // 16  # codes + E4M3 scales of the active local experts
+    per_launch = float(ms.item()) * 1e-3 / layers
+    t_hbm, t_link = weight / (hbm * 1e9), 2 * (world - 1) * rows * hidden * 2 / world / (NVLINK_GBS * 1e9)
+    if t_hbm >= t_link:
+        roof = {"bound": "hbm", "achieved": round(weight / per_launch / 1e9, 1), "peak": hbm, "unit": "GB/s"}
+    else:
+        roof = {"bound": "nvlink", "achieved": round(t_link * NVLINK_GBS / per_launch, 1), "peak": NVLINK_GBS, "unit": "GB/s"}
+    roof.update(frac=round(roof["achieved"] / roof["peak"], 4), peak_source=f"of {which}", kernel="moe_kernel",
+                algorithmic_bytes_per_launch=weight, avg_launch_us=round(per_launch * 1e6, 2), traffic=None)
+    print(json.dumps({
+        "metric": "fused NVFP4 expert down-projection+combine+reduction latency per MoE layer", "value":
+        round(per_launch * 1e6, 2), "unit": "us", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(float(ms.item()), 4), "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+        "dtype": "nvfp4 (e2m1 x ue4m3 per 16), fp32 accumulate", "data": "synthetic",
+        "config": {"workload": shape["name"] + f", {args.routing} routing, TP={world}, {layers} layers per step",
+                   "active_local_experts": active_local, "tp": world},
+        "gpu_launches": int(launches_per_step * args.steps), "roofline": roof, "clocks": clock_report}))
+
+
+
 def reference_gpu_path(torch, group, lin_o, lin_d, norms, x_o, x_d, h, stream, timed, args, world):
     """torch.mm (cuBLAS) into the symmetric partial followed by the reference's own reduce_norm_residual kernel, the
     same 72 operations, captured in a graph and timed the same way. Returns None when oracle/_ref is not present."""
@@ -365,6 +484,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=36, help="layers per step; fewer only for profiler captures")
+    ap.add_argument("--workload", default="c2", choices=["c2", "c4", "c5"], help="c2 is the bench line; c4/c5 time the "
+                    "NVFP4 expert path of BASELINE configs 4 and 5")
+    ap.add_argument("--routing", default="uniform", choices=["uniform", "zipf"])
     args = ap.parse_args()
     global LAYERS
     LAYERS = args.layers
@@ -376,7 +498,7 @@ def main():
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (torchrun --nproc-per-node {args.gpus}); "
                          f"WORLD_SIZE is {world}")
-    run_gpu(args, rank, world)
+    (run_gpu if args.workload == "c2" else run_gpu_moe)(args, rank, world)
     if world > 1:
         import torch.distributed as dist
 

@@ -417,7 +417,8 @@ static int fill_moe(MoeDev* d, const DlmMoe* m) {
     d->y = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(m->workspace) + kWorkspaceHeader);
     d->m = m->m, d->n = m->n, d->f = m->f, d->top_k = m->top_k, d->m_max = m->m_max;
     d->lo = m->lo, d->e_local = m->e_local, d->e_total = m->e_total;
-    d->rows_cap = (m->m_max + 31) / 32 * 32;
+    d->rows_cap = (m->m_max + 31) / 32 * 32;  // activation rows of one work item: at most 128
+    if (d->rows_cap > 128) d->rows_cap = 128;
     d->stages = moe_stages(d->rows_cap);
     return DLM_OK;
 }

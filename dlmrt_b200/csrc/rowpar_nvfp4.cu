@@ -31,25 +31,28 @@ constexpr int kCodeTileW = 128 * 128;  // 128 rows x 128 bytes (256 FP4) of W2 c
 constexpr int kBoxRows = 32;           // activation rows per TMA box
 constexpr int kAtom = 512;             // one 128-row x 4-scale atom
 constexpr int kStepsPerBlock = 4;      // K = 64 instructions per 256-element k-block
-constexpr int kTmemAcc = 0, kTmemSfa = 256, kTmemSfb = 272, kTmemCols = 512;
+constexpr int kItemRows = 128;         // rows of one work item: the MMA's N; experts with more rows take several items
+constexpr int kTmemAcc = 0, kTmemSfa = 256, kTmemSfb = 272, kTmemCols = 512;  // two 128-column accumulators, then scales
 constexpr int kMaxLocalExperts = 256;
+constexpr int kMaxEntries = 2 * kMaxLocalExperts;  // (expert, row block) pairs: m_max <= 256 gives at most two blocks
 
 struct MoeSmem {
     uint64_t full[kMaxStages];
     uint64_t empty[kMaxStages];
-    uint64_t acc_full;
-    uint64_t acc_empty;
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
     uint32_t tmem_base;
     int n_active, epoch, gen;
     int warp_count[8];
     float scratch[32];
-    short active[kMaxLocalExperts];
+    short active[kMaxEntries];  // expert | row block << 8
+    short rows[kMaxEntries];    // rows of that block
 };
 
 }  // namespace
 
-int moe_stage_bytes(int rows_cap) {
-    return kCodeTileW + rows_cap * 128 + kStepsPerBlock * kAtom + kStepsPerBlock * ((rows_cap + 127) / 128) * kAtom;
+int moe_stage_bytes(int rows_cap) {  // rows_cap: rows of one item's activation tile (a multiple of 32, <= 128)
+    return kCodeTileW + rows_cap * 128 + 2 * kStepsPerBlock * kAtom;
 }
 
 int moe_stages(int rows_cap) {
@@ -66,8 +69,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int block = static_cast<int>(blockIdx.x), blocks = static_cast<int>(gridDim.x);
 
-    const int atoms = (g.rows_cap + 127) / 128;  // activation scale atoms per K = 64 step
-    const int stage_bytes = kCodeTileW + g.rows_cap * 128 + kStepsPerBlock * kAtom + kStepsPerBlock * atoms * kAtom;
+    const int stage_bytes = kCodeTileW + g.rows_cap * 128 + 2 * kStepsPerBlock * kAtom;
     const int off_a = kCodeTileW, off_sfa = off_a + g.rows_cap * 128, off_sfb = off_sfa + kStepsPerBlock * kAtom;
     const int feature_tiles = g.n / kBlockF;
     const int steps = g.f / 64;                  // K = 64 instructions per item
@@ -79,11 +81,13 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < g.stages; ++i) {
-            mbar_init(&sm->full[i], 2);  // the TMA producer's expect_tx arrival and the scale loader's arrival
+            mbar_init(&sm->full[i], 33);  // the TMA producer's expect_tx arrival and the scale loader's 32 lanes
             mbar_init(&sm->empty[i], 1);
         }
-        mbar_init(&sm->acc_full, 1);
-        mbar_init(&sm->acc_empty, 8);    // one arrival per epilogue warp
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&sm->acc_full[i], 1);
+            mbar_init(&sm->acc_empty[i], 8);  // one arrival per epilogue warp
+        }
         fence_barrier_init();
         tma_prefetch_descriptor(&g.tm_w);
         tma_prefetch_descriptor(&g.tm_a);
@@ -92,19 +96,28 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
     // Routing (counts, slots, activations) comes from the previous kernels of the stream: nothing of it may be read
     // before they are complete.
     pdl_wait();
-    // Compact list of this rank's experts that have rows, in expert order.
+    // Compact list of (expert, block of 128 rows) pairs that have rows, in expert order.
     {
         const int e = threadIdx.x;
-        const bool has = e < g.e_local && g.counts[g.lo + e] > 0;
-        const unsigned ballot = __ballot_sync(0xffffffff, has);
-        if (warp < 8 && lane == 0) sm->warp_count[warp] = __popc(ballot);
+        const int nb = e < g.e_local ? (min(g.counts[g.lo + e], g.m_max) + kItemRows - 1) / kItemRows : 0;
+        int incl = nb;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffff, incl, o);
+            if (lane >= o) incl += up;
+        }
+        if (warp < 8 && lane == 31) sm->warp_count[warp] = incl;
         tcgen05_fence_before();
         __syncthreads();
         tcgen05_fence_after();
         if (warp < 8) {
             int base = 0;
             for (int wv = 0; wv < warp; ++wv) base += sm->warp_count[wv];
-            if (has) sm->active[base + __popc(ballot & ((1u << lane) - 1))] = static_cast<short>(e);
+            const int total_rows = nb ? min(g.counts[g.lo + e], g.m_max) : 0;
+            for (int j = 0; j < nb; ++j) {
+                sm->active[base + incl - nb + j] = static_cast<short>(e | (j << 8));
+                sm->rows[base + incl - nb + j] = static_cast<short>(min(total_rows - j * kItemRows, kItemRows));
+            }
             if (threadIdx.x == 0) {
                 int total = 0;
                 for (int wv = 0; wv < 8; ++wv) total += sm->warp_count[wv];
@@ -121,13 +134,24 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
     const int n_items = sm->n_active * feature_tiles;
     const long long deadline = globaltimer() + (c.timeout_ns > 0 ? c.timeout_ns : 2000000000ll);
 
+    // An item: entry (expert e, row block rb) x feature tile ft; `cnt` rows of the expert starting at row0.
+    struct Item {
+        int e, ft, row0, cnt;
+    };
+    auto item_of = [&](int i) {
+        const int entry = sm->active[i / feature_tiles];
+        Item t;
+        t.e = entry & 0xFF, t.ft = i % feature_tiles, t.row0 = (entry >> 8) * kItemRows;
+        t.cnt = sm->rows[i / feature_tiles];
+        return t;
+    };
+
     if (warp == 0) {
         if (lane == 0) {
             int it = 0;
             for (int i = block; i < n_items; i += blocks) {
-                const int e = sm->active[i / feature_tiles], ft = i % feature_tiles;
-                const int cnt = min(g.counts[g.lo + e], g.rows_cap);
-                const int boxes = (cnt + kBoxRows - 1) / kBoxRows;
+                const Item t = item_of(i);
+                const int boxes = (t.cnt + kBoxRows - 1) / kBoxRows;
                 for (int kb = 0; kb < nkb; ++kb, ++it) {
                     const int st = it % g.stages;
                     if (it >= g.stages && !mbar_wait(&sm->empty[st], ((it / g.stages) & 1) ^ 1, deadline)) {
@@ -137,21 +161,21 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
                     }
                     uint8_t* stage = tiles + st * stage_bytes;
                     mbar_expect_tx(&sm->full[st], static_cast<uint32_t>(kCodeTileW + boxes * kBoxRows * 128));
-                    tma_load_2d(stage, &g.tm_w, &sm->full[st], kb * 128, e * g.n + ft * kBlockF, kEvictFirst);
+                    tma_load_2d(stage, &g.tm_w, &sm->full[st], kb * 128, t.e * g.n + t.ft * kBlockF, kEvictFirst);
                     for (int b = 0; b < boxes; ++b)
                         tma_load_2d(stage + off_a + b * kBoxRows * 128, &g.tm_a, &sm->full[st], kb * 128,
-                                    e * g.m_max + b * kBoxRows, kEvictLast);
+                                    t.e * g.m_max + t.row0 + b * kBoxRows, kEvictLast);
                 }
             }
         }
     } else if (warp == 3) {
-        // Scale loader. Atom byte (r % 32) * 16 + ((r % 128) / 32) * 4 + j holds scale j of row r.
-        const int total_slots = g.e_local * g.m_max;
+        // Scale loader: asynchronous copies straight into the atoms, so it never waits for data and runs as far ahead
+        // as the ring allows. Atom byte (r % 32) * 16 + (r / 32) * 4 + j holds scale j of row r (< 128).
+        const int last_slot = g.e_local * g.m_max - 1;
         int it = 0;
         for (int i = block; i < n_items; i += blocks) {
-            const int e = sm->active[i / feature_tiles], ft = i % feature_tiles;
-            const int cnt = min(g.counts[g.lo + e], g.rows_cap);
-            const int rows = ((cnt + kBoxRows - 1) / kBoxRows) * kBoxRows;
+            const Item t = item_of(i);
+            const int rows = ((t.cnt + kBoxRows - 1) / kBoxRows) * kBoxRows;
             bool alive = true;
             for (int kb = 0; kb < nkb; ++kb, ++it) {
                 const int st = it % g.stages;
@@ -161,21 +185,17 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
                 }
                 uint8_t* stage = tiles + st * stage_bytes;
                 const int nsteps = min(kStepsPerBlock, steps - kb * kStepsPerBlock);
-                const uint4* wsrc = reinterpret_cast<const uint4*>(
-                    g.w_scales + (static_cast<size_t>(e * feature_tiles + ft) * steps + kb * kStepsPerBlock) * kAtom);
-                uint4* wdst = reinterpret_cast<uint4*>(stage + off_sfa);
-                for (int v = lane; v < nsteps * (kAtom / 16); v += 32) wdst[v] = __ldg(wsrc + v);
+                const uint8_t* wsrc =
+                    g.w_scales + (static_cast<size_t>(t.e * feature_tiles + t.ft) * steps + kb * kStepsPerBlock) * kAtom;
+                for (int v = lane; v < nsteps * (kAtom / 16); v += 32) cp_async_16(stage + off_sfa + v * 16, wsrc + v * 16);
                 for (int r = lane; r < rows; r += 32) {
-                    const int srow = e * g.m_max + r;
-                    const uint32_t* src = reinterpret_cast<const uint32_t*>(
-                        g.a_scales + static_cast<size_t>(srow) * scale_row + kb * kStepsPerBlock * 4);
-                    uint8_t* dst = stage + off_sfb + (r / 128) * kAtom + (r % 32) * 16 + ((r % 128) / 32) * 4;
-                    for (int s = 0; s < nsteps; ++s)
-                        *reinterpret_cast<uint32_t*>(dst + s * atoms * kAtom) = srow < total_slots ? __ldcg(src + s) : 0u;
+                    // Rows past the expert's count are padding: any readable scale will do for them.
+                    const int srow = min(t.e * g.m_max + t.row0 + r, last_slot);
+                    const uint8_t* src = g.a_scales + static_cast<size_t>(srow) * scale_row + kb * kStepsPerBlock * 4;
+                    uint8_t* dst = stage + off_sfb + (r % 32) * 16 + (r / 32) * 4;
+                    for (int s2 = 0; s2 < nsteps; ++s2) cp_async_4(dst + s2 * kAtom, src + s2 * 4);
                 }
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sm->full[st]);
+                cp_async_arrive(&sm->full[st]);
             }
             if (!alive) break;
         }
@@ -183,13 +203,14 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
         if (lane == 0) {
             int it = 0, item = 0;
             for (int i = block; i < n_items; i += blocks, ++item) {
-                const int e = sm->active[i / feature_tiles];
-                const int cnt = min(g.counts[g.lo + e], g.rows_cap);
-                const int n_mma = max(16, (cnt + 15) & ~15);
+                const Item t = item_of(i);
+                const int n_mma = max(16, (t.cnt + 15) & ~15);
                 const uint32_t idesc = umma_idesc_nvfp4(kBlockF, n_mma);
+                const int buf = item & 1;
+                const uint32_t acc = tmem + kTmemAcc + buf * kItemRows;
                 bool alive = true;
-                // The accumulator of the previous item must have been read out.
-                if (item > 0 && !mbar_wait(&sm->acc_empty, (item - 1) & 1, deadline)) {
+                // The accumulator buffer must have been read out by the epilogue of two items ago.
+                if (item >= 2 && !mbar_wait(&sm->acc_empty[buf], ((item >> 1) - 1) & 1, deadline)) {
                     report(c.status, kErrTimeout, 0, kPhasePipeline, 4);
                     break;
                 }
@@ -201,21 +222,21 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
                         alive = false;
                         break;
                     }
+                    fence_proxy_async();  // the scale atoms were written through the generic proxy
                     tcgen05_fence_after();
                     uint8_t* stage = tiles + st * stage_bytes;
                     const int nsteps = min(kStepsPerBlock, steps - kb * kStepsPerBlock);
-                    for (int s = 0; s < nsteps; ++s) {
-                        utccp_128x4(tmem + kTmemSfa + 4 * s, utccp_desc(stage + off_sfa + s * kAtom));
-                        for (int a = 0; a * 128 < n_mma; ++a)
-                            utccp_128x4(tmem + kTmemSfb + 8 * s + 4 * a, utccp_desc(stage + off_sfb + (s * atoms + a) * kAtom));
+                    for (int s2 = 0; s2 < nsteps; ++s2) {
+                        utccp_128x4(tmem + kTmemSfa + 4 * s2, utccp_desc(stage + off_sfa + s2 * kAtom));
+                        utccp_128x4(tmem + kTmemSfb + 4 * s2, utccp_desc(stage + off_sfb + s2 * kAtom));
                     }
                     const uint64_t dw = umma_desc_k128(stage), da = umma_desc_k128(stage + off_a);
-                    for (int s = 0; s < nsteps; ++s)
-                        umma_nvfp4(tmem + kTmemAcc, dw + 2 * s, da + 2 * s, idesc, tmem + kTmemSfa + 4 * s,
-                                   tmem + kTmemSfb + 8 * s, (kb | s) != 0);
+                    for (int s2 = 0; s2 < nsteps; ++s2)
+                        umma_nvfp4(acc, dw + 2 * s2, da + 2 * s2, idesc, tmem + kTmemSfa + 4 * s2, tmem + kTmemSfb + 4 * s2,
+                                   (kb | s2) != 0);
                     umma_commit(&sm->empty[st]);
                 }
-                umma_commit(&sm->acc_full);
+                umma_commit(&sm->acc_full[buf]);
                 if (!alive) break;
             }
         }
@@ -224,29 +245,41 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
         const int quarter = warp & 3, half = (warp - 4) >> 2;
         int item = 0;
         for (int i = block; i < n_items; i += blocks, ++item) {
-            const int e = sm->active[i / feature_tiles], ft = i % feature_tiles;
-            const int cnt = min(g.counts[g.lo + e], g.rows_cap);
-            const int n_mma = max(16, (cnt + 15) & ~15);
-            const float g2 = g.g2[e];
-            const int* slots = g.amap + static_cast<size_t>(g.lo + e) * g.m_max;
-            const bool ok = mbar_wait(&sm->acc_full, item & 1, deadline);
+            const Item t = item_of(i);
+            const int n_mma = max(16, (t.cnt + 15) & ~15);
+            const int buf = item & 1;
+            // Issued before the wait so that their latency overlaps the item's MMAs: the expert's scale and, for each
+            // of this warp's 16-row chunks (at most four), the destination row of lane % 16's accumulator column.
+            const float g2 = g.g2[t.e];
+            const int* slots = g.amap + static_cast<size_t>(g.lo + t.e) * g.m_max + t.row0;
+            int dest[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int row = (half + 2 * q) * 16 + (lane & 15);
+                dest[q] = row < t.cnt ? slots[row] : -1;
+            }
+            const bool ok = mbar_wait(&sm->acc_full[buf], (item >> 1) & 1, deadline);
             if (!ok) report(c.status, kErrTimeout, 0, kPhasePipeline, 2);
             tcgen05_fence_after();
-            const int col = ft * kBlockF + quarter * 32 + lane;
-            for (int chunk = half; chunk < n_mma / 16 && ok; chunk += 2) {
-                uint32_t r[16];
-                tmem_load_16(tmem + kTmemAcc + (static_cast<uint32_t>(quarter * 32) << 16) + chunk * 16, r);
-                tmem_load_wait();
+            const int col = t.ft * kBlockF + quarter * 32 + lane;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int row = chunk * 16 + j;
-                    if (row < cnt)
-                        g.y[static_cast<size_t>(slots[row]) * g.n + col] = __float2bfloat16_rn(__uint_as_float(r[j]) * g2);
+            for (int q = 0; q < 4; ++q) {
+                const int chunk = half + 2 * q;
+                if (chunk < n_mma / 16 && ok) {
+                    uint32_t r[16];
+                    tmem_load_16(tmem + kTmemAcc + buf * kItemRows + (static_cast<uint32_t>(quarter * 32) << 16) + chunk * 16, r);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int pair = __shfl_sync(0xffffffff, dest[q], j);
+                        if (pair >= 0)
+                            g.y[static_cast<size_t>(pair) * g.n + col] = __float2bfloat16_rn(__uint_as_float(r[j]) * g2);
+                    }
                 }
             }
             tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&sm->acc_empty);
+            if (lane == 0) mbar_arrive(&sm->acc_empty[buf]);
             if (!ok) break;
         }
     }

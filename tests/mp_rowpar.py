@@ -78,6 +78,19 @@ def main():
             assert_same_bits(bits(out), want, f"fused {i}.{rep}")
             for r, other in enumerate(gather(out)):
                 assert_same_bits(bits(other), bits(out), f"fused {i}.{rep}: rank {r} vs rank {rank}")
+    # NVFP4 experts split whole across the ranks (expert parallel), exact operands: bit-exact end to end
+    from test_moe_gpu import device_args, make_case, oracle_out
+    from dlmrt_b200.quantization import nvfp4
+
+    case = make_case(32, 2048, 512, 64, 8, seed=11, exact=True)
+    e_local = 64 // world
+    args = device_args(case, rank * e_local, e_local, dev)
+    want = red.reduce(np.stack([oracle_out(case, r * e_local, e_local)[0] for r in range(world)]))
+    for rep in range(3):
+        out = nvfp4.moe_down(out=None, group=group, site=f"moe.{rep % 2}", chain=32, **args)
+        torch.cuda.synchronize()
+        group.check()
+        assert_same_bits(bits(out), want, f"moe {rep}")
     dist.barrier()
     if rank == 0:
         print(f"MULTIGPU_OK world={world} multicast={report['multicast']}")

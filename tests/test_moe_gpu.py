@@ -86,7 +86,8 @@ def run_single(case, shared=None):
 
 
 @pytest.mark.parametrize("rows, hidden, f, e_total, top_k", [(32, 2048, 512, 16, 4), (32, 2048, 512, 256, 8),
-                                                            (64, 256, 704, 8, 2), (256, 2816, 704, 32, 8)])
+                                                            (64, 256, 704, 8, 2), (256, 2816, 704, 32, 8),
+                                                            (256, 256, 512, 8, 8), (160, 512, 704, 4, 3)])
 def test_exact_operands_match_bit_for_bit(rows, hidden, f, e_total, top_k):
     case = make_case(rows, hidden, f, e_total, top_k, seed=rows + f, exact=True)
     want, _ = oracle_out(case, 0, e_total)
