@@ -14,7 +14,10 @@ OK, ERR_SHAPE, ERR_ALIGN, ERR_WORLD, ERR_NULL, ERR_GRID, ERR_CUDA, ERR_WORKSPACE
     ERR_SCRATCH = 0, -1, -2, -3, -4, -5, -6, -7, -8, -9, -10
 REDUCE, REDUCE_NORM, REDUCE_NORM_RESIDUAL = 0, 1, 2
 
-LIB_PATH = Path(__file__).resolve().parent / "libdlmrt_b200.so"
+import os
+
+# DLMRT_B200_LIB points at another build of the same library (kernel experiments); the default is the in-tree build.
+LIB_PATH = Path(os.environ.get("DLMRT_B200_LIB") or Path(__file__).resolve().parent / "libdlmrt_b200.so")
 
 
 class DlmComm(C.Structure):

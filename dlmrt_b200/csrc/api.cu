@@ -406,7 +406,7 @@ static int make_map_u8(CUtensorMap* map, const void* base, long long rows, int r
 static int fill_moe(MoeDev* d, const DlmMoe* m) {
     std::memset(d, 0, sizeof(*d));
     int rc = make_map_u8(&d->tm_w, m->w_codes, static_cast<long long>(m->e_local) * m->n, m->f / 2, kBlockF);
-    if (rc == DLM_OK) rc = make_map_u8(&d->tm_a, m->act_codes, static_cast<long long>(m->e_local) * m->m_max, m->f / 2, 32);
+    if (rc == DLM_OK) rc = make_map_u8(&d->tm_a, m->act_codes, static_cast<long long>(m->e_local) * m->m_max, m->f / 2, 8);
     if (rc != DLM_OK) return rc;
     d->a_scales = static_cast<const uint8_t*>(m->act_scales);
     d->w_scales = static_cast<const uint8_t*>(m->w_scales);
@@ -417,7 +417,7 @@ static int fill_moe(MoeDev* d, const DlmMoe* m) {
     d->y = reinterpret_cast<__nv_bfloat16*>(static_cast<char*>(m->workspace) + kWorkspaceHeader);
     d->m = m->m, d->n = m->n, d->f = m->f, d->top_k = m->top_k, d->m_max = m->m_max;
     d->lo = m->lo, d->e_local = m->e_local, d->e_total = m->e_total;
-    d->rows_cap = (m->m_max + 31) / 32 * 32;  // activation rows of one work item: at most 128
+    d->rows_cap = (m->m_max + 15) / 16 * 16;  // activation rows of one work item: at most 128
     if (d->rows_cap > 128) d->rows_cap = 128;
     d->stages = moe_stages(d->rows_cap);
     return DLM_OK;

@@ -17,7 +17,7 @@ constexpr uint32_t kSentinel = 0xFFFFFFFFu; // two armed BF16 lanes (0xFFFF: a n
 // ---------------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ long long globaltimer() {
     long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");  // ordered with barriers and memory operations
     return t;
 }
 

@@ -115,6 +115,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
                             token0, kEvictLast);
             }
         }
+        __syncwarp();  // lanes 1-31 must not run ahead to the block-wide barrier while lane 0 is still issuing
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_bf16(kBlockF, mt);
@@ -137,12 +138,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
             }
             umma_commit(&sm->acc_full);
         }
+        __syncwarp();
     } else if (warp == 3) {
         if (lane == 0) {
             pdl_wait();
             if (p.fused) sm->epoch = c.epochs[block];
             if (g.splits > 1) sm->gen = g.gen[block];
         }
+        __syncwarp();
     } else if (warp >= 4) {
         // Epilogue: thread `lane` of a warp holds feature 32 * quarter + lane; 16 token columns per tcgen05.ld.
         const int quarter = warp & 3, half = (warp - 4) >> 2;

@@ -12,7 +12,7 @@
 //
 // Work item = (active local expert, 128 output features): W2's [128 x F] slab sits on the MMA's M axis, the expert's
 // rows (tokens routed to it, padded to 16) on its N axis. Persistent CTAs take items round-robin:
-//   warp 0   TMA: per 256-element k-block the 16 KB code slab of W2 and the expert's activation rows (boxes of 32 rows)
+//   warp 0   TMA: per 256-element k-block the 16 KB code slab of W2 and the expert's activation rows (boxes of 8 rows)
 //   warp 3   scale loader: W2's pre-interleaved 128 x 4 scale atoms and the activation rows' linear E4M3 scales,
 //            rewritten into the same atom layout, into the stage
 //   warp 1   per k-block: tcgen05.cp the scale atoms into tensor memory, then up to four
@@ -28,11 +28,13 @@ namespace {
 
 constexpr int kMoeThreads = kFusedThreads;
 constexpr int kCodeTileW = 128 * 128;  // 128 rows x 128 bytes (256 FP4) of W2 codes
-constexpr int kBoxRows = 32;           // activation rows per TMA box
+constexpr int kBoxRows = 8;            // activation rows per TMA box (one 1 KB swizzle atom)
 constexpr int kAtom = 512;             // one 128-row x 4-scale atom
 constexpr int kStepsPerBlock = 4;      // K = 64 instructions per 256-element k-block
 constexpr int kItemRows = 128;         // rows of one work item: the MMA's N; experts with more rows take several items
-constexpr int kTmemAcc = 0, kTmemSfa = 256, kTmemSfb = 272, kTmemCols = 512;  // two 128-column accumulators, then scales
+constexpr int kTmemAcc = 0, kTmemSfa = 256, kTmemSfb = 384, kTmemCols = 512;  // two 128-column accumulators, then scales
+constexpr int kSfSets = 4;             // scale columns rotate over four sets, so copying a k-block's scales in does not
+                                       // have to wait for the previous k-block's MMAs to finish reading theirs
 constexpr int kMaxLocalExperts = 256;
 constexpr int kMaxEntries = 2 * kMaxLocalExperts;  // (expert, row block) pairs: m_max <= 256 gives at most two blocks
 
@@ -68,6 +70,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
     const CommDev& c = p.c[slot];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int block = static_cast<int>(blockIdx.x), blocks = static_cast<int>(gridDim.x);
+    if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 7] = globaltimer();
 
     const int stage_bytes = kCodeTileW + g.rows_cap * 128 + 2 * kStepsPerBlock * kAtom;
     const int off_a = kCodeTileW, off_sfa = off_a + g.rows_cap * 128, off_sfb = off_sfa + kStepsPerBlock * kAtom;
@@ -99,7 +102,11 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
     // Compact list of (expert, block of 128 rows) pairs that have rows, in expert order.
     {
         const int e = threadIdx.x;
-        const int nb = e < g.e_local ? (min(g.counts[g.lo + e], g.m_max) + kItemRows - 1) / kItemRows : 0;
+        const int total_rows = e < g.e_local ? min(g.counts[g.lo + e], g.m_max) : 0;
+        int early = 0;  // the invocation counters, fetched in the same round trip as the counts
+        if (threadIdx.x == 352 && p.fused) early = c.epochs[block];
+        if (threadIdx.x == 353) early = g.gen[block];
+        const int nb = (total_rows + kItemRows - 1) / kItemRows;
         int incl = nb;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -113,7 +120,6 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
         if (warp < 8) {
             int base = 0;
             for (int wv = 0; wv < warp; ++wv) base += sm->warp_count[wv];
-            const int total_rows = nb ? min(g.counts[g.lo + e], g.m_max) : 0;
             for (int j = 0; j < nb; ++j) {
                 sm->active[base + incl - nb + j] = static_cast<short>(e | (j << 8));
                 sm->rows[base + incl - nb + j] = static_cast<short>(min(total_rows - j * kItemRows, kItemRows));
@@ -124,12 +130,11 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
                 sm->n_active = total;
             }
         }
-        if (threadIdx.x == 96) {
-            if (p.fused) sm->epoch = c.epochs[block];
-            sm->gen = g.gen[block];
-        }
+        if (threadIdx.x == 352) sm->epoch = early;
+        if (threadIdx.x == 353) sm->gen = early;
         __syncthreads();
     }
+    if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 0] = globaltimer();
     const uint32_t tmem = sm->tmem_base;
     const int n_items = sm->n_active * feature_tiles;
     const long long deadline = globaltimer() + (c.timeout_ns > 0 ? c.timeout_ns : 2000000000ll);
@@ -148,13 +153,13 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
 
     if (warp == 0) {
         if (lane == 0) {
-            int it = 0;
+            int st = 0;
+            uint32_t phase = 1;  // waiting for parity 1 on a fresh barrier returns at once: the first lap is free
             for (int i = block; i < n_items; i += blocks) {
                 const Item t = item_of(i);
                 const int boxes = (t.cnt + kBoxRows - 1) / kBoxRows;
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
-                    const int st = it % g.stages;
-                    if (it >= g.stages && !mbar_wait(&sm->empty[st], ((it / g.stages) & 1) ^ 1, deadline)) {
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!mbar_wait(&sm->empty[st], phase, deadline)) {
                         report(c.status, kErrTimeout, st, kPhasePipeline, 0);
                         i = n_items;
                         break;
@@ -165,21 +170,23 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
                     for (int b = 0; b < boxes; ++b)
                         tma_load_2d(stage + off_a + b * kBoxRows * 128, &g.tm_a, &sm->full[st], kb * 128,
                                     t.e * g.m_max + t.row0 + b * kBoxRows, kEvictLast);
+                    if (++st == g.stages) st = 0, phase ^= 1;
                 }
             }
         }
+        __syncwarp();  // lanes 1-31 must not run ahead to the block-wide barrier while lane 0 is still issuing
     } else if (warp == 3) {
         // Scale loader: asynchronous copies straight into the atoms, so it never waits for data and runs as far ahead
         // as the ring allows. Atom byte (r % 32) * 16 + (r / 32) * 4 + j holds scale j of row r (< 128).
         const int last_slot = g.e_local * g.m_max - 1;
-        int it = 0;
+        int st = 0;
+        uint32_t phase = 1;
         for (int i = block; i < n_items; i += blocks) {
             const Item t = item_of(i);
-            const int rows = ((t.cnt + kBoxRows - 1) / kBoxRows) * kBoxRows;
+            const int rows = (t.cnt + 15) & ~15;  // the MMA reads scales of all its N rows
             bool alive = true;
-            for (int kb = 0; kb < nkb; ++kb, ++it) {
-                const int st = it % g.stages;
-                if (it >= g.stages && !mbar_wait(&sm->empty[st], ((it / g.stages) & 1) ^ 1, deadline)) {
+            for (int kb = 0; kb < nkb; ++kb) {
+                if (!mbar_wait(&sm->empty[st], phase, deadline)) {
                     alive = false;
                     break;
                 }
@@ -196,50 +203,69 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
                     for (int s2 = 0; s2 < nsteps; ++s2) cp_async_4(dst + s2 * kAtom, src + s2 * 4);
                 }
                 cp_async_arrive(&sm->full[st]);
+                if (++st == g.stages) st = 0, phase ^= 1;
             }
             if (!alive) break;
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            int it = 0, item = 0;
-            for (int i = block; i < n_items; i += blocks, ++item) {
-                const Item t = item_of(i);
-                const int n_mma = max(16, (t.cnt + 15) & ~15);
-                const uint32_t idesc = umma_idesc_nvfp4(kBlockF, n_mma);
+            // One thread feeds the tensor pipe, so its own instruction count per k-block matters: ring position, phase
+            // and scale-column set advance by increments (no divisions), descriptors differ by constants.
+            const uint32_t stage0 = smem_u32(tiles);
+            const uint64_t desc_hi = umma_desc_k128(tiles) & 0xFFFFFFFF00000000ull;     // swizzled operand tiles
+            const uint64_t sf_hi = utccp_desc(tiles) & 0xFFFFFFFF00000000ull;           // scale atoms
+            int st = 0, set = 0, item = 0;
+            uint32_t phase = 0;
+            bool alive = true;
+            for (int i = block; i < n_items && alive; i += blocks, ++item) {
+                const int cnt = sm->rows[i / feature_tiles];
+                const uint32_t idesc = umma_idesc_nvfp4(kBlockF, max(16, (cnt + 15) & ~15));
                 const int buf = item & 1;
                 const uint32_t acc = tmem + kTmemAcc + buf * kItemRows;
-                bool alive = true;
                 // The accumulator buffer must have been read out by the epilogue of two items ago.
                 if (item >= 2 && !mbar_wait(&sm->acc_empty[buf], ((item >> 1) - 1) & 1, deadline)) {
                     report(c.status, kErrTimeout, 0, kPhasePipeline, 4);
                     break;
                 }
-                tcgen05_fence_after();
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
-                    const int st = it % g.stages;
-                    if (!mbar_wait(&sm->full[st], (it / g.stages) & 1, deadline)) {
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!mbar_wait(&sm->full[st], phase, deadline)) {
                         report(c.status, kErrTimeout, st, kPhasePipeline, 1);
                         alive = false;
                         break;
                     }
                     fence_proxy_async();  // the scale atoms were written through the generic proxy
                     tcgen05_fence_after();
-                    uint8_t* stage = tiles + st * stage_bytes;
+                    const uint32_t base = stage0 + st * stage_bytes;
+                    const uint64_t dw = desc_hi | ((base & 0x3FFFF) >> 4), da = desc_hi | (((base + off_a) & 0x3FFFF) >> 4);
+                    const uint64_t fa = sf_hi | (((base + off_sfa) & 0x3FFFF) >> 4), fb = sf_hi | (((base + off_sfb) & 0x3FFFF) >> 4);
+                    const uint32_t sfa = tmem + kTmemSfa + set * 4 * kStepsPerBlock;
+                    const uint32_t sfb = tmem + kTmemSfb + set * 4 * kStepsPerBlock;
                     const int nsteps = min(kStepsPerBlock, steps - kb * kStepsPerBlock);
-                    for (int s2 = 0; s2 < nsteps; ++s2) {
-                        utccp_128x4(tmem + kTmemSfa + 4 * s2, utccp_desc(stage + off_sfa + s2 * kAtom));
-                        utccp_128x4(tmem + kTmemSfb + 4 * s2, utccp_desc(stage + off_sfb + s2 * kAtom));
+                    if (nsteps == kStepsPerBlock) {
+#pragma unroll
+                        for (int s2 = 0; s2 < kStepsPerBlock; ++s2) {
+                            utccp_128x4(sfa + 4 * s2, fa + s2 * (kAtom >> 4));
+                            utccp_128x4(sfb + 4 * s2, fb + s2 * (kAtom >> 4));
+                        }
+#pragma unroll
+                        for (int s2 = 0; s2 < kStepsPerBlock; ++s2)
+                            umma_nvfp4(acc, dw + 2 * s2, da + 2 * s2, idesc, sfa + 4 * s2, sfb + 4 * s2, (kb | s2) != 0);
+                    } else {
+                        for (int s2 = 0; s2 < nsteps; ++s2) {
+                            utccp_128x4(sfa + 4 * s2, fa + s2 * (kAtom >> 4));
+                            utccp_128x4(sfb + 4 * s2, fb + s2 * (kAtom >> 4));
+                        }
+                        for (int s2 = 0; s2 < nsteps; ++s2)
+                            umma_nvfp4(acc, dw + 2 * s2, da + 2 * s2, idesc, sfa + 4 * s2, sfb + 4 * s2, (kb | s2) != 0);
                     }
-                    const uint64_t dw = umma_desc_k128(stage), da = umma_desc_k128(stage + off_a);
-                    for (int s2 = 0; s2 < nsteps; ++s2)
-                        umma_nvfp4(acc, dw + 2 * s2, da + 2 * s2, idesc, tmem + kTmemSfa + 4 * s2, tmem + kTmemSfb + 4 * s2,
-                                   (kb | s2) != 0);
                     umma_commit(&sm->empty[st]);
+                    set = (set + 1) & (kSfSets - 1);
+                    if (++st == g.stages) st = 0, phase ^= 1;
                 }
-                umma_commit(&sm->acc_full[buf]);
-                if (!alive) break;
+                if (alive) umma_commit(&sm->acc_full[buf]);
             }
         }
+        __syncwarp();
     } else if (warp >= 4) {
         // Epilogue: lane = output feature of the tile, registers = the expert's rows. Scatter through the slot map.
         const int quarter = warp & 3, half = (warp - 4) >> 2;
@@ -285,34 +311,51 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
     }
     // Every Y row this CTA produced is written; announce it and wait for the rest of the grid (the combine reads rows
     // written by other CTAs). Counters are banked by launch generation as in the BF16 kernel.
+#ifdef DLM_STAMP16
+    if (c.stamps && lane == 0) c.stamps[block * kStampSlots + 11 + (warp == 0 ? 0 : warp == 1 ? 1 : warp == 3 ? 2 : warp == 4 ? 3 : 4)] = globaltimer();
+#endif
     __threadfence();
     tcgen05_fence_before();
     __syncthreads();
+    if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 4] = globaltimer();
     if (warp == 2) {
         tcgen05_fence_after();
         tmem_dealloc(tmem, kTmemCols);
+#ifdef DLM_STAMP16
+        if (c.stamps && lane == 0) c.stamps[block * kStampSlots + 8] = globaltimer();
+#endif
     }
     CommCtx x{};
     if (p.fused) x = comm_begin(c, block, blocks, sm->epoch);
+#ifdef DLM_STAMP16
+    if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 9] = globaltimer();
+#endif
     {
         const int gen = sm->gen + 1;
         int* counter = g.counters + (gen & 1) * kMaxTiles;
         if (threadIdx.x == 0) {
             if (block == 0) g.counters[((gen + 1) & 1) * kMaxTiles] = 0;
             atomicAdd(counter, 1);
-            int seen;
-            do {
+            // Only CTAs that have output rows to combine need the others' Y rows; polling is paced so that the
+            // arrivals of the rest of the grid are not queued behind a storm of loads on the same word.
+            while (block < g.m) {
+                int seen;
                 asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
                 if (seen >= blocks) break;
                 if (globaltimer() > deadline) {
                     report(c.status, kErrTimeout, 0, kPhasePipeline, 3);
                     break;
                 }
-            } while (true);
+                __nanosleep(100);
+            }
             for (int j = block; j < kEpochSlots; j += blocks) g.gen[j] = gen;
+#ifdef DLM_STAMP16
+            if (c.stamps) c.stamps[block * kStampSlots + 10] = globaltimer();
+#endif
         }
         __syncthreads();
     }
+    if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 5] = globaltimer();
     // Combine: out[row] = bf16(sum over k in list order of w_k * y_k), experts of other ranks contribute 0 * 0.
     {
         const int t = threadIdx.x, threads = g.n / kVec;
