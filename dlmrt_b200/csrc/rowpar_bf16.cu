@@ -101,40 +101,43 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
             for (int it = 0; it < pre; ++it)
                 tma_load_2d(tiles + it * stage_bytes + kTileBytesW, &g.tm_x, &sm->full[it], (kb0 + it) * kBlockK,
                             token0, kEvictLast);
+            int st = pre == g.stages ? 0 : pre;
+            uint32_t parity = 0;  // second lap of the ring waits for the first release of each stage
             for (int it = pre; it < iters; ++it) {
-                const int st = it % g.stages;
-                const uint32_t parity = ((it / g.stages) & 1) ^ 1;
                 if (!mbar_wait(&sm->empty[st], parity, pipeline_deadline)) {
                     report(c.status, kErrTimeout, st, kPhasePipeline, 0);
                     break;
                 }
+                uint8_t* stage = tiles + st * stage_bytes;
                 mbar_expect_tx(&sm->full[st], static_cast<uint32_t>(stage_bytes));
-                tma_load_2d(tiles + st * stage_bytes, &g.tm_w, &sm->full[st], (kb0 + it) * kBlockK, f * kBlockF,
-                            kEvictFirst);
-                tma_load_2d(tiles + st * stage_bytes + kTileBytesW, &g.tm_x, &sm->full[st], (kb0 + it) * kBlockK,
-                            token0, kEvictLast);
+                tma_load_2d(stage, &g.tm_w, &sm->full[st], (kb0 + it) * kBlockK, f * kBlockF, kEvictFirst);
+                tma_load_2d(stage + kTileBytesW, &g.tm_x, &sm->full[st], (kb0 + it) * kBlockK, token0, kEvictLast);
+                if (++st == g.stages) st = 0, parity ^= 1;
             }
         }
         __syncwarp();  // lanes 1-31 must not run ahead to the block-wide barrier while lane 0 is still issuing
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_bf16(kBlockF, mt);
+            const uint64_t desc_hi = umma_desc_k128(tiles) & 0xFFFFFFFF00000000ull;
+            const uint32_t stage0 = smem_u32(tiles);
+            int st = 0;
+            uint32_t parity = 0;
             for (int it = 0; it < iters; ++it) {
-                const int st = it % g.stages;
-                const uint32_t parity = (it / g.stages) & 1;
                 if (!mbar_wait(&sm->full[st], parity, pipeline_deadline)) {
                     report(c.status, kErrTimeout, st, kPhasePipeline, 1);
                     break;
                 }
                 tcgen05_fence_after();
-                const uint64_t dw = umma_desc_k128(tiles + st * stage_bytes);
-                const uint64_t dx = umma_desc_k128(tiles + st * stage_bytes + kTileBytesW);
+                const uint32_t base = stage0 + st * stage_bytes;
+                const uint64_t dw = desc_hi | ((base & 0x3FFFF) >> 4), dx = desc_hi | (((base + kTileBytesW) & 0x3FFFF) >> 4);
 #pragma unroll
                 for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
                     // Advancing 16 BF16 = 32 bytes inside the swizzled row: +2 in the descriptor's 16-byte units.
                     umma_bf16(tmem, dw + 2 * kk, dx + 2 * kk, idesc, (it | kk) != 0);
                 }
                 umma_commit(&sm->empty[st]);
+                if (++st == g.stages) st = 0, parity ^= 1;
             }
             umma_commit(&sm->acc_full);
         }
