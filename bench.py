@@ -196,15 +196,19 @@ def run_gpu(args, rank, world):
     x_o, x_d = host_xo.to(device), host_xd.to(device)
     host_out = torch.empty(ROWS, HIDDEN, dtype=torch.bfloat16).pin_memory()
     flush = None
-    if sum(weight_bytes(world)) * LAYERS <= 130e6:
+    if sum(weight_bytes(world)) * LAYERS <= 130e6 or args.workload == "k3":
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+    only_reduce = args.workload == "k3"  # the reduction of GIVEN partials alone (dlm_reduce_bf16), no GEMM
+    given = group.symmetric("given", (ROWS, HIDDEN))
+    given.copy_(torch.randn(ROWS, HIDDEN, generator=g).to(torch.bfloat16))
 
     def step():
         out = None
         for i in range(LAYERS):
-            p = lin_o[i](x_o, out=group.partial(f"{i}.o", (ROWS, HIDDEN)))
+            p = given if only_reduce else lin_o[i](x_o, out=group.partial(f"{i}.o", (ROWS, HIDDEN)))
             group.reduce_norm(p, h, norms[2 * i], EPS, site=f"{i}.post")
-            p = lin_d[i](x_d, out=group.partial(f"{i}.down", (ROWS, HIDDEN)))
+            p = given if only_reduce else lin_d[i](x_d, out=group.partial(f"{i}.down", (ROWS, HIDDEN)))
             out = group.reduce_norm(p, h, norms[2 * i + 1], EPS, site=f"{i + 1}.input")
         return out
 
@@ -288,7 +292,12 @@ def run_gpu(args, rank, world):
                 "unit": "GB/s"}
     roof["frac"] = round(roof["achieved"] / roof["peak"], 4)
     roof["peak_source"] = f"of {which}"
-    roof["kernel"] = "rowpar_kernel"
+    roof["kernel"] = "reduce_kernel" if args.workload == "k3" else "rowpar_kernel"
+    if args.workload == "k3":  # no weights: the bytes are the partial read, the slot write+read and the output write
+        moved = 4 * ROWS * HIDDEN * 2
+        roof.update(bound="latency", achieved=round(moved / avg_launch_s / 1e9, 1), peak=hbm, unit="GB/s",
+                    algorithmic_bytes_per_launch=moved)
+        roof["frac"] = round(roof["achieved"] / roof["peak"], 4)
     roof["algorithmic_bytes_per_launch"] = (wo + wd) // 2 if roof["bound"] == "hbm" else reduction_bytes(world)
     roof["avg_launch_us"] = round(avg_launch_s * 1e6, 2)
     traffic = ROOT / "profiles" / "rowpar_kernel_traffic.json"
@@ -296,7 +305,8 @@ def run_gpu(args, rank, world):
 
     cpu_sec, cores = cpu_layer_seconds(world, 5) if world == 1 else (None, None)
     line = {
-        "metric": METRIC, "value": round(ms * 1e3 / LAYERS, 2), "unit": "us", "n_gpus": world, "steps": args.steps,
+        "metric": METRIC if args.workload == "c2" else "reduction of given partials (reduce + residual + RMSNorm), "
+        "latency per pair of reductions", "value": round(ms * 1e3 / LAYERS, 2), "unit": "us", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": False, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config(world),
         "e2e": {"value": round(e2e_ms * 1e3 / LAYERS, 2), "unit": "us",
@@ -456,7 +466,8 @@ def reference_gpu_path(torch, group, lin_o, lin_d, norms, x_o, x_d, h, stream, t
     def step():
         for i in range(2 * LAYERS):
             lin, x = (lin_o[i // 2], x_o) if i % 2 == 0 else (lin_d[i // 2], x_d)
-            torch.mm(x, lin.weight.t(), out=partial)
+            if args.workload != "k3":
+                torch.mm(x, lin.weight.t(), out=partial)
             last = state["last"]
             rearm, numel = (last.data_ptr(), last.numel()) if last is not None else (0, 0)
             ref.reduce_norm_residual(partial, recv_ptrs, h, norms[i], outs[i], mcs[i], peers[i], rearm, numel, epochs,
@@ -484,8 +495,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=36, help="layers per step; fewer only for profiler captures")
-    ap.add_argument("--workload", default="c2", choices=["c2", "c4", "c5"], help="c2 is the bench line; c4/c5 time the "
-                    "NVFP4 expert path of BASELINE configs 4 and 5")
+    ap.add_argument("--workload", default="c2", choices=["c2", "k3", "c4", "c5"], help="c2 is the bench line; k3 times "
+                    "the reduction of given partials alone; c4/c5 time the NVFP4 expert path of BASELINE configs 4 and 5")
     ap.add_argument("--routing", default="uniform", choices=["uniform", "zipf"])
     args = ap.parse_args()
     global LAYERS
@@ -498,7 +509,7 @@ def main():
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (torchrun --nproc-per-node {args.gpus}); "
                          f"WORLD_SIZE is {world}")
-    (run_gpu if args.workload == "c2" else run_gpu_moe)(args, rank, world)
+    (run_gpu if args.workload in ("c2", "k3") else run_gpu_moe)(args, rank, world)
     if world > 1:
         import torch.distributed as dist
 

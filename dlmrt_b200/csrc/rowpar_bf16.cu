@@ -46,7 +46,7 @@ __device__ __forceinline__ uint32_t tmem_cols(int m) {
 }  // namespace
 
 template <int NR>
-__global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_constant__ RowparParams<NR> p) {
+__global__ void __launch_bounds__(kFusedThreads, 2) rowpar_kernel(const __grid_constant__ RowparParams<NR> p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const int slot = NR == 1 ? 0 : static_cast<int>(blockIdx.y);
     const GemmDev& g = p.g[slot];
@@ -229,20 +229,28 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
         for (int v = threadIdx.x; v < (tok_hi - tok_lo) * (kBlockF / kVec); v += kFusedThreads) {
             const int token = tok_lo + v / (kBlockF / kVec), j = v % (kBlockF / kVec);
             const float* src = base + static_cast<size_t>(token) * kBlockF + j * kVec;
-            float4 a[kMaxSplits], b[kMaxSplits];
+            // Summed in split order, four splits' loads in flight at a time.
+            float acc[kVec];
+            for (int base_sp = 0; base_sp < g.splits; base_sp += 4) {
+                float4 a[4], b[4];
 #pragma unroll
-            for (int sp = 0; sp < kMaxSplits; ++sp) {
-                if (sp < g.splits) {
-                    a[sp] = __ldcg(reinterpret_cast<const float4*>(src + sp * split_stride));
-                    b[sp] = __ldcg(reinterpret_cast<const float4*>(src + sp * split_stride) + 1);
+                for (int u = 0; u < 4; ++u) {
+                    if (base_sp + u < g.splits) {
+                        a[u] = __ldcg(reinterpret_cast<const float4*>(src + (base_sp + u) * split_stride));
+                        b[u] = __ldcg(reinterpret_cast<const float4*>(src + (base_sp + u) * split_stride) + 1);
+                    }
                 }
-            }
-            float acc[kVec] = {a[0].x, a[0].y, a[0].z, a[0].w, b[0].x, b[0].y, b[0].z, b[0].w};
 #pragma unroll
-            for (int sp = 1; sp < kMaxSplits; ++sp) {
-                if (sp < g.splits) {
-                    acc[0] += a[sp].x, acc[1] += a[sp].y, acc[2] += a[sp].z, acc[3] += a[sp].w;
-                    acc[4] += b[sp].x, acc[5] += b[sp].y, acc[6] += b[sp].z, acc[7] += b[sp].w;
+                for (int u = 0; u < 4; ++u) {
+                    if (base_sp + u < g.splits) {
+                        if (base_sp + u == 0) {
+                            acc[0] = a[u].x, acc[1] = a[u].y, acc[2] = a[u].z, acc[3] = a[u].w;
+                            acc[4] = b[u].x, acc[5] = b[u].y, acc[6] = b[u].z, acc[7] = b[u].w;
+                        } else {
+                            acc[0] += a[u].x, acc[1] += a[u].y, acc[2] += a[u].z, acc[3] += a[u].w;
+                            acc[4] += b[u].x, acc[5] += b[u].y, acc[6] += b[u].z, acc[7] += b[u].w;
+                        }
+                    }
                 }
             }
             const uint4 packed = pack_bf16x8(acc);
@@ -280,8 +288,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
 }
 
 int rowpar_stages(int m) {  // m: tokens per tile
+    // Up to 128 tokens per tile the ring is kept under half of an SM's shared memory, so that two CTAs fit on one SM:
+    // the next kernel of a stream (a programmatic dependent launch) can then move in, build its barriers and prefetch
+    // its first weight slabs while this kernel's CTAs sit in the NVLink waits of the reduction.
     const int stage = kTileBytesW + m * kBlockK * 2;
-    int stages = kSmemBudget / stage;
+    int stages = (m <= 128 ? 100 * 1024 : kSmemBudget) / stage;
     if (stages > kMaxStages) stages = kMaxStages;
     return stages;
 }
