@@ -498,9 +498,12 @@ def main():
     ap.add_argument("--workload", default="c2", choices=["c2", "k3", "c4", "c5"], help="c2 is the bench line; k3 times "
                     "the reduction of given partials alone; c4/c5 time the NVFP4 expert path of BASELINE configs 4 and 5")
     ap.add_argument("--routing", default="uniform", choices=["uniform", "zipf"])
+    ap.add_argument("--shard-of", type=int, default=1, help="profiling aid: run the K shard of a TP=<n> rank on the GPUs "
+                    "given (the GEMM of a higher TP degree without its peers)")
     args = ap.parse_args()
-    global LAYERS
+    global LAYERS, K_O, K_DOWN
     LAYERS = args.layers
+    K_O, K_DOWN = K_O // args.shard_of, K_DOWN // args.shard_of
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     if args.impl == "reference":

@@ -32,7 +32,7 @@ class DlmComm(C.Structure):
 class DlmGemm(C.Structure):
     _fields_ = [("x", C.c_void_p), ("w", C.c_void_p), ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
                 ("ldx", C.c_int64), ("ldw", C.c_int64), ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
-                ("splits", C.c_int32), ("token_tiles", C.c_int32)]
+                ("splits", C.c_int32), ("token_tiles", C.c_int32), ("w_tiled", C.c_int32), ("use_cluster", C.c_int32)]
 
 
 class DlmMoe(C.Structure):

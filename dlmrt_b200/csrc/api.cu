@@ -131,8 +131,17 @@ int make_map(CUtensorMap* map, const void* base, int rows, int cols, long long l
 // never faster than the whole weight shard streams from HBM; several splits add the partial-tile round trip through L2
 // and the rendezvous. Token tiles re-read W from L2 but need no rendezvous, which wins for short K (high TP degrees);
 // K splits win for long K (TP = 1).
-void choose_tiling(int m, int n, int k, int avail, int* tiles_out, int* splits_out) {
-    const double sm_bytes_per_us = 120e3, hbm_bytes_per_us = 6.0e6, rendezvous_us = 3.0;
+// Can the `splits` CTAs of each of `clusters` tiles run as co-resident thread-block clusters (partials exchanged through
+// distributed shared memory)? The partial tile must also fit over the drained pipeline stages.
+bool cluster_fits(int mt, int splits, int clusters) {
+    if (splits < 2 || splits > 8) return false;
+    const int stage = kBlockF * kBlockK * 2 + mt * kBlockK * 2;
+    if (mt * kBlockF * 4 > rowpar_stages(mt) * stage) return false;
+    return rowpar_max_clusters(mt, splits) >= clusters;
+}
+
+void choose_tiling(int m, int n, int k, int avail, int* tiles_out, int* splits_out, bool clusters = true, int ranks = 1) {
+    const double sm_bytes_per_us = 120e3, hbm_bytes_per_us = 6.0e6;
     const int feature_tiles = n / kBlockF, nkb = k / kBlockK;
     double best = 1e30;
     *tiles_out = 1;
@@ -147,7 +156,12 @@ void choose_tiling(int m, int n, int k, int avail, int* tiles_out, int* splits_o
             double us = kb * (16384.0 + mt * 128.0) / sm_bytes_per_us;
             const double hbm = static_cast<double>(n) * k * 2 / hbm_bytes_per_us;
             if (us < hbm) us = hbm;
-            if (sp > 1) us += rendezvous_us + 2.0 * mt * kBlockF * 4 / sm_bytes_per_us;
+            if (sp > 1) {
+                // Meeting in distributed shared memory costs about a microsecond; through L2 (partial tiles written,
+                // fenced, counted, read back) about three plus the traffic.
+                if (clusters && cluster_fits(mt, sp, feature_tiles * t * ranks)) us += 1.0;
+                else us += 3.0 + 2.0 * mt * kBlockF * 4 / sm_bytes_per_us;
+            }
             if (us < best - 1e-9) {
                 best = us;
                 *tiles_out = t;
@@ -163,7 +177,8 @@ int check_gemm(const DlmGemm* g) {
     if (g->m < 16 || g->m > DLM_MAX_M || g->m % 16) return DLM_ERR_SHAPE;
     if (g->n < kBlockF || g->n % kBlockF || g->k < kBlockK || g->k % kBlockK) return DLM_ERR_SHAPE;
     if (g->n / kBlockF > 64) return DLM_ERR_SHAPE;
-    if (g->ldx < g->k || g->ldw < g->k || g->ldx % 8 || g->ldw % 8) return DLM_ERR_ALIGN;
+    if (g->ldx < g->k || g->ldx % 8 || (!g->w_tiled && (g->ldw < g->k || g->ldw % 8))) return DLM_ERR_ALIGN;
+    if (g->w_tiled < 0 || g->w_tiled > 1 || g->use_cluster < 0 || g->use_cluster > 1) return DLM_ERR_SHAPE;
     if (!aligned16(g->x) || !aligned16(g->w) || (reinterpret_cast<uintptr_t>(g->workspace) & 255)) return DLM_ERR_ALIGN;
     if (g->splits < 0 || g->splits > kMaxSplits) return DLM_ERR_SHAPE;
     if (g->token_tiles < 0 || (g->token_tiles > 0 && (g->m % (16 * g->token_tiles) || g->token_tiles > 16)))
@@ -172,14 +187,14 @@ int check_gemm(const DlmGemm* g) {
 }
 
 // Fills the device-side GEMM block; returns the per-rank grid in *grid.
-int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid) {
+int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid, int ranks = 1) {
     std::memset(d, 0, sizeof(*d));
     const int avail = max_ctas > 0 && max_ctas < sms ? max_ctas : sms;
     const int feature_tiles = g->n / kBlockF, nkb = g->k / kBlockK;
     int token_tiles = g->token_tiles, splits = g->splits;
     if (token_tiles == 0 || splits == 0) {
         int t = 1, sp = 1;
-        choose_tiling(g->m, g->n, g->k, avail, &t, &sp);
+        choose_tiling(g->m, g->n, g->k, avail, &t, &sp, g->use_cluster, ranks);
         if (token_tiles == 0 && splits == 0) {
             token_tiles = t;
             splits = sp;
@@ -193,10 +208,13 @@ int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid) {
     const int tiles = feature_tiles * token_tiles;
     if (tiles > kMaxTiles || tiles * splits > avail) return DLM_ERR_GRID;
     const int mt = g->m / token_tiles;
-    int rc = make_map(&d->tm_w, g->w, g->n, g->k, g->ldw, kBlockF);
+    int rc = g->w_tiled ? DLM_OK : make_map(&d->tm_w, g->w, g->n, g->k, g->ldw, kBlockF);
+    if (g->w_tiled) d->w_tiles = static_cast<const uint8_t*>(g->w);
     if (rc == DLM_OK) rc = make_map(&d->tm_x, g->x, g->m, g->k, g->ldx, mt);
     if (rc != DLM_OK) return rc;
-    const size_t need = kWorkspaceHeader + (splits > 1 ? static_cast<size_t>(splits) * g->m * g->n * sizeof(float) : 0);
+    const bool in_cluster = g->use_cluster && cluster_fits(mt, splits, tiles * ranks);
+    const size_t need =
+        kWorkspaceHeader + (splits > 1 && !in_cluster ? static_cast<size_t>(splits) * g->m * g->n * sizeof(float) : 0);
     if (g->workspace_bytes < static_cast<int64_t>(need)) return DLM_ERR_WORKSPACE;
     d->gen = static_cast<int*>(g->workspace);
     d->counters = d->gen + kEpochSlots;
@@ -207,6 +225,7 @@ int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid) {
     d->splits = splits;
     d->token_tiles = token_tiles;
     d->stages = rowpar_stages(mt);
+    d->cluster = g->use_cluster && cluster_fits(mt, splits, tiles * ranks) ? 1 : 0;
     *grid = tiles * splits;
     return DLM_OK;
 }
@@ -271,7 +290,7 @@ int dlm_gemm_bf16(const DlmGemm* gemm, void* out, int64_t ldo, int pdl, dlm_stre
     p.g[0].out = static_cast<__nv_bfloat16*>(out);
     p.g[0].ldo = ldo;
     p.fused = 0;
-    return launch_rowpar(p, grid, {static_cast<cudaStream_t>(stream), pdl != 0, false});
+    return launch_rowpar(p, grid, {static_cast<cudaStream_t>(stream), pdl != 0, false, p.g[0].cluster ? p.g[0].splits : 1});
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -305,7 +324,7 @@ int dlm_gemm_bf16_noalloc(const void* x, const void* w, void* out, int m, int n,
     DlmGemm g;
     std::memset(&g, 0, sizeof(g));
     g.x = x, g.w = w, g.m = m, g.n = n, g.k = k, g.ldx = ldx, g.ldw = ldw;
-    g.splits = splits, g.token_tiles = token_tiles;
+    g.splits = splits, g.token_tiles = token_tiles, g.w_tiled = 0;
     g.workspace = reinterpret_cast<void*>(uintptr_t(256));  // placeholder for the argument checks only
     g.workspace_bytes = DLM_NOALLOC_SCRATCH_BYTES;
     int rc = check_gemm(&g);
@@ -325,7 +344,7 @@ int dlm_gemm_bf16_noalloc(const void* x, const void* w, void* out, int m, int n,
     g.workspace = scratch;
     if (g.splits == 0 || g.token_tiles == 0) {
         int t = 1, sp = 1;
-        choose_tiling(m, n, k, info.sms, &t, &sp);
+        choose_tiling(m, n, k, info.sms, &t, &sp, false);
         if (g.token_tiles == 0) g.token_tiles = g.splits == 0 ? t : 1;
         if (g.splits == 0) g.splits = token_tiles == 0 ? sp : 1;
         while (g.splits > 1 && kWorkspaceHeader + g.splits * per_split > DLM_NOALLOC_SCRATCH_BYTES) --g.splits;
@@ -343,7 +362,7 @@ int dlm_gemm_bf16_noalloc(const void* x, const void* w, void* out, int m, int n,
     // generation and arrival counters); the partial tiles are fully rewritten before they are read.
     const cudaError_t err = cudaMemsetAsync(scratch, 0, kWorkspaceHeader, s);
     if (err != cudaSuccess) return cuda_fail(err);
-    return launch_rowpar(p, grid, {s, pdl != 0, false});
+    return launch_rowpar(p, grid, {s, pdl != 0, false, 1});
 }
 
 static int check_pair(const DlmGemm* gemm, const DlmComm* comm) {
@@ -367,7 +386,8 @@ int dlm_rowpar_bf16(const DlmGemm* gemm, const DlmComm* comm, dlm_stream_t strea
     if (rc != DLM_OK) return rc;
     fill_comm(&p.c[0], comm);
     p.fused = 1;
-    return launch_rowpar(p, grid, {static_cast<cudaStream_t>(stream), comm->pdl != 0, false});
+    return launch_rowpar(p, grid, {static_cast<cudaStream_t>(stream), comm->pdl != 0, false,
+                                   p.g[0].cluster ? p.g[0].splits : 1});
 }
 
 static int check_moe(const DlmMoe* m) {
@@ -510,14 +530,15 @@ int dlm_rowpar_bf16_loopback(const DlmGemm* gemm, const DlmComm* comm, int nrank
         if (gemm[i].m != gemm[0].m || gemm[i].n != gemm[0].n || gemm[i].k != gemm[0].k) return DLM_ERR_SHAPE;
         int cap = comm[0].max_ctas > 0 && comm[0].max_ctas < per_rank ? comm[0].max_ctas : per_rank;
         int gi = 0;
-        rc = fill_gemm(&p.g[i], &gemm[i], cap, per_rank, &gi);
+        rc = fill_gemm(&p.g[i], &gemm[i], cap, per_rank, &gi, nranks);
         if (rc != DLM_OK) return rc;
         if (i > 0 && gi != grid) return DLM_ERR_SHAPE;
         grid = gi;
         fill_comm(&p.c[i], &comm[i]);
     }
     p.fused = 1;
-    return launch_rowpar_loopback(p, grid, nranks, {static_cast<cudaStream_t>(stream), false, true});
+    return launch_rowpar_loopback(p, grid, nranks, {static_cast<cudaStream_t>(stream), false, true,
+                                                    p.g[0].cluster ? p.g[0].splits : 1});
 }
 
 size_t dlm_workspace_bytes(int m, int n, int k) {

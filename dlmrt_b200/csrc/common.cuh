@@ -162,6 +162,28 @@ __device__ __forceinline__ bool elect_one() {
 }
 
 // ---------------------------------------------------------------------------------------------------------------
+// Thread-block clusters: barrier and distributed shared memory
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
+// Address, in the cluster's shared window, of this CTA's shared address `local` as seen in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local, int rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    return remote;
+}
+
+__device__ __forceinline__ float4 cluster_load_f4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(addr)
+                 : "memory");
+    return v;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
 // TMA (tiled bulk tensor loads into this CTA's shared memory; no cluster multicast anywhere in this library)
 // ---------------------------------------------------------------------------------------------------------------
 constexpr uint64_t kEvictNormal = 0x1000000000000000ull;
@@ -179,6 +201,15 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, ui
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
         " [%0], [%1, {%3, %4}], [%2], %5;"
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y), "l"(hint)
+        : "memory");
+}
+
+// Untiled bulk copy of `bytes` (a multiple of 16, both addresses 16-byte aligned) of contiguous global memory.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar,
+                                          uint64_t hint) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+        ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)), "l"(hint)
         : "memory");
 }
 

@@ -21,12 +21,14 @@ constexpr int kSmemBudget = 200 * 1024;
 struct alignas(64) GemmDev {
     CUtensorMap tm_w;  // W [n, k] BF16, box 64 x 128, 128-byte swizzle
     CUtensorMap tm_x;  // x [m, k] BF16, box 64 x (m / token_tiles), 128-byte swizzle
+    const uint8_t* w_tiles;  // or: W pre-tiled [n / 128][k / 64][16 KB], each tile already in the swizzled smem layout
     float* ws;         // FP32 partial tiles [tile][split][tokens per tile][128]
     int* gen;          // [256] launch generation of this workspace, every entry kept equal (like the epochs)
     int* counters;     // [2][kMaxTiles] split-K arrivals per tile, banked by generation parity
     __nv_bfloat16* out;
     long long ldo;
     int m, n, k, splits, token_tiles, stages;
+    int cluster;       // the K splits of a tile form a thread-block cluster and meet in distributed shared memory
 };
 
 template <int NR>
@@ -73,6 +75,7 @@ struct LaunchOpts {
     cudaStream_t stream;
     bool pdl;
     bool cooperative;
+    int cluster = 1;  // CTAs per cluster along x
 };
 
 int launch_reduce(const ReduceParams<1>& p, int grid, int threads, const LaunchOpts& o);
@@ -86,6 +89,7 @@ int moe_stages(int rows_cap);
 int rowpar_smem_bytes(int m, int stages);
 int rowpar_stages(int m);
 int rowpar_max_ctas_per_sm(int m);
+int rowpar_max_clusters(int tokens_per_tile, int cluster);  // co-resident clusters of that size, 0 if unsupported
 
 extern int g_last_cuda_error;
 extern long long g_launches;

@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2) rowpar_kernel(const __grid_c
         }
         mbar_init(&sm->acc_full, 1);
         fence_barrier_init();
-        tma_prefetch_descriptor(&g.tm_w);
+        if (!g.w_tiles) tma_prefetch_descriptor(&g.tm_w);
         tma_prefetch_descriptor(&g.tm_x);
     }
     if (warp == 2) tmem_alloc(&sm->tmem_base, cols);
@@ -94,8 +94,12 @@ __global__ void __launch_bounds__(kFusedThreads, 2) rowpar_kernel(const __grid_c
             const int pre = iters < g.stages ? iters : g.stages;
             for (int it = 0; it < pre; ++it) {
                 mbar_expect_tx(&sm->full[it], static_cast<uint32_t>(stage_bytes));
-                tma_load_2d(tiles + it * stage_bytes, &g.tm_w, &sm->full[it], (kb0 + it) * kBlockK, f * kBlockF,
-                            kEvictFirst);
+                if (g.w_tiles)
+                    bulk_load(tiles + it * stage_bytes, g.w_tiles + (static_cast<size_t>(f) * nkb + kb0 + it) * kTileBytesW,
+                              kTileBytesW, &sm->full[it], kEvictFirst);
+                else
+                    tma_load_2d(tiles + it * stage_bytes, &g.tm_w, &sm->full[it], (kb0 + it) * kBlockK, f * kBlockF,
+                                kEvictFirst);
             }
             pdl_wait();
             for (int it = 0; it < pre; ++it)
@@ -110,7 +114,11 @@ __global__ void __launch_bounds__(kFusedThreads, 2) rowpar_kernel(const __grid_c
                 }
                 uint8_t* stage = tiles + st * stage_bytes;
                 mbar_expect_tx(&sm->full[st], static_cast<uint32_t>(stage_bytes));
-                tma_load_2d(stage, &g.tm_w, &sm->full[st], (kb0 + it) * kBlockK, f * kBlockF, kEvictFirst);
+                if (g.w_tiles)
+                    bulk_load(stage, g.w_tiles + (static_cast<size_t>(f) * nkb + kb0 + it) * kTileBytesW, kTileBytesW,
+                              &sm->full[st], kEvictFirst);
+                else
+                    tma_load_2d(stage, &g.tm_w, &sm->full[st], (kb0 + it) * kBlockK, f * kBlockF, kEvictFirst);
                 tma_load_2d(stage + kTileBytesW, &g.tm_x, &sm->full[st], (kb0 + it) * kBlockK, token0, kEvictLast);
                 if (++st == g.stages) st = 0, parity ^= 1;
             }
@@ -163,9 +171,12 @@ __global__ void __launch_bounds__(kFusedThreads, 2) rowpar_kernel(const __grid_c
         // One K split: the BF16 tile is staged in shared memory, token-major, over the drained pipeline stages.
         // Several: this CTA's FP32 partial tile goes to the workspace (which the previous kernel of the chain may
         // still be reading, hence the wait).
-        float* part = g.ws + (static_cast<size_t>(tile) * g.splits + s) * mt * kBlockF;
+        // With a cluster the partial tile stays in this CTA's shared memory (over the drained stages), where the other
+        // CTAs of the cluster read it.
+        float* part = g.cluster ? reinterpret_cast<float*>(tiles)
+                                : g.ws + (static_cast<size_t>(tile) * g.splits + s) * mt * kBlockF;
         __nv_bfloat16* staged = reinterpret_cast<__nv_bfloat16*>(tiles);
-        if (g.splits > 1) pdl_wait();
+        if (g.splits > 1 && !g.cluster) pdl_wait();
         for (int chunk = half; chunk < mt / 16; chunk += 2) {
             uint32_t r[16];
             if (iters > 0 && ok) {
@@ -188,7 +199,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2) rowpar_kernel(const __grid_c
         tcgen05_fence_before();
     }
     pdl_wait();
-    if (g.splits > 1) __threadfence();
+    if (g.splits > 1 && !g.cluster) __threadfence();
     __syncthreads();
     if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 5] = globaltimer();
     if (warp == 2) {
@@ -201,7 +212,52 @@ __global__ void __launch_bounds__(kFusedThreads, 2) rowpar_kernel(const __grid_c
         x = comm_begin(c, block, blocks, sm->epoch);
         stamp(c, x, 0);
     }
-    if (g.splits > 1) {
+    if (g.splits > 1 && g.cluster) {
+        // Split-K inside a cluster: the CTAs of a tile are one thread-block cluster (cluster rank = split). After the
+        // cluster barrier every CTA sums ITS share of the tile's tokens over the splits, in split order, straight out
+        // of the other CTAs' shared memory, and pushes it. No global round trip, no atomics.
+        cluster_arrive();
+        cluster_wait();
+        const int tok_lo = static_cast<int>(static_cast<long long>(s) * mt / g.splits);
+        const int tok_hi = static_cast<int>(static_cast<long long>(s + 1) * mt / g.splits);
+        const uint32_t local = smem_u32(tiles);
+        for (int v = threadIdx.x; v < (tok_hi - tok_lo) * (kBlockF / kVec); v += kFusedThreads) {
+            const int token = tok_lo + v / (kBlockF / kVec), j = v % (kBlockF / kVec);
+            const uint32_t off = local + (token * kBlockF + j * kVec) * 4;
+            float acc[kVec];
+            for (int base_sp = 0; base_sp < g.splits; base_sp += 4) {
+                float4 a[4], b[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (base_sp + u < g.splits) {
+                        const uint32_t remote = cluster_map(off, base_sp + u);
+                        a[u] = cluster_load_f4(remote);
+                        b[u] = cluster_load_f4(remote + 16);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (base_sp + u < g.splits) {
+                        if (base_sp + u == 0) {
+                            acc[0] = a[u].x, acc[1] = a[u].y, acc[2] = a[u].z, acc[3] = a[u].w;
+                            acc[4] = b[u].x, acc[5] = b[u].y, acc[6] = b[u].z, acc[7] = b[u].w;
+                        } else {
+                            acc[0] += a[u].x, acc[1] += a[u].y, acc[2] += a[u].z, acc[3] += a[u].w;
+                            acc[4] += b[u].x, acc[5] += b[u].y, acc[6] += b[u].z, acc[7] += b[u].w;
+                        }
+                    }
+                }
+            }
+            const uint4 packed = pack_bf16x8(acc);
+            const int col = f * kBlockF + j * kVec;
+            if (p.fused) {
+                store_v4(push_address(c, x, token0 + token, col), packed);
+            } else {
+                store_v4(g.out + static_cast<size_t>(token0 + token) * g.ldo + col, packed);
+            }
+        }
+        cluster_arrive();  // done reading the others' partials; the matching wait is at the very end of the kernel
+    } else if (g.splits > 1) {
         // Split-K rendezvous: every CTA of the tile announces its partial, waits for the others, then sums ITS share of
         // the tile's tokens over the splits in split order (so the value never depends on timing) and pushes it.
         // Arrival counters alternate between two banks by launch generation; this launch clears the other bank.
@@ -285,6 +341,8 @@ __global__ void __launch_bounds__(kFusedThreads, 2) rowpar_kernel(const __grid_c
     } else {
         pdl_launch_dependents();
     }
+    // A CTA's shared memory must outlive the reads of its cluster peers.
+    if (g.splits > 1 && g.cluster) cluster_wait();
 }
 
 int rowpar_stages(int m) {  // m: tokens per tile
@@ -320,7 +378,7 @@ static int launch_impl(const RowparParams<NR>& p, dim3 grid, const LaunchOpts& o
         config.blockDim = dim3(kFusedThreads);
         config.dynamicSmemBytes = static_cast<size_t>(smem);
         config.stream = o.stream;
-        cudaLaunchAttribute attrs[2];
+        cudaLaunchAttribute attrs[3];
         int n = 0;
         if (o.pdl) {
             attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -330,6 +388,13 @@ static int launch_impl(const RowparParams<NR>& p, dim3 grid, const LaunchOpts& o
         if (o.cooperative) {
             attrs[n].id = cudaLaunchAttributeCooperative;
             attrs[n].val.cooperative = 1;
+            ++n;
+        }
+        if (o.cluster > 1) {
+            attrs[n].id = cudaLaunchAttributeClusterDimension;
+            attrs[n].val.clusterDim.x = static_cast<unsigned>(o.cluster);
+            attrs[n].val.clusterDim.y = 1;
+            attrs[n].val.clusterDim.z = 1;
             ++n;
         }
         config.attrs = attrs;
@@ -349,6 +414,34 @@ int launch_rowpar(const RowparParams<1>& p, int grid, const LaunchOpts& o) { ret
 
 int launch_rowpar_loopback(const RowparParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o) {
     return launch_impl<kMaxWorld>(p, dim3(grid, nranks), o);
+}
+
+int rowpar_max_clusters(int tokens_per_tile, int cluster) {
+    static int cache[257][9];  // by tokens per tile and cluster size; 0 = not asked yet, -1 = unsupported
+    if (tokens_per_tile < 1 || tokens_per_tile > 256 || cluster < 2 || cluster > 8) return 0;
+    int& slot = cache[tokens_per_tile][cluster];
+    if (slot == 0) {
+        const int smem = rowpar_smem_bytes(tokens_per_tile, rowpar_stages(tokens_per_tile));
+        cudaLaunchConfig_t config{};
+        config.gridDim = dim3(static_cast<unsigned>(cluster) * 64);
+        config.blockDim = dim3(kFusedThreads);
+        config.dynamicSmemBytes = static_cast<size_t>(smem);
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = static_cast<unsigned>(cluster);
+        attr.val.clusterDim.y = attr.val.clusterDim.z = 1;
+        config.attrs = &attr;
+        config.numAttrs = 1;
+        int n = 0;
+        if (cudaFuncSetAttribute(rowpar_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 rowpar_smem_bytes(256, rowpar_stages(256))) != cudaSuccess ||
+            cudaOccupancyMaxActiveClusters(&n, rowpar_kernel<1>, &config) != cudaSuccess) {
+            (void)cudaGetLastError();
+            n = -1;
+        }
+        slot = n > 0 ? n : -1;
+    }
+    return slot > 0 ? slot : 0;
 }
 
 int rowpar_max_ctas_per_sm(int m) {

@@ -239,8 +239,8 @@ class Group:
             raise ValueError("row-parallel input must be BF16 with contiguous K")
         nbytes = _lib.lib().dlm_workspace_bytes(m, linear.n, k)
         ws = self.workspace(chain, nbytes)
-        g.x, g.w, g.m, g.n, g.k = x.data_ptr(), linear.weight.data_ptr(), m, linear.n, k
-        g.ldx, g.ldw = x.stride(0), linear.weight.stride(0)
+        linear.describe(g)
+        g.x, g.m, g.n, g.k, g.ldx = x.data_ptr(), m, linear.n, k, x.stride(0)
         g.workspace, g.workspace_bytes, g.splits = ws.data_ptr(), ws.numel(), 0
         return g
 

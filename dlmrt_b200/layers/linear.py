@@ -18,10 +18,25 @@ from .. import _lib
 from .._lib import DlmGemm
 
 
+def tile_weight(weight):
+    """[N, K] BF16 row-major -> the streaming layout of the kernels: [N / 128, K / 64] tiles of 128 rows x 64 columns,
+    each 16 KB tile contiguous and already in the 128-byte-swizzled order it has in shared memory (16-byte chunk c of
+    tile row r sits at chunk position c ^ (r % 8)). One bulk copy then brings a tile in, and a CTA's weight slab is a
+    contiguous run of HBM instead of 128-byte pieces a row pitch apart."""
+    n, k = weight.shape
+    if n % 128 or k % 64:
+        raise ValueError(f"weight {tuple(weight.shape)}: N must be a multiple of 128 and K of 64")
+    t = weight.reshape(n // 128, 128, k // 64, 8, 8).permute(0, 2, 1, 3, 4)  # (tile row, tile col, r, chunk, 8 elems)
+    r = torch.arange(128, device=weight.device).view(128, 1)
+    c = torch.arange(8, device=weight.device).view(1, 8)
+    src = (c ^ (r % 8)).view(1, 1, 128, 8, 1).expand(n // 128, k // 64, 128, 8, 8)  # position p holds chunk p ^ (r % 8)
+    return torch.gather(t, 3, src).contiguous()
+
+
 class Linear:
     """y = x @ W^T, BF16 in and out, FP32 accumulation in increasing K (K ranges summed in order when split)."""
 
-    def __init__(self, weight, fp8=False, b200=False, group=None):
+    def __init__(self, weight, fp8=False, b200=False, group=None, tiled=True):
         if fp8:
             raise NotImplementedError("FP8 linears are not part of the row-parallel BF16 path")
         if weight.dtype != torch.bfloat16 or weight.dim() != 2:
@@ -30,6 +45,8 @@ class Linear:
         self.fp8 = False
         self.b200 = False  # the SM 12.x emulation switch of the reference has no meaning on a B200
         self.weight = weight.contiguous()
+        # `tiled`: stream a re-laid copy of the weight (see tile_weight) instead of the row-major matrix.
+        self.tiles = tile_weight(self.weight) if tiled and self.n % 128 == 0 and self.k % 64 == 0 else None
         self.group = group
         self._workspace = None
         _lib.lib()
@@ -50,13 +67,20 @@ class Linear:
             with torch.inference_mode(False):
                 self._workspace = torch.zeros(nbytes, device=x.device, dtype=torch.uint8)
         g = DlmGemm()
-        g.x, g.w, g.m, g.n, g.k = x.data_ptr(), self.weight.data_ptr(), m, self.n, k
-        g.ldx, g.ldw = x.stride(0), self.weight.stride(0)
+        self.describe(g)
+        g.x, g.m, g.n, g.k, g.ldx = x.data_ptr(), m, self.n, k, x.stride(0)
         g.workspace, g.workspace_bytes, g.splits = self._workspace.data_ptr(), self._workspace.numel(), 0
         stream = torch.cuda.current_stream(x.device).cuda_stream
         _lib.check(_lib.lib().dlm_gemm_bf16(C.byref(g), out.data_ptr(), out.stride(0), int(pdl), stream),
                    f"gemm [{m}, {self.n}, {k}]")
         return out
+
+    def describe(self, g):
+        """Fill the weight fields of a DlmGemm."""
+        if self.tiles is not None:
+            g.w, g.ldw, g.w_tiled = self.tiles.data_ptr(), self.k, 1
+        else:
+            g.w, g.ldw, g.w_tiled = self.weight.data_ptr(), self.weight.stride(0), 0
 
     def __call__(self, x, scales=None, out=None):
         if out is None:

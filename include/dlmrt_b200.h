@@ -109,6 +109,15 @@ typedef struct DlmGemm {
     int32_t splits;  /* K splits across CTAs, 0 = chosen by the library; FP32 partial tiles are summed in split
                         order, so the result does not depend on scheduling */
     int32_t token_tiles; /* tiles along m (each m / token_tiles tokens, a multiple of 16), 0 = chosen by the library */
+    int32_t w_tiled; /* 0: w is row-major [n, k] (ldw). 1: w is pre-tiled for streaming, [n / 128][k / 64] tiles of
+                        128 rows x 64 BF16 (16 KB, contiguous), the 16-byte chunk c of tile row r stored at chunk
+                        position c ^ (r % 8) (the 128-byte shared-memory swizzle); ldw is ignored. Weights are static,
+                        so the layout is made once when they are loaded, as the reference re-lays its FP8 and NVFP4
+                        weights (linear.py:30-31, nvfp4.py:104-112). */
+    int32_t use_cluster; /* 0 (default): FP32 partial tiles of a split K meet through the workspace. 1: where the GPU can
+                        hold them all at once, the CTAs of a tile run as one thread-block cluster and sum the partial
+                        tiles out of each other's shared memory. Same result either way; measured slower on B200 for
+                        these shapes (remote shared-memory reads), kept for shapes where it may pay. */
 } DlmGemm;
 
 /* The NVFP4 expert half of a fused call: GEMM2 (down-projection) of this rank's routed experts and the weighted top-k

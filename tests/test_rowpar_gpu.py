@@ -22,7 +22,7 @@ def short_timeouts(monkeypatch):
     monkeypatch.setattr(parallel, "TIMEOUT_NS", 500_000_000)
 
 
-def gemm(x, w, splits=0, token_tiles=0):
+def gemm(x, w, splits=0, token_tiles=0, use_cluster=0):
     from dlmrt_b200 import _lib
     from dlmrt_b200._lib import DlmGemm
 
@@ -33,6 +33,7 @@ def gemm(x, w, splits=0, token_tiles=0):
     g = DlmGemm()
     g.x, g.w, g.m, g.n, g.k, g.ldx, g.ldw = x.data_ptr(), w.data_ptr(), m, n, k, x.stride(0), w.stride(0)
     g.workspace, g.workspace_bytes, g.splits, g.token_tiles = ws.data_ptr(), ws.numel(), splits, token_tiles
+    g.use_cluster = use_cluster
     _lib.check(_lib.lib().dlm_gemm_bf16(C.byref(g), out.data_ptr(), n, 0, None), "gemm")
     torch.cuda.synchronize()
     return out
@@ -102,8 +103,9 @@ def test_gemm_token_tiles_and_splits_agree(token_tiles, splits):
     x, w = integer_case(m, n, k, seed=3)
     want = f32_to_bf16(rowpar.gemm_f32(bits(x), bits(w)))
     from dlmrt_b200.layers.linear import Linear
-    for _ in range(2):
-        assert_same_bits(bits(gemm(x, w, splits, token_tiles)), want, f"tiles {token_tiles} splits {splits}")
+    for use_cluster in (0, 1, 0):  # partial tiles through the workspace, clusters meeting in shared memory, and back
+        assert_same_bits(bits(gemm(x, w, splits, token_tiles, use_cluster)), want,
+                         f"tiles {token_tiles} splits {splits} use_cluster {use_cluster}")
     lin = Linear(w)
     out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
     for _ in range(5):  # same workspace, back to back, no host synchronisation in between
