@@ -30,7 +30,7 @@ constexpr int kStampSlots = 16;
 constexpr int kStampSlots = 8;
 #endif
 //  // %globaltimer stamps per CTA: 0 start, 1 pushed, 2 owned rows broadcast, 3 collected;
-                                // fused kernels add 4 accumulator ready, 5 partial tile written, 6 tile summed and pushed
+                                // fused kernels add 4 accumulator ready, 5 dependency wait returned, 6 tile summed and pushed
 
 enum Mode { kReduce = 0, kReduceNorm = 1, kReduceNormResidual = 2 };
 

@@ -213,6 +213,17 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
         : "memory");
 }
 
+// Prefetches into L2 only: a contiguous range, or one box of a tensor map. Nothing is written to shared memory and
+// nothing signals completion; the loads that follow simply find the data closer.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gmem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gmem_src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_l2_2d(const void* tmap, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(tmap)),
+                 "r"(x), "r"(y)
+                 : "memory");
+}
+
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, uint64_t* bar, int x, int y, int z,
                                             uint64_t hint) {
     asm volatile(

@@ -20,6 +20,8 @@
 //   the splits in split order (the value never depends on timing). Either way each token row's 256 bytes are stored
 //   (plain GEMM) or pushed straight into the owner rank's receive slot over NVLink, and every CTA goes on to the
 //   re-arm / own / collect phases of the reduction (comm.cuh).
+#include <cstdlib>
+
 #include "kernels.cuh"
 
 namespace dlm {
@@ -101,7 +103,18 @@ __global__ void __launch_bounds__(kFusedThreads, 2) rowpar_kernel(const __grid_c
                     tma_load_2d(tiles + it * stage_bytes, &g.tm_w, &sm->full[it], (kb0 + it) * kBlockK, f * kBlockF,
                                 kEvictFirst);
             }
+            // The rest of this CTA's weight slab is pulled into L2 now, while the previous kernel of the stream is still
+            // finishing: weights never depend on it, and the ring then refills at L2 latency instead of HBM latency.
+            if (iters > pre) {
+                if (g.w_tiles) {
+                    bulk_prefetch_l2(g.w_tiles + (static_cast<size_t>(f) * nkb + kb0 + pre) * kTileBytesW,
+                                     static_cast<uint32_t>(iters - pre) * kTileBytesW);
+                } else {
+                    for (int it = pre; it < iters; ++it) tma_prefetch_l2_2d(&g.tm_w, (kb0 + it) * kBlockK, f * kBlockF);
+                }
+            }
             pdl_wait();
+            if (c.stamps) c.stamps[block * kStampSlots + 5] = globaltimer();
             for (int it = 0; it < pre; ++it)
                 tma_load_2d(tiles + it * stage_bytes + kTileBytesW, &g.tm_x, &sm->full[it], (kb0 + it) * kBlockK,
                             token0, kEvictLast);
@@ -201,7 +214,6 @@ __global__ void __launch_bounds__(kFusedThreads, 2) rowpar_kernel(const __grid_c
     pdl_wait();
     if (g.splits > 1 && !g.cluster) __threadfence();
     __syncthreads();
-    if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 5] = globaltimer();
     if (warp == 2) {
         tcgen05_fence_after();
         tmem_dealloc(tmem, cols);
@@ -350,7 +362,12 @@ int rowpar_stages(int m) {  // m: tokens per tile
     // the next kernel of a stream (a programmatic dependent launch) can then move in, build its barriers and prefetch
     // its first weight slabs while this kernel's CTAs sit in the NVLink waits of the reduction.
     const int stage = kTileBytesW + m * kBlockK * 2;
-    int stages = (m <= 128 ? 100 * 1024 : kSmemBudget) / stage;
+    static const int small_tile_kb = [] {
+        const char* e = getenv("DLMRT_SMALL_TILE_SMEM_KB");  // tuning knob: ring budget for tiles of up to 128 tokens
+        const int v = e ? atoi(e) : 0;
+        return v >= 48 && v <= 200 ? v : 100;
+    }();
+    int stages = (m <= 128 ? small_tile_kb * 1024 : kSmemBudget) / stage;
     if (stages > kMaxStages) stages = kMaxStages;
     return stages;
 }

@@ -89,7 +89,7 @@ typedef struct DlmComm {
     int32_t* status;               /* [DLM_STATUS_WORDS] int32 device words, zero-initialised, or NULL */
     int64_t* stamps;               /* [grid, DLM_STAMP_SLOTS] int64 %globaltimer phase stamps per CTA, or NULL
                                       (tp_comm.cu:121): 0 start, 1 pushed, 2 owned rows broadcast, 3 collected; fused
-                                      kernels also 4 accumulator ready, 5 partial tile written, 6 tile summed+pushed,
+                                      kernels also 4 accumulator ready, 5 dependency wait returned, 6 tile summed+pushed,
                                       7 kernel entry */
     int64_t timeout_ns;            /* budget of every device wait; 0 = 2 s */
     int32_t pdl;                   /* launch as a programmatic dependent launch (tp_comm.cu:304-309) */
