@@ -1,5 +1,7 @@
 // extern "C" boundary of libdlmrt_b200.so (include/dlmrt_b200.h): argument checks, tensor-map construction, launch.
 // Mirrors the host checks of the reference's launch<> (dlmrt/ops/csrc/tp_comm.cu:282-287) as return codes.
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "../../include/dlmrt_b200.h"
@@ -126,11 +128,6 @@ int make_map(CUtensorMap* map, const void* base, int rows, int cols, long long l
     return DLM_OK;
 }
 
-// Picks (token tiles, K splits) for a [m, n, k] GEMM on `avail` CTAs with a small cost model, in microseconds:
-// a CTA streams ceil(nkb / S) k-blocks of (16 KB of W + tokens-per-tile x 128 B of x) at what one SM pulls from L2,
-// never faster than the whole weight shard streams from HBM; several splits add the partial-tile round trip through L2
-// and the rendezvous. Token tiles re-read W from L2 but need no rendezvous, which wins for short K (high TP degrees);
-// K splits win for long K (TP = 1).
 // Can the `splits` CTAs of each of `clusters` tiles run as co-resident thread-block clusters (partials exchanged through
 // distributed shared memory)? The partial tile must also fit over the drained pipeline stages.
 bool cluster_fits(int mt, int splits, int clusters) {
@@ -140,8 +137,17 @@ bool cluster_fits(int mt, int splits, int clusters) {
     return rowpar_max_clusters(mt, splits) >= clusters;
 }
 
-void choose_tiling(int m, int n, int k, int avail, int* tiles_out, int* splits_out, bool clusters = true, int ranks = 1) {
-    const double sm_bytes_per_us = 120e3, hbm_bytes_per_us = 6.0e6;
+// Picks (token tiles, K splits) for a [m, n, k] GEMM on `avail` CTAs with a cost model fitted to measurements on B200
+// (256 x 2560 outputs, K from 512 to 9728, every tiling; microseconds):
+//   4.8                          launch, prologue, first loads, epilogue and push
+//   + kb * (0.24 + 0.0009 * mt)  kb k-blocks per CTA; a k-block costs more the more tokens (mt) the tile holds
+//   + 0.4 + 0.022 * mt           if K is split: partial tiles through L2 and the rendezvous (a cluster: about 1)
+//   + ceil(R / CTAs) * 1.3       owner phase of the reduction: each CTA takes its rows one after the other
+// and never less than the weight shard takes to stream from HBM. Long K (TP = 1) ends up split seven ways over 140 SMs,
+// short K (TP = 8) tiled along the tokens, in between a mix of both.
+void choose_tiling(int m, int n, int k, int avail, int* tiles_out, int* splits_out, bool clusters = false, int ranks = 1,
+                   int owner_rows = 0) {
+    const double hbm_bytes_per_us = 6.0e6;
     const int feature_tiles = n / kBlockF, nkb = k / kBlockK;
     double best = 1e30;
     *tiles_out = 1;
@@ -151,17 +157,15 @@ void choose_tiling(int m, int n, int k, int avail, int* tiles_out, int* splits_o
         const int mt = m / t;
         if (feature_tiles * t > avail || feature_tiles * t > kMaxTiles) break;
         for (int sp = 1; sp <= kMaxSplits && sp <= nkb; ++sp) {
-            if (feature_tiles * t * sp > avail) break;
+            const int ctas = feature_tiles * t * sp;
+            if (ctas > avail) break;
             const int kb = (nkb + sp - 1) / sp;
-            double us = kb * (16384.0 + mt * 128.0) / sm_bytes_per_us;
+            double us = kb * (0.24 + 0.0009 * mt);
             const double hbm = static_cast<double>(n) * k * 2 / hbm_bytes_per_us;
             if (us < hbm) us = hbm;
-            if (sp > 1) {
-                // Meeting in distributed shared memory costs about a microsecond; through L2 (partial tiles written,
-                // fenced, counted, read back) about three plus the traffic.
-                if (clusters && cluster_fits(mt, sp, feature_tiles * t * ranks)) us += 1.0;
-                else us += 3.0 + 2.0 * mt * kBlockF * 4 / sm_bytes_per_us;
-            }
+            us += 4.8;
+            if (sp > 1) us += clusters && cluster_fits(mt, sp, feature_tiles * t * ranks) ? 1.0 : 0.4 + 0.022 * mt;
+            if (owner_rows > 0) us += ((owner_rows + ctas - 1) / ctas) * 1.3;
             if (us < best - 1e-9) {
                 best = us;
                 *tiles_out = t;
@@ -187,14 +191,22 @@ int check_gemm(const DlmGemm* g) {
 }
 
 // Fills the device-side GEMM block; returns the per-rank grid in *grid.
-int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid, int ranks = 1) {
+int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid, int ranks = 1, int owner_rows = 0) {
     std::memset(d, 0, sizeof(*d));
     const int avail = max_ctas > 0 && max_ctas < sms ? max_ctas : sms;
     const int feature_tiles = g->n / kBlockF, nkb = g->k / kBlockK;
     int token_tiles = g->token_tiles, splits = g->splits;
+    if (token_tiles == 0 && splits == 0) {
+        // Tuning aid: DLMRT_TILING="<token tiles>,<splits>" overrides the library's choice where the caller left both open.
+        if (const char* e = getenv("DLMRT_TILING")) {
+            int t = 0, sp = 0;
+            if (sscanf(e, "%d,%d", &t, &sp) == 2 && t > 0 && sp > 0 && sp <= kMaxSplits && g->m % (16 * t) == 0)
+                token_tiles = t, splits = sp;
+        }
+    }
     if (token_tiles == 0 || splits == 0) {
         int t = 1, sp = 1;
-        choose_tiling(g->m, g->n, g->k, avail, &t, &sp, g->use_cluster, ranks);
+        choose_tiling(g->m, g->n, g->k, avail, &t, &sp, g->use_cluster, ranks, owner_rows);
         if (token_tiles == 0 && splits == 0) {
             token_tiles = t;
             splits = sp;
@@ -344,7 +356,7 @@ int dlm_gemm_bf16_noalloc(const void* x, const void* w, void* out, int m, int n,
     g.workspace = scratch;
     if (g.splits == 0 || g.token_tiles == 0) {
         int t = 1, sp = 1;
-        choose_tiling(m, n, k, info.sms, &t, &sp, false);
+        choose_tiling(m, n, k, info.sms, &t, &sp);
         if (g.token_tiles == 0) g.token_tiles = g.splits == 0 ? t : 1;
         if (g.splits == 0) g.splits = token_tiles == 0 ? sp : 1;
         while (g.splits > 1 && kWorkspaceHeader + g.splits * per_split > DLM_NOALLOC_SCRATCH_BYTES) --g.splits;
@@ -382,7 +394,7 @@ int dlm_rowpar_bf16(const DlmGemm* gemm, const DlmComm* comm, dlm_stream_t strea
     RowparParams<1> p;
     std::memset(&p, 0, sizeof(p));
     int grid = 0;
-    rc = fill_gemm(&p.g[0], gemm, comm->max_ctas, info.sms, &grid);
+    rc = fill_gemm(&p.g[0], gemm, comm->max_ctas, info.sms, &grid, 1, comm->rows / comm->world);
     if (rc != DLM_OK) return rc;
     fill_comm(&p.c[0], comm);
     p.fused = 1;
@@ -530,7 +542,7 @@ int dlm_rowpar_bf16_loopback(const DlmGemm* gemm, const DlmComm* comm, int nrank
         if (gemm[i].m != gemm[0].m || gemm[i].n != gemm[0].n || gemm[i].k != gemm[0].k) return DLM_ERR_SHAPE;
         int cap = comm[0].max_ctas > 0 && comm[0].max_ctas < per_rank ? comm[0].max_ctas : per_rank;
         int gi = 0;
-        rc = fill_gemm(&p.g[i], &gemm[i], cap, per_rank, &gi, nranks);
+        rc = fill_gemm(&p.g[i], &gemm[i], cap, per_rank, &gi, nranks, comm[i].rows / comm[i].world);
         if (rc != DLM_OK) return rc;
         if (i > 0 && gi != grid) return DLM_ERR_SHAPE;
         grid = gi;

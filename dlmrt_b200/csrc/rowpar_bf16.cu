@@ -47,6 +47,10 @@ __device__ __forceinline__ uint32_t tmem_cols(int m) {
 
 }  // namespace
 
+// The early L2 prefetch pays where the next kernel's CTAs can start while this one still runs (narrow tiles, two CTAs
+// per SM); with 256-token tiles a CTA starts only when its SM is free and the stream is already bandwidth-bound.
+__device__ __forceinline__ bool getenv_prefetch(int, int mt) { return mt <= 128; }
+
 template <int NR>
 __global__ void __launch_bounds__(kFusedThreads, 2) rowpar_kernel(const __grid_constant__ RowparParams<NR> p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -71,19 +75,20 @@ __global__ void __launch_bounds__(kFusedThreads, 2) rowpar_kernel(const __grid_c
 
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     SmemLayout* sm = reinterpret_cast<SmemLayout*>(tiles + g.stages * stage_bytes);
-    const uint32_t cols = tmem_cols(mt);
+    const uint32_t cols = tmem_cols(mt);                 // columns of one accumulator
+    const int issuers = cols <= 128 && iters >= 2 ? 2 : 1;  // MMA-issuing threads, each with its own accumulator
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < g.stages; ++i) {
             mbar_init(&sm->full[i], 1);
             mbar_init(&sm->empty[i], 1);
         }
-        mbar_init(&sm->acc_full, 1);
+        mbar_init(&sm->acc_full, static_cast<uint32_t>(issuers));
         fence_barrier_init();
         if (!g.w_tiles) tma_prefetch_descriptor(&g.tm_w);
         tma_prefetch_descriptor(&g.tm_x);
     }
-    if (warp == 2) tmem_alloc(&sm->tmem_base, cols);
+    if (warp == 2) tmem_alloc(&sm->tmem_base, cols * issuers);
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
@@ -105,7 +110,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2) rowpar_kernel(const __grid_c
             }
             // The rest of this CTA's weight slab is pulled into L2 now, while the previous kernel of the stream is still
             // finishing: weights never depend on it, and the ring then refills at L2 latency instead of HBM latency.
-            if (iters > pre) {
+            if (iters > pre && getenv_prefetch(g.stages, mt)) {
                 if (g.w_tiles) {
                     bulk_prefetch_l2(g.w_tiles + (static_cast<size_t>(f) * nkb + kb0 + pre) * kTileBytesW,
                                      static_cast<uint32_t>(iters - pre) * kTileBytesW);
@@ -137,37 +142,46 @@ __global__ void __launch_bounds__(kFusedThreads, 2) rowpar_kernel(const __grid_c
             }
         }
         __syncwarp();  // lanes 1-31 must not run ahead to the block-wide barrier while lane 0 is still issuing
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == 3) {
+        // MMA issue. One thread feeds the tensor pipe; for narrow tiles its own instruction stream (barrier wait,
+        // descriptors, four MMAs, commit per k-block) is slower than the MMAs it issues, so tiles of up to 128 tokens
+        // get a second issuer with its own accumulator: warp 1 takes the even k-blocks, warp 3 the odd ones, and the
+        // epilogue adds the two accumulators.
+        const int who = warp == 1 ? 0 : 1;
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc_bf16(kBlockF, mt);
-            const uint64_t desc_hi = umma_desc_k128(tiles) & 0xFFFFFFFF00000000ull;
-            const uint32_t stage0 = smem_u32(tiles);
-            int st = 0;
-            uint32_t parity = 0;
-            for (int it = 0; it < iters; ++it) {
-                if (!mbar_wait(&sm->full[st], parity, pipeline_deadline)) {
-                    report(c.status, kErrTimeout, st, kPhasePipeline, 1);
-                    break;
-                }
-                tcgen05_fence_after();
-                const uint32_t base = stage0 + st * stage_bytes;
-                const uint64_t dw = desc_hi | ((base & 0x3FFFF) >> 4), dx = desc_hi | (((base + kTileBytesW) & 0x3FFFF) >> 4);
-#pragma unroll
-                for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
-                    // Advancing 16 BF16 = 32 bytes inside the swizzled row: +2 in the descriptor's 16-byte units.
-                    umma_bf16(tmem, dw + 2 * kk, dx + 2 * kk, idesc, (it | kk) != 0);
-                }
-                umma_commit(&sm->empty[st]);
-                if (++st == g.stages) st = 0, parity ^= 1;
+            if (who == 1) {
+                pdl_wait();
+                if (p.fused) sm->epoch = c.epochs[block];
+                if (g.splits > 1) sm->gen = g.gen[block];
             }
-            umma_commit(&sm->acc_full);
-        }
-        __syncwarp();
-    } else if (warp == 3) {
-        if (lane == 0) {
-            pdl_wait();
-            if (p.fused) sm->epoch = c.epochs[block];
-            if (g.splits > 1) sm->gen = g.gen[block];
+            if (who < issuers) {
+                const uint32_t idesc = umma_idesc_bf16(kBlockF, mt);
+                const uint64_t desc_hi = umma_desc_k128(tiles) & 0xFFFFFFFF00000000ull;
+                const uint32_t stage0 = smem_u32(tiles);
+                const uint32_t acc = tmem + who * cols;
+                int st = 0;
+                uint32_t parity = 0;
+                for (int it = 0; it < iters; ++it) {
+                    if ((it & (issuers - 1)) == who) {
+                        if (!mbar_wait(&sm->full[st], parity, pipeline_deadline)) {
+                            report(c.status, kErrTimeout, st, kPhasePipeline, 1);
+                            break;
+                        }
+                        tcgen05_fence_after();
+                        const uint32_t base = stage0 + st * stage_bytes;
+                        const uint64_t dw = desc_hi | ((base & 0x3FFFF) >> 4);
+                        const uint64_t dx = desc_hi | (((base + kTileBytesW) & 0x3FFFF) >> 4);
+#pragma unroll
+                        for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+                            // Advancing 16 BF16 = 32 bytes inside the swizzled row: +2 in the descriptor's 16-byte units.
+                            umma_bf16(acc, dw + 2 * kk, dx + 2 * kk, idesc, (it >= issuers) | (kk != 0));
+                        }
+                        umma_commit(&sm->empty[st]);
+                    }
+                    if (++st == g.stages) st = 0, parity ^= 1;
+                }
+                umma_commit(&sm->acc_full);
+            }
         }
         __syncwarp();
     } else if (warp >= 4) {
@@ -193,8 +207,16 @@ __global__ void __launch_bounds__(kFusedThreads, 2) rowpar_kernel(const __grid_c
         for (int chunk = half; chunk < mt / 16; chunk += 2) {
             uint32_t r[16];
             if (iters > 0 && ok) {
-                tmem_load_16(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + chunk * 16, r);
+                const uint32_t at = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + chunk * 16;
+                tmem_load_16(at, r);
                 tmem_load_wait();
+                if (issuers == 2) {
+                    uint32_t q[16];
+                    tmem_load_16(at + cols, q);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(q[j]));
+                }
             } else {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) r[j] = 0;
@@ -216,7 +238,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2) rowpar_kernel(const __grid_c
     __syncthreads();
     if (warp == 2) {
         tcgen05_fence_after();
-        tmem_dealloc(tmem, cols);
+        tmem_dealloc(tmem, cols * issuers);
     }
 
     CommCtx x{};
@@ -358,14 +380,13 @@ __global__ void __launch_bounds__(kFusedThreads, 2) rowpar_kernel(const __grid_c
 }
 
 int rowpar_stages(int m) {  // m: tokens per tile
-    // Up to 128 tokens per tile the ring is kept under half of an SM's shared memory, so that two CTAs fit on one SM:
-    // the next kernel of a stream (a programmatic dependent launch) can then move in, build its barriers and prefetch
-    // its first weight slabs while this kernel's CTAs sit in the NVLink waits of the reduction.
+    // The ring takes what an SM has. (A half-SM ring for narrow tiles, which lets the next kernel of the stream move in
+    // early as a programmatic dependent launch, measured slower than the deeper ring: DLMRT_SMALL_TILE_SMEM_KB=100.)
     const int stage = kTileBytesW + m * kBlockK * 2;
     static const int small_tile_kb = [] {
         const char* e = getenv("DLMRT_SMALL_TILE_SMEM_KB");  // tuning knob: ring budget for tiles of up to 128 tokens
         const int v = e ? atoi(e) : 0;
-        return v >= 48 && v <= 200 ? v : 100;
+        return v >= 48 && v <= 200 ? v : 200;
     }();
     int stages = (m <= 128 ? small_tile_kb * 1024 : kSmemBudget) / stage;
     if (stages > kMaxStages) stages = kMaxStages;
