@@ -24,12 +24,7 @@ namespace dlm {
 
 constexpr int kMaxWorld = 8;
 constexpr int kEpochSlots = 256;
-#ifdef DLM_STAMP16
-constexpr int kStampSlots = 16;
-#else
-constexpr int kStampSlots = 8;
-#endif
-//  // %globaltimer stamps per CTA: 0 start, 1 pushed, 2 owned rows broadcast, 3 collected;
+constexpr int kStampSlots = 8; //  // %globaltimer stamps per CTA: 0 start, 1 pushed, 2 owned rows broadcast, 3 collected;
                                 // fused kernels add 4 accumulator ready, 5 dependency wait returned, 6 tile summed and pushed
 
 enum Mode { kReduce = 0, kReduceNorm = 1, kReduceNormResidual = 2 };

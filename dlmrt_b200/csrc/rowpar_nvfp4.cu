@@ -207,10 +207,14 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
             }
             if (!alive) break;
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == 2) {
+        // Two threads feed the tensor pipe: warp 1 takes this CTA's even work items, warp 2 the odd ones. Each item has
+        // its own accumulator buffer anyway (item & 1), and each issuer its own two sets of scale columns, so the two
+        // instruction streams never touch the same tensor memory. One thread alone is the bottleneck of the stream:
+        // per 256-element k-block it waits on a barrier, issues eight scale copies and four MMAs and commits. Ring
+        // position, phase and scale set advance by increments (no divisions); descriptors differ by constants.
+        const int who = warp - 1;
         if (lane == 0) {
-            // One thread feeds the tensor pipe, so its own instruction count per k-block matters: ring position, phase
-            // and scale-column set advance by increments (no divisions), descriptors differ by constants.
             const uint32_t stage0 = smem_u32(tiles);
             const uint64_t desc_hi = umma_desc_k128(tiles) & 0xFFFFFFFF00000000ull;     // swizzled operand tiles
             const uint64_t sf_hi = utccp_desc(tiles) & 0xFFFFFFFF00000000ull;           // scale atoms
@@ -218,12 +222,16 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
             uint32_t phase = 0;
             bool alive = true;
             for (int i = block; i < n_items && alive; i += blocks, ++item) {
+                if ((item & 1) != who) {  // the other issuer's item: only step over its k-blocks in the ring
+                    st += nkb;
+                    while (st >= g.stages) st -= g.stages, phase ^= 1;
+                    continue;
+                }
                 const int cnt = sm->rows[i / feature_tiles];
                 const uint32_t idesc = umma_idesc_nvfp4(kBlockF, max(16, (cnt + 15) & ~15));
-                const int buf = item & 1;
-                const uint32_t acc = tmem + kTmemAcc + buf * kItemRows;
+                const uint32_t acc = tmem + kTmemAcc + who * kItemRows;
                 // The accumulator buffer must have been read out by the epilogue of two items ago.
-                if (item >= 2 && !mbar_wait(&sm->acc_empty[buf], ((item >> 1) - 1) & 1, deadline)) {
+                if (item >= 2 && !mbar_wait(&sm->acc_empty[who], ((item >> 1) - 1) & 1, deadline)) {
                     report(c.status, kErrTimeout, 0, kPhasePipeline, 4);
                     break;
                 }
@@ -238,8 +246,8 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
                     const uint32_t base = stage0 + st * stage_bytes;
                     const uint64_t dw = desc_hi | ((base & 0x3FFFF) >> 4), da = desc_hi | (((base + off_a) & 0x3FFFF) >> 4);
                     const uint64_t fa = sf_hi | (((base + off_sfa) & 0x3FFFF) >> 4), fb = sf_hi | (((base + off_sfb) & 0x3FFFF) >> 4);
-                    const uint32_t sfa = tmem + kTmemSfa + set * 4 * kStepsPerBlock;
-                    const uint32_t sfb = tmem + kTmemSfb + set * 4 * kStepsPerBlock;
+                    const uint32_t sfa = tmem + kTmemSfa + (2 * who + set) * 4 * kStepsPerBlock;
+                    const uint32_t sfb = tmem + kTmemSfb + (2 * who + set) * 4 * kStepsPerBlock;
                     const int nsteps = min(kStepsPerBlock, steps - kb * kStepsPerBlock);
                     if (nsteps == kStepsPerBlock) {
 #pragma unroll
@@ -259,10 +267,10 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
                             umma_nvfp4(acc, dw + 2 * s2, da + 2 * s2, idesc, sfa + 4 * s2, sfb + 4 * s2, (kb | s2) != 0);
                     }
                     umma_commit(&sm->empty[st]);
-                    set = (set + 1) & (kSfSets - 1);
+                    set ^= 1;
                     if (++st == g.stages) st = 0, phase ^= 1;
                 }
-                if (alive) umma_commit(&sm->acc_full[buf]);
+                if (alive) umma_commit(&sm->acc_full[who]);
             }
         }
         __syncwarp();
@@ -311,9 +319,6 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
     }
     // Every Y row this CTA produced is written; announce it and wait for the rest of the grid (the combine reads rows
     // written by other CTAs). Counters are banked by launch generation as in the BF16 kernel.
-#ifdef DLM_STAMP16
-    if (c.stamps && lane == 0) c.stamps[block * kStampSlots + 11 + (warp == 0 ? 0 : warp == 1 ? 1 : warp == 3 ? 2 : warp == 4 ? 3 : 4)] = globaltimer();
-#endif
     __threadfence();
     tcgen05_fence_before();
     __syncthreads();
@@ -321,15 +326,9 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
     if (warp == 2) {
         tcgen05_fence_after();
         tmem_dealloc(tmem, kTmemCols);
-#ifdef DLM_STAMP16
-        if (c.stamps && lane == 0) c.stamps[block * kStampSlots + 8] = globaltimer();
-#endif
     }
     CommCtx x{};
     if (p.fused) x = comm_begin(c, block, blocks, sm->epoch);
-#ifdef DLM_STAMP16
-    if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 9] = globaltimer();
-#endif
     {
         const int gen = sm->gen + 1;
         int* counter = g.counters + (gen & 1) * kMaxTiles;
@@ -349,9 +348,6 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
                 __nanosleep(100);
             }
             for (int j = block; j < kEpochSlots; j += blocks) g.gen[j] = gen;
-#ifdef DLM_STAMP16
-            if (c.stamps) c.stamps[block * kStampSlots + 10] = globaltimer();
-#endif
         }
         __syncthreads();
     }
