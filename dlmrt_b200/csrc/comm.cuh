@@ -109,9 +109,11 @@ __device__ __forceinline__ void rearm(const CommDev& c, const CommCtx& x, int pa
 // Waits until the 16-byte vectors at base + s * stride (s < world) have all arrived and returns them. Every round
 // issues all pending loads before testing any (one L2 round trip per round, tp_comm.cu:52-54). Returns false when the
 // deadline passed first; the words of slots that did not arrive are then meaningless.
+// `pending` names the slots still to be waited for (the others already hold arrived data in v).
 __device__ __forceinline__ bool poll_all(const __nv_bfloat16* base, size_t stride, int world, uint4 (&v)[kMaxWorld],
-                                         const CommDev& c, const CommCtx& x, int phase) {
-    unsigned pending = (1u << world) - 1;
+                                         const CommDev& c, const CommCtx& x, int phase, unsigned pending = ~0u) {
+    pending &= (1u << world) - 1;
+    if (!pending) return true;
     while (true) {
         const unsigned was = pending;
 #pragma unroll
@@ -154,6 +156,10 @@ __device__ __forceinline__ void own_and_collect(const CommDev& c, const CommCtx&
     const size_t col = static_cast<size_t>(active ? t : 0) * kVec;
     const __nv_bfloat16* mine = c.recv[c.rank] + x.buf * x.buf_elems;
     uint4 slots[kMaxWorld];
+    // With one or two ranks a CTA may own several rows (R > CTAs): the next row's slots are then read early, while
+    // this row is being normalised, so that consecutive rows do not each pay a full round trip to L2.
+    uint4 early[2];
+    bool have_early = false;
     for (int r = x.block; r < c.R; r += x.blocks) {
         const size_t off = static_cast<size_t>(c.rank * c.R + r) * c.n + col;
         // Local operands first, so their latency overlaps the wait for the peers (tp_comm.cu:225-228).
@@ -161,7 +167,26 @@ __device__ __forceinline__ void own_and_collect(const CommDev& c, const CommCtx&
         if (MODE == kReduceNormResidual && active) hraw = *reinterpret_cast<const uint4*>(c.h + off);
         if (MODE != kReduce && active) wraw = *reinterpret_cast<const uint4*>(c.weight + col);
         bool ok = true;
-        if (active) ok = poll_all(mine + static_cast<size_t>(r) * c.n + col, x.slot_elems, c.world, slots, c, x, kPhaseReceive);
+        if (active) {
+            unsigned pending = ~0u;
+            if (have_early) {
+                pending = 0;
+#pragma unroll
+                for (int s = 0; s < 2; ++s) {
+                    if (s < c.world) {
+                        slots[s] = early[s];
+                        if (!arrived(early[s])) pending |= 1u << s;
+                    }
+                }
+            }
+            ok = poll_all(mine + static_cast<size_t>(r) * c.n + col, x.slot_elems, c.world, slots, c, x, kPhaseReceive, pending);
+            have_early = c.world <= 2 && r + x.blocks < c.R;
+            if (have_early) {
+#pragma unroll
+                for (int s = 0; s < 2; ++s)
+                    if (s < c.world) early[s] = load_volatile(mine + static_cast<size_t>(r + x.blocks) * c.n + col + s * x.slot_elems);
+            }
+        }
         float v[kVec] = {};
         if (active) {
 #pragma unroll

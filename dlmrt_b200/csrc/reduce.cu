@@ -11,8 +11,10 @@ long long g_launches = 0;
 
 // NR = 1: one rank per GPU (production). NR = 8: up to eight ranks emulated by one launch on one GPU, rank slot =
 // blockIdx.y; the grid is launched cooperatively so that all ranks' CTAs are resident together.
-template <int NR>
-__global__ void __launch_bounds__(1024, 1) reduce_kernel(const __grid_constant__ ReduceParams<NR> p) {
+// MAXT: 512 for hidden sizes up to 4096 (blocks of hidden / 8 threads), where the compiler may then use 128 registers
+// per thread; 1024 for the rest.
+template <int NR, int MAXT>
+__global__ void __launch_bounds__(MAXT, 1) reduce_kernel(const __grid_constant__ ReduceParams<NR> p) {
     const int slot = NR == 1 ? 0 : static_cast<int>(blockIdx.y);
     const CommDev& c = p.c[slot];
     __shared__ float scratch[32];
@@ -48,7 +50,8 @@ static int launch_impl(const ReduceParams<NR>& p, dim3 grid, int threads, const 
     }
     config.attrs = attrs;
     config.numAttrs = n;
-    const cudaError_t err = cudaLaunchKernelEx(&config, reduce_kernel<NR>, p);
+    const cudaError_t err = threads <= 512 ? cudaLaunchKernelEx(&config, reduce_kernel<NR, 512>, p)
+                                           : cudaLaunchKernelEx(&config, reduce_kernel<NR, 1024>, p);
     if (err != cudaSuccess) {
         g_last_cuda_error = static_cast<int>(err);
         (void)cudaGetLastError();

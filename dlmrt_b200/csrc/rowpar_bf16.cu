@@ -52,7 +52,7 @@ __device__ __forceinline__ uint32_t tmem_cols(int m) {
 __device__ __forceinline__ bool getenv_prefetch(int, int mt) { return mt <= 128; }
 
 template <int NR>
-__global__ void __launch_bounds__(kFusedThreads, 2) rowpar_kernel(const __grid_constant__ RowparParams<NR> p) {
+__global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_constant__ RowparParams<NR> p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const int slot = NR == 1 ? 0 : static_cast<int>(blockIdx.y);
     const GemmDev& g = p.g[slot];
