@@ -148,7 +148,7 @@ bool cluster_fits(int mt, int splits, int clusters) {
 void choose_tiling(int m, int n, int k, int avail, int* tiles_out, int* splits_out, bool clusters = false, int ranks = 1,
                    int owner_rows = 0) {
     const double hbm_bytes_per_us = 6.0e6;
-    const int feature_tiles = n / kBlockF, nkb = k / kBlockK;
+    const int feature_tiles = n / kBlockF, nkb = (k + kBlockK - 1) / kBlockK;
     double best = 1e30;
     *tiles_out = 1;
     *splits_out = 1;
@@ -179,7 +179,7 @@ int check_gemm(const DlmGemm* g) {
     if (g == nullptr) return DLM_ERR_NULL;
     if (g->x == nullptr || g->w == nullptr || g->workspace == nullptr) return DLM_ERR_NULL;
     if (g->m < 16 || g->m > DLM_MAX_M || g->m % 16) return DLM_ERR_SHAPE;
-    if (g->n < kBlockF || g->n % kBlockF || g->k < kBlockK || g->k % kBlockK) return DLM_ERR_SHAPE;
+    if (g->n < kBlockF || g->n % kBlockF || g->k < kBlockK || g->k % 8) return DLM_ERR_SHAPE;
     if (g->n / kBlockF > 64) return DLM_ERR_SHAPE;
     if (g->ldx < g->k || g->ldx % 8 || (!g->w_tiled && (g->ldw < g->k || g->ldw % 8))) return DLM_ERR_ALIGN;
     if (g->w_tiled < 0 || g->w_tiled > 1 || g->use_cluster < 0 || g->use_cluster > 1) return DLM_ERR_SHAPE;
@@ -194,7 +194,7 @@ int check_gemm(const DlmGemm* g) {
 int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid, int ranks = 1, int owner_rows = 0) {
     std::memset(d, 0, sizeof(*d));
     const int avail = max_ctas > 0 && max_ctas < sms ? max_ctas : sms;
-    const int feature_tiles = g->n / kBlockF, nkb = g->k / kBlockK;
+    const int feature_tiles = g->n / kBlockF, nkb = (g->k + kBlockK - 1) / kBlockK;
     int token_tiles = g->token_tiles, splits = g->splits;
     if (token_tiles == 0 && splits == 0) {
         // Tuning aid: DLMRT_TILING="<token tiles>,<splits>" overrides the library's choice where the caller left both open.
@@ -562,8 +562,7 @@ size_t dlm_workspace_bytes(int m, int n, int k) {
 
 int dlm_choose_tiling(int m, int n, int k, int max_ctas, int* token_tiles, int* splits) {
     if (token_tiles == nullptr || splits == nullptr) return DLM_ERR_NULL;
-    if (m < 16 || m > DLM_MAX_M || m % 16 || n < kBlockF || n % kBlockF || k < kBlockK || k % kBlockK)
-        return DLM_ERR_SHAPE;
+    if (m < 16 || m > DLM_MAX_M || m % 16 || n < kBlockF || n % kBlockF || k < kBlockK || k % 8) return DLM_ERR_SHAPE;
     DeviceInfo info;
     int sms = 148;
     if (device_info(&info) == DLM_OK) sms = info.sms;

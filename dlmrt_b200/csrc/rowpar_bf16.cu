@@ -67,7 +67,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
     const int f = tile / g.token_tiles, t = tile - f * g.token_tiles;
     const int mt = g.m / g.token_tiles;  // tokens of this tile: the MMA's N
     const int token0 = t * mt;
-    const int nkb = g.k / kBlockK;
+    const int nkb = (g.k + kBlockK - 1) / kBlockK;  // a ragged last k-block is zero-filled (TMA out-of-bounds fill, padded tiles)
     const int kb0 = static_cast<int>(static_cast<long long>(s) * nkb / g.splits);
     const int kb1 = static_cast<int>(static_cast<long long>(s + 1) * nkb / g.splits);
     const int iters = kb1 - kb0;

@@ -109,10 +109,10 @@ class LoopbackWorld:
         self._done(chain, outs)
         return outs
 
-    def moe(self, descriptors, *, site, chain=0):
+    def moe(self, descriptors, *, site, chain=0, hs=None, weight=None, eps=0.0, scale=1.0):
         """All ranks of the fused NVFP4 expert down-projection + reduction in one launch; descriptors[r] is rank r's
         DlmMoe (dlmrt_b200.quantization.nvfp4.descriptor)."""
-        comms, outs = self._comms(descriptors[0].m, descriptors[0].n, site, chain, None, None, 0.0, 1.0)
+        comms, outs = self._comms(descriptors[0].m, descriptors[0].n, site, chain, hs, weight, eps, scale)
         moes = (DlmMoe * self.world)(*descriptors)
         stream = torch.cuda.current_stream(self.device).cuda_stream
         _lib.check(_lib.lib().dlm_rowpar_nvfp4_moe_loopback(moes, comms, self.world, stream), f"loopback moe {site}")

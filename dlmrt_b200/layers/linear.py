@@ -24,8 +24,11 @@ def tile_weight(weight):
     tile row r sits at chunk position c ^ (r % 8)). One bulk copy then brings a tile in, and a CTA's weight slab is a
     contiguous run of HBM instead of 128-byte pieces a row pitch apart."""
     n, k = weight.shape
-    if n % 128 or k % 64:
-        raise ValueError(f"weight {tuple(weight.shape)}: N must be a multiple of 128 and K of 64")
+    if n % 128 or k % 8:
+        raise ValueError(f"weight {tuple(weight.shape)}: N must be a multiple of 128 and K of 8")
+    if k % 64:  # a ragged last k-block is padded with zeros to a whole tile
+        weight = torch.nn.functional.pad(weight, (0, 64 - k % 64))
+        k = weight.shape[1]
     t = weight.reshape(n // 128, 128, k // 64, 8, 8).permute(0, 2, 1, 3, 4)  # (tile row, tile col, r, chunk, 8 elems)
     r = torch.arange(128, device=weight.device).view(128, 1)
     c = torch.arange(8, device=weight.device).view(1, 8)
@@ -36,17 +39,21 @@ def tile_weight(weight):
 class Linear:
     """y = x @ W^T, BF16 in and out, FP32 accumulation in increasing K (K ranges summed in order when split)."""
 
-    def __init__(self, weight, fp8=False, b200=False, group=None, tiled=True):
+    def __init__(self, weight, fp8=False, b200=False, group=None, tiled=True, nn=False):
         if fp8:
             raise NotImplementedError("FP8 linears are not part of the row-parallel BF16 path")
         if weight.dtype != torch.bfloat16 or weight.dim() != 2:
             raise ValueError("weight must be a BF16 [N, K] matrix")
+        # `nn`: the weight is [K, N] (y = x @ W), as the tied embedding is for the self-conditioning soft-embedding
+        # GEMM of the reference (dlmrt/models/sdar/model.py:196-203, torch.mm(probs, E)); it is re-laid as [N, K] once.
+        if nn:
+            weight = weight.t()
         self.n, self.k = weight.shape
         self.fp8 = False
         self.b200 = False  # the SM 12.x emulation switch of the reference has no meaning on a B200
         self.weight = weight.contiguous()
         # `tiled`: stream a re-laid copy of the weight (see tile_weight) instead of the row-major matrix.
-        self.tiles = tile_weight(self.weight) if tiled and self.n % 128 == 0 and self.k % 64 == 0 else None
+        self.tiles = tile_weight(self.weight) if tiled and self.n % 128 == 0 and self.k % 8 == 0 else None
         self.group = group
         self._workspace = None
         _lib.lib()

@@ -94,19 +94,24 @@ def descriptor(act_codes, act_scales, amap, counts, experts, ids, weights, buffe
 
 
 def moe_down(act_codes, act_scales, amap, counts, experts, ids, weights, buffers, out, num_experts, shared=None,
-             group=None, site=None, chain=0):
+             group=None, site=None, chain=0, h=None, norm_weight=None, eps=0.0, scale=1.0):
     """out = sum over each token's experts in this rank's [lo, lo + count) of weight * expert_down(activation)
     [+ shared], BF16; with `group`, the sum over ranks of that, in the call site's buffer (one fused launch).
 
     `act_codes` [count * m_max, F / 2] uint8 and `act_scales` [count * m_max, F / 16] E4M3: GEMM2's quantised input in
     expert-major slots; `amap` [num_experts, m_max] / `counts` [num_experts] the slot map of the router; `ids` int32 /
-    `weights` FP32 [rows, top_k] hold global expert ids and the BF16-rounded routing weights."""
+    `weights` FP32 [rows, top_k] hold global expert ids and the BF16-rounded routing weights.
+
+    With `group` and `norm_weight` the owner rows are also normalised before the all-gather, and with `h` added to the
+    residual stream first, exactly as `Group.reduce_norm` does: the row kernel that follows the reduction in the
+    reference (`rmsnorm(h, weight, delta=reduced)`, dlmrt/ops/triton/core.py:29-56) folded into the same launch."""
     m = descriptor(act_codes, act_scales, amap, counts, experts, ids, weights, buffers, num_experts, shared)
     stream = torch.cuda.current_stream(act_codes.device).cuda_stream
     if group is None:
         _lib.check(_lib.lib().dlm_moe_nvfp4(C.byref(m), out.data_ptr(), out.stride(0), 1, stream), "moe_down")
         return out
-    comm, reduced = group._comm(m.m, m.n, site, chain, _lib.REDUCE, None, None, 0.0, 1.0)
+    mode = _lib.REDUCE if norm_weight is None else _lib.REDUCE_NORM_RESIDUAL if h is not None else _lib.REDUCE_NORM
+    comm, reduced = group._comm(m.m, m.n, site, chain, mode, h, norm_weight, eps, scale)
     _lib.check(_lib.lib().dlm_rowpar_nvfp4_moe(C.byref(m), C.byref(comm), stream), f"moe_down {site}")
     group._last[chain] = reduced
     return reduced

@@ -101,7 +101,8 @@ typedef struct DlmComm {
 typedef struct DlmGemm {
     const void* x;   /* [m, k] BF16, leading dimension ldx elements */
     const void* w;   /* [n, k] BF16, leading dimension ldw elements */
-    int32_t m, n, k; /* m % 16 == 0, 16 <= m <= 256; n % 128 == 0; k % 64 == 0 */
+    int32_t m, n, k; /* m % 16 == 0, 16 <= m <= 256; n % 128 == 0; k % 8 == 0, k >= 64 (a last k-block shorter than 64 is
+                        zero-filled; pre-tiled weights are padded to whole tiles) */
     int64_t ldx, ldw;/* multiples of 8 */
     void* workspace; /* dlm_workspace_bytes(m, n, k) bytes, zero-initialised once, 256-byte aligned; one per chain
                         (split-K partial tiles, arrival counters and a launch generation live in it) */
@@ -109,8 +110,8 @@ typedef struct DlmGemm {
     int32_t splits;  /* K splits across CTAs, 0 = chosen by the library; FP32 partial tiles are summed in split
                         order, so the result does not depend on scheduling */
     int32_t token_tiles; /* tiles along m (each m / token_tiles tokens, a multiple of 16), 0 = chosen by the library */
-    int32_t w_tiled; /* 0: w is row-major [n, k] (ldw). 1: w is pre-tiled for streaming, [n / 128][k / 64] tiles of
-                        128 rows x 64 BF16 (16 KB, contiguous), the 16-byte chunk c of tile row r stored at chunk
+    int32_t w_tiled; /* 0: w is row-major [n, k] (ldw). 1: w is pre-tiled for streaming, [n / 128][ceil(k / 64)] tiles of
+                        128 rows x 64 BF16 (16 KB, contiguous, K zero-padded), the 16-byte chunk c of tile row r stored at chunk
                         position c ^ (r % 8) (the 128-byte shared-memory swizzle); ldw is ignored. Weights are static,
                         so the layout is made once when they are loaded, as the reference re-lays its FP8 and NVFP4
                         weights (linear.py:30-31, nvfp4.py:104-112). */

@@ -91,7 +91,7 @@ def gemm(**kw):
 
 @pytest.mark.parametrize("kw, code", [
     (dict(m=8), _lib.ERR_SHAPE), (dict(m=272), _lib.ERR_SHAPE), (dict(m=40), _lib.ERR_SHAPE), (dict(n=192), _lib.ERR_SHAPE),
-    (dict(k=96), _lib.ERR_SHAPE), (dict(ldx=64), _lib.ERR_ALIGN), (dict(ldw=132), _lib.ERR_ALIGN),
+    (dict(k=100), _lib.ERR_SHAPE), (dict(k=56), _lib.ERR_SHAPE), (dict(ldx=64), _lib.ERR_ALIGN), (dict(ldw=132), _lib.ERR_ALIGN),
     (dict(x=0x1004), _lib.ERR_ALIGN), (dict(workspace=0x10010), _lib.ERR_ALIGN), (dict(w=None), _lib.ERR_NULL),
     (dict(splits=9), _lib.ERR_SHAPE), (dict(token_tiles=3), _lib.ERR_SHAPE), (dict(m=48, token_tiles=2), _lib.ERR_SHAPE),
 ])

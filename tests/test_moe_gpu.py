@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 import torch
 
-from gpu_util import assert_same_bits, bits
+from gpu_util import assert_norm_close, assert_same_bits, bits, randn_bf16
 from oracle import nvfp4 as onv
 from oracle import reduce as red
 from oracle.bf16 import bf16_to_f32, f32_to_bf16, to_torch
@@ -135,3 +135,27 @@ def test_expert_parallel_loopback_matches_oracle(world):
         want = red.reduce(np.stack(partials))
         for r, out in enumerate(outs):
             assert_same_bits(bits(out), want, f"rep {rep} rank {r}")
+
+
+def test_fused_residual_norm_after_the_experts():
+    """The reduction's residual + RMSNorm variants behind the expert kernel (the post-reduction row kernel folded into
+    the launch): residual stream bit-exact, normalised rows within one BF16 code point of the oracle."""
+    from dlmrt_b200.distributed.loopback import LoopbackWorld
+    from dlmrt_b200.quantization import nvfp4
+
+    world, rows, hidden, f, e_total, top_k = 2, 32, 2048, 512, 16, 4
+    case = make_case(rows, hidden, f, e_total, top_k, seed=21, exact=True)
+    e_local = e_total // world
+    lw = LoopbackWorld(world)
+    weight = randn_bf16(hidden, seed=3, std=0.1) + 1
+    hs = [randn_bf16(rows, hidden, seed=4 + r) for r in range(world)]
+    h_before = np.stack([bits(h) for h in hs])
+    keep = [device_args(case, r * e_local, e_local) for r in range(world)]
+    outs = lw.moe([nvfp4.descriptor(**a) for a in keep], site="moe.norm", hs=hs, weight=weight, eps=1e-6)
+    torch.cuda.synchronize()
+    lw.check()
+    partials = np.stack([oracle_out(case, r * e_local, e_local)[0] for r in range(world)])
+    want, h_after = red.reduce_norm(partials, bits(weight), 1e-6, 1.0, h_before)
+    for r in range(world):
+        assert_norm_close(bits(outs[r]), want, f"rank {r}")
+        assert_same_bits(bits(hs[r]), h_after[r], f"residual of rank {r}")

@@ -114,6 +114,21 @@ def test_gemm_token_tiles_and_splits_agree(token_tiles, splits):
     assert_same_bits(bits(out), want, "five launches on one workspace")
 
 
+@pytest.mark.parametrize("m, n, k, tiled", [(32, 256, 200, True), (32, 256, 200, False), (256, 2560, 18992, True)])
+def test_ragged_k_and_nn_layout(m, n, k, tiled):
+    """K that is not a multiple of 64 (the vocabulary shard of the self-conditioning soft-embedding GEMM: 151936 / 8 =
+    18992) and a [K, N] weight (`nn`), exact on integer operands."""
+    from dlmrt_b200.layers.linear import Linear
+
+    x, w = integer_case(m, n, k, seed=k)
+    want = f32_to_bf16(rowpar.gemm_f32(bits(x), bits(w)))
+    lin = Linear(w.t().contiguous(), nn=True, tiled=tiled)  # handed over as [K, N]
+    assert (lin.n, lin.k) == (n, k)
+    out = lin(x)
+    torch.cuda.synchronize()
+    assert_same_bits(bits(out), want, f"nn gemm {m}x{n}x{k}")
+
+
 def test_gemm_strided_operands():
     m, n, k = 32, 256, 256
     xs, ws = randn_bf16(m, 2 * k, seed=7), randn_bf16(n, 3 * k, seed=8)
