@@ -146,6 +146,97 @@ __device__ __forceinline__ float block_sum(float x, float* scratch, int threads)
     return x;
 }
 
+// block_sum of NROWS independent values at once (same tree for each, so each equals block_sum of it alone); `scratch`
+// holds 32 floats per value.
+template <int NROWS>
+__device__ __forceinline__ void block_sum_n(float (&x)[NROWS], float* scratch, int threads) {
+#pragma unroll
+    for (int i = 0; i < NROWS; ++i) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) x[i] += __shfl_xor_sync(0xffffffff, x[i], o);
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < NROWS; ++i) scratch[i * 32 + warp] = x[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < NROWS; ++i) {
+        x[i] = lane < (threads >> 5) ? scratch[i * 32 + lane] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) x[i] += __shfl_xor_sync(0xffffffff, x[i], o);
+    }
+    __syncthreads();  // scratch is reused by the next rows
+}
+
+// What an owner does with rows once it holds the rank-ordered FP32 sums `v[i]` of its thread's eight columns:
+// optional residual add and RMSNorm (tp_comm.cu:237-258), BF16 rounding, and the store into OUT on every rank.
+// NROWS rows go through the block-wide sums together. `off[i]` is the element offset of the thread's columns in row
+// i; rows with store[i] false are computed but not written (their inputs never arrived, or there is no such row).
+// All threads of the block must call it.
+template <int MODE, int NROWS>
+__device__ __forceinline__ void finish_rows(const CommDev& c, float (&v)[NROWS][kVec], const uint4 (&hraw)[NROWS],
+                                            uint4 wraw, const size_t (&off)[NROWS], bool active,
+                                            const bool (&store)[NROWS], float* scratch, int threads) {
+    if (MODE != kReduce) {
+        float ss[NROWS];
+#pragma unroll
+        for (int i = 0; i < NROWS; ++i) {
+            // The reduced sum is rounded to BF16 before the residual add, as an unfused all-reduce would hand it over.
+            const uint4 rounded = pack_bf16x8(v[i]);
+#pragma unroll
+            for (int j = 0; j < kVec; ++j) v[i][j] = 0.f;
+            add_bf16x8(v[i], rounded);
+            if (MODE == kReduceNormResidual) {
+                add_bf16x8(v[i], hraw[i]);
+                if (active && store[i]) *reinterpret_cast<uint4*>(c.h + off[i]) = pack_bf16x8(v[i]);
+            }
+            ss[i] = 0.f;
+#pragma unroll
+            for (int j = 0; j < kVec; ++j) ss[i] = fmaf(v[i][j], v[i][j], ss[i]);
+            if (!active) ss[i] = 0.f;
+        }
+        block_sum_n<NROWS>(ss, scratch, threads);
+        const __nv_bfloat162* w = reinterpret_cast<const __nv_bfloat162*>(&wraw);
+#pragma unroll
+        for (int i = 0; i < NROWS; ++i) {
+            const float rs = rsqrtf(ss[i] / c.n + c.eps) * c.scale;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(w[j]);
+                v[i][2 * j] = v[i][2 * j] * rs * f.x;
+                v[i][2 * j + 1] = v[i][2 * j + 1] * rs * f.y;
+            }
+        }
+    }
+    // Broadcast the rows: one multicast store, or one store per rank. A row whose inputs never arrived is not
+    // broadcast, so every rank's collect phase reports the failure too.
+#pragma unroll
+    for (int i = 0; i < NROWS; ++i) {
+        if (active && store[i]) {
+            const uint4 packed = pack_bf16x8(v[i]);
+            if (c.out_mc) {
+                multicast_store(c.out_mc + off[i], packed);
+            } else {
+                for (int s = 0; s < c.world; ++s) store_v4(c.out_peers[s] + off[i], packed);
+            }
+        }
+    }
+}
+
+template <int MODE>
+__device__ __forceinline__ void finish_row(const CommDev& c, float (&v)[kVec], uint4 hraw, uint4 wraw, size_t off,
+                                           bool active, bool ok, float* scratch, int threads) {
+    float vv[1][kVec];
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) vv[0][j] = v[j];
+    const uint4 hh[1] = {hraw};
+    const size_t oo[1] = {off};
+    const bool st[1] = {ok};
+    finish_rows<MODE, 1>(c, vv, hh, wraw, oo, active, st, scratch, threads);
+}
+
 // Owner phase + collect phase. Thread t < n / 8 holds columns [8t, 8t + 8) of the row being reduced; threads beyond
 // that only take part in the block-wide synchronisation. `scratch` is 32 floats of shared memory.
 template <int MODE>
@@ -193,39 +284,7 @@ __device__ __forceinline__ void own_and_collect(const CommDev& c, const CommCtx&
             for (int s = 0; s < kMaxWorld; ++s)
                 if (s < c.world) add_bf16x8(v, slots[s]);
         }
-        if (MODE != kReduce) {
-            // The reduced sum is rounded to BF16 before the residual add, as an unfused all-reduce would hand it over.
-            const uint4 rounded = pack_bf16x8(v);
-#pragma unroll
-            for (int i = 0; i < kVec; ++i) v[i] = 0.f;
-            add_bf16x8(v, rounded);
-            if (MODE == kReduceNormResidual) {
-                add_bf16x8(v, hraw);
-                if (active && ok) *reinterpret_cast<uint4*>(c.h + off) = pack_bf16x8(v);
-            }
-            float ss = 0.f;
-#pragma unroll
-            for (int i = 0; i < kVec; ++i) ss = fmaf(v[i], v[i], ss);
-            if (!active) ss = 0.f;
-            const float rs = rsqrtf(block_sum(ss, scratch, threads) / c.n + c.eps) * c.scale;
-            const __nv_bfloat162* w = reinterpret_cast<const __nv_bfloat162*>(&wraw);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 f = __bfloat1622float2(w[i]);
-                v[2 * i] = v[2 * i] * rs * f.x;
-                v[2 * i + 1] = v[2 * i + 1] * rs * f.y;
-            }
-        }
-        // Broadcast the row: one multicast store, or one store per rank. A row whose inputs never arrived is not
-        // broadcast, so every rank's collect phase reports the failure too.
-        if (active && ok) {
-            const uint4 packed = pack_bf16x8(v);
-            if (c.out_mc) {
-                multicast_store(c.out_mc + off, packed);
-            } else {
-                for (int s = 0; s < c.world; ++s) store_v4(c.out_peers[s] + off, packed);
-            }
-        }
+        finish_row<MODE>(c, v, hraw, wraw, off, active, ok, scratch, threads);
     }
     stamp(c, x, 2);
     // Collect: rows s * R + r of this rank's OUT copy, from every owner s. With one rank every row of OUT was stored

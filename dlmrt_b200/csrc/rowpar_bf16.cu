@@ -34,7 +34,7 @@ struct SmemLayout {
     uint64_t acc_full;
     uint32_t tmem_base;
     int epoch, gen;  // epochs[block] and gen[block], fetched by a spare warp while the pipeline runs
-    float scratch[32];
+    float scratch[64];
 };
 
 constexpr int kTileBytesW = kBlockF * kBlockK * 2;  // 16 KB
@@ -46,6 +46,110 @@ __device__ __forceinline__ uint32_t tmem_cols(int m) {
 }
 
 }  // namespace
+
+// Owner phase of a single rank whose K was split: CTA `block` owns rows block, block + blocks, ... and takes them two
+// at a time (their loads and block-wide sums overlap). For each it waits until every CTA of the row's token tile has
+// announced its partial tile, sums the row's FP32 split partials in split order, rounds to BF16 (that is the rank's
+// partial, as the push path would have stored it) and finishes the row as any owner does. Thread t < n / 8 holds
+// columns [8t, 8t + 8): feature tile t / 16, 32 bytes of that tile's row. `scratch`: 64 floats.
+template <int MODE>
+__device__ __forceinline__ void own_rows_from_splits(const GemmDev& g, const CommDev& c, const CommCtx& x,
+                                                     const int* counter, int mt, float* scratch) {
+    constexpr int kRows = 2;
+    constexpr int kGroup = 3;  // splits whose loads are in flight together (per row)
+    const int t = threadIdx.x;
+    const int threads = c.n / kVec;
+    const bool active = t < threads;
+    const int col = (active ? t : 0) * kVec;
+    const int f = col / kBlockF, j = col % kBlockF;
+    const int expected = (g.n / kBlockF) * g.splits;
+    const size_t split_stride = static_cast<size_t>(mt) * kBlockF;
+    uint4 wraw = make_uint4(0, 0, 0, 0);
+    if (MODE != kReduce && active) wraw = *reinterpret_cast<const uint4*>(c.weight + col);
+    int ready_tile = -1;  // rows are owned in increasing order, so token tiles are waited for in increasing order
+    bool ok = true;
+    for (int r0 = x.block; r0 < c.rows; r0 += kRows * x.blocks) {
+        size_t off[kRows];
+        uint4 hraw[kRows];
+        bool store[kRows];
+        const float* src[kRows];
+        int last_tile = 0;
+#pragma unroll
+        for (int i = 0; i < kRows; ++i) {
+            const int r = r0 + i * x.blocks;
+            store[i] = r < c.rows;
+            const int tt = store[i] ? r / mt : 0, token = store[i] ? r - tt * mt : 0;
+            off[i] = static_cast<size_t>(store[i] ? r : 0) * c.n + col;
+            hraw[i] = make_uint4(0, 0, 0, 0);
+            if (MODE == kReduceNormResidual && active && store[i]) hraw[i] = *reinterpret_cast<const uint4*>(c.h + off[i]);
+            src[i] = g.ws + (static_cast<size_t>(f) * g.token_tiles + tt) * g.splits * split_stride +
+                     static_cast<size_t>(token) * kBlockF + j;
+            if (store[i]) last_tile = tt;
+        }
+        if (ok && last_tile > ready_tile) {  // uniform over the block
+            if (t == 0) {
+                bool arrived_all = true;
+                for (int tt = ready_tile + 1; tt <= last_tile && arrived_all; ++tt) {
+                    int seen;
+                    do {
+                        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter + tt) : "memory");
+                        if (seen >= expected) break;
+                        if (globaltimer() > x.deadline) {
+                            report(c.status, kErrTimeout, tt, kPhasePipeline, 3);
+                            arrived_all = false;
+                            break;
+                        }
+                    } while (true);
+                }
+                scratch[0] = arrived_all ? 1.f : 0.f;
+            }
+            __syncthreads();
+            ok = scratch[0] != 0.f;
+            __syncthreads();  // scratch is reused by the block-wide sums
+            if (ok) ready_tile = last_tile;
+        }
+        float v[kRows][kVec] = {};
+        if (active && ok) {
+            float acc[kRows][kVec];
+            for (int base_sp = 0; base_sp < g.splits; base_sp += kGroup) {
+                float4 a[kRows][kGroup], b[kRows][kGroup];
+#pragma unroll
+                for (int i = 0; i < kRows; ++i) {
+#pragma unroll
+                    for (int u = 0; u < kGroup; ++u) {
+                        if (base_sp + u < g.splits && store[i]) {
+                            a[i][u] = __ldcg(reinterpret_cast<const float4*>(src[i] + (base_sp + u) * split_stride));
+                            b[i][u] = __ldcg(reinterpret_cast<const float4*>(src[i] + (base_sp + u) * split_stride) + 1);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < kRows; ++i) {
+#pragma unroll
+                    for (int u = 0; u < kGroup; ++u) {
+                        if (base_sp + u < g.splits && store[i]) {
+                            if (base_sp + u == 0) {
+                                acc[i][0] = a[i][u].x, acc[i][1] = a[i][u].y, acc[i][2] = a[i][u].z, acc[i][3] = a[i][u].w;
+                                acc[i][4] = b[i][u].x, acc[i][5] = b[i][u].y, acc[i][6] = b[i][u].z, acc[i][7] = b[i][u].w;
+                            } else {
+                                acc[i][0] += a[i][u].x, acc[i][1] += a[i][u].y, acc[i][2] += a[i][u].z, acc[i][3] += a[i][u].w;
+                                acc[i][4] += b[i][u].x, acc[i][5] += b[i][u].y, acc[i][6] += b[i][u].z, acc[i][7] += b[i][u].w;
+                            }
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < kRows; ++i)
+                if (store[i]) add_bf16x8(v[i], pack_bf16x8(acc[i]));  // +0.0f + partial: the rank-ordered sum over one rank
+        }
+#pragma unroll
+        for (int i = 0; i < kRows; ++i) store[i] = store[i] && ok;
+        finish_rows<MODE, kRows>(c, v, hraw, wraw, off, active, store, scratch, threads);
+    }
+    stamp(c, x, 2);
+    stamp(c, x, 3);
+}
 
 // The early L2 prefetch pays where the next kernel's CTAs can start while this one still runs (narrow tiles, two CTAs
 // per SM); with 256-token tiles a CTA starts only when its SM is free and the stream is already bandwidth-bound.
@@ -77,6 +181,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
     SmemLayout* sm = reinterpret_cast<SmemLayout*>(tiles + g.stages * stage_bytes);
     const uint32_t cols = tmem_cols(mt);                 // columns of one accumulator
     const int issuers = cols <= 128 && iters >= 2 ? 2 : 1;  // MMA-issuing threads, each with its own accumulator
+    // One rank, K split: the owner of a row sums the FP32 split partials itself (in split order), so the BF16 partial
+    // never travels through the receive slots; the value is the same, bit for bit, as pushing and summing one rank.
+    const bool local_rows = p.fused && c.world == 1 && g.splits > 1 && !g.cluster;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < g.stages; ++i) {
@@ -291,14 +398,23 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
             }
         }
         cluster_arrive();  // done reading the others' partials; the matching wait is at the very end of the kernel
+    } else if (local_rows) {
+        // Announce this CTA's partial tile on the counter of its token tile; the rows' owners wait for it below.
+        const int gen = sm->gen + 1;
+        if (threadIdx.x == 0) {
+            for (int j = block; j < kMaxTiles; j += blocks) g.counters[((gen + 1) & 1) * kMaxTiles + j] = 0;
+            atomicAdd(g.counters + (gen & 1) * kMaxTiles + t, 1);
+            for (int j = block; j < kEpochSlots; j += blocks) g.gen[j] = gen;
+        }
     } else if (g.splits > 1) {
         // Split-K rendezvous: every CTA of the tile announces its partial, waits for the others, then sums ITS share of
         // the tile's tokens over the splits in split order (so the value never depends on timing) and pushes it.
-        // Arrival counters alternate between two banks by launch generation; this launch clears the other bank.
+        // Arrival counters alternate between two banks by launch generation; this launch clears the whole other bank
+        // (whatever tiling the next launch on this workspace uses, it finds its counters at zero).
         const int gen = sm->gen + 1;
         int* counter = g.counters + (gen & 1) * kMaxTiles + tile;
         if (threadIdx.x == 0) {
-            if (s == 0) g.counters[((gen + 1) & 1) * kMaxTiles + tile] = 0;
+            for (int j = block; j < kMaxTiles; j += blocks) g.counters[((gen + 1) & 1) * kMaxTiles + j] = 0;
             atomicAdd(counter, 1);
             int seen;
             do {
@@ -369,7 +485,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
         stamp(c, x, 1);
         pdl_launch_dependents();
         rearm_early(c, x);
-        own_and_collect(c, x, sm->scratch);
+        if (local_rows) {
+            const int* counter = g.counters + ((sm->gen + 1) & 1) * kMaxTiles;
+            if (c.mode == kReduce) own_rows_from_splits<kReduce>(g, c, x, counter, mt, sm->scratch);
+            else if (c.mode == kReduceNorm) own_rows_from_splits<kReduceNorm>(g, c, x, counter, mt, sm->scratch);
+            else own_rows_from_splits<kReduceNormResidual>(g, c, x, counter, mt, sm->scratch);
+        } else {
+            own_and_collect(c, x, sm->scratch);
+        }
         rearm_late(c, x);
         comm_end(c, x);
     } else {

@@ -143,7 +143,8 @@ def test_gemm_strided_operands():
 
 @pytest.mark.parametrize("world, m, n, k, splits", [(1, 32, 2048, 2048, 0), (1, 256, 2560, 4096, 0), (2, 256, 2560, 9728, 3),
                                                      (2, 32, 2048, 2048, 2), (4, 256, 2816, 4096, 1), (8, 32, 2048, 2048, 1),
-                                                     (8, 256, 2048, 9728, 1), (4, 64, 2560, 1024, 0)])
+                                                     (8, 256, 2048, 9728, 1), (4, 64, 2560, 1024, 0),
+                                                     (1, 256, 2560, 9728, 7), (1, 64, 2048, 2048, 3), (1, 32, 2816, 4096, 4)])
 def test_fused_rowpar_loopback_matches_oracle(world, m, n, k, splits):
     """Fused projection + reduction over `world` emulated ranks: with exact (integer) operands the whole pipeline is
     bit-exact against the oracle; with Gaussian operands the reduction of this kernel's own GEMM partials is."""
@@ -188,6 +189,27 @@ def test_fused_rowpar_loopback_matches_oracle(world, m, n, k, splits):
         if mode == 2:
             for r in range(world):
                 assert_same_bits(bits(hs[r]), h_after[r], f"call {i}: residual of rank {r}")
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_alternating_tilings_share_one_workspace(world):
+    """Calls of one chain share the split-K workspace whatever their tiling: the arrival counters a launch finds must
+    be at zero even when the launches before it used more (or other) tiles."""
+    from dlmrt_b200.distributed.loopback import LoopbackWorld
+
+    lw = LoopbackWorld(world)
+    m, n, k = 64, 1024, 2048 * world
+    for i, (tt, sp) in enumerate([(2, 3), (1, 3), (2, 3), (1, 2), (2, 2), (1, 7 if world == 1 else 3), (2, 3), (1, 1), (2, 3)]):
+        x, w = integer_case(m, n, k, seed=50 + i)
+        xs = [t.contiguous() for t in x.chunk(world, 1)]
+        ws = [t.contiguous() for t in w.chunk(world, 1)]
+        outs = lw.rowpar(xs, ws, site=f"s{i}", splits=sp, token_tiles=tt)
+        torch.cuda.synchronize()
+        lw.check()
+        _, exact = rowpar.rowpar(bits(x), bits(w), world)
+        want = red.reduce(exact)
+        for r in range(world):
+            assert_same_bits(bits(outs[r]), want, f"call {i} (token tiles {tt}, splits {sp}) rank {r}")
 
 
 def test_linear_defers_into_group_reduce():
