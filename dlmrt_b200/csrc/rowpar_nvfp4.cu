@@ -62,6 +62,56 @@ int moe_stages(int rows_cap) {
     return s > kMaxStages ? kMaxStages : s;
 }
 
+// One output row of the combine step for thread t's eight columns: FP32 sum over the token's expert list, in list
+// order, of weight * y (fused multiply-add; experts of other ranks contribute 0 * 0), rounded to BF16, then the
+// shared expert's BF16 row added and rounded again (dlmrt/ops/triton/nvfp4_moe.py:134-150).
+__device__ __forceinline__ uint4 combine_row(const MoeDev& g, int row, int t) {
+    float acc[kVec] = {};
+    for (int k = 0; k < g.top_k; ++k) {
+        const int e = g.ids[row * g.top_k + k] - g.lo;
+        const bool local = e >= 0 && e < g.e_local;
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        float w = 0.f;
+        if (local) {
+            w = g.weights[row * g.top_k + k];
+            raw = __ldcg(reinterpret_cast<const uint4*>(g.y + static_cast<size_t>(row * g.top_k + k) * g.n) + t);
+        }
+        const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(b[i]);
+            acc[2 * i] = fmaf(w, f.x, acc[2 * i]);
+            acc[2 * i + 1] = fmaf(w, f.y, acc[2 * i + 1]);
+        }
+    }
+    uint4 packed = pack_bf16x8(acc);
+    if (g.shared) {
+        float v[kVec] = {};
+        add_bf16x8(v, packed);
+        add_bf16x8(v, *(reinterpret_cast<const uint4*>(g.shared + static_cast<size_t>(row) * g.n) + t));
+        packed = pack_bf16x8(v);
+    }
+    return packed;
+}
+
+// Single rank: combine each owned row and finish it (residual + RMSNorm by mode, store into OUT) in one go.
+template <int MODE>
+__device__ __forceinline__ void combine_and_finish(const MoeDev& g, const CommDev& c, int block, int blocks, float* scratch) {
+    const int t = threadIdx.x, threads = g.n / kVec;
+    const bool active = t < threads;
+    const int col = (active ? t : 0) * kVec;
+    uint4 wraw = make_uint4(0, 0, 0, 0);
+    if (MODE != kReduce && active) wraw = *reinterpret_cast<const uint4*>(c.weight + col);
+    for (int row = block; row < g.m; row += blocks) {
+        const size_t off = static_cast<size_t>(row) * c.n + col;
+        uint4 hraw = make_uint4(0, 0, 0, 0);
+        if (MODE == kReduceNormResidual && active) hraw = *reinterpret_cast<const uint4*>(c.h + off);
+        float v[kVec] = {};
+        if (active) add_bf16x8(v, combine_row(g, row, t));  // +0.0f + partial: the rank-ordered sum over one rank
+        finish_row<MODE>(c, v, hraw, wraw, off, active, true, scratch, threads);
+    }
+}
+
 template <int NR>
 __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_constant__ MoeParams<NR> p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -353,35 +403,18 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
     }
     if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 5] = globaltimer();
     // Combine: out[row] = bf16(sum over k in list order of w_k * y_k), experts of other ranks contribute 0 * 0.
-    {
+    // With one rank the sum over ranks is the identity and the CTA that combines a row is also its owner (rows block,
+    // block + blocks, ... in both roles), so the row is finished here and never travels through the receive slots.
+    const bool local_rows = p.fused && c.world == 1;
+    if (local_rows) {
+        if (c.mode == kReduce) combine_and_finish<kReduce>(g, c, block, blocks, sm->scratch);
+        else if (c.mode == kReduceNorm) combine_and_finish<kReduceNorm>(g, c, block, blocks, sm->scratch);
+        else combine_and_finish<kReduceNormResidual>(g, c, block, blocks, sm->scratch);
+    } else {
         const int t = threadIdx.x, threads = g.n / kVec;
         for (int row = block; row < g.m; row += blocks) {
             if (t < threads) {
-                float acc[kVec] = {};
-                for (int k = 0; k < g.top_k; ++k) {
-                    const int e = g.ids[row * g.top_k + k] - g.lo;
-                    const bool local = e >= 0 && e < g.e_local;
-                    uint4 raw = make_uint4(0, 0, 0, 0);
-                    float w = 0.f;
-                    if (local) {
-                        w = g.weights[row * g.top_k + k];
-                        raw = __ldcg(reinterpret_cast<const uint4*>(g.y + static_cast<size_t>(row * g.top_k + k) * g.n) + t);
-                    }
-                    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float2 f = __bfloat1622float2(b[i]);
-                        acc[2 * i] = fmaf(w, f.x, acc[2 * i]);
-                        acc[2 * i + 1] = fmaf(w, f.y, acc[2 * i + 1]);
-                    }
-                }
-                uint4 packed = pack_bf16x8(acc);
-                if (g.shared) {
-                    float v[kVec] = {};
-                    add_bf16x8(v, packed);
-                    add_bf16x8(v, *(reinterpret_cast<const uint4*>(g.shared + static_cast<size_t>(row) * g.n) + t));
-                    packed = pack_bf16x8(v);
-                }
+                const uint4 packed = combine_row(g, row, t);
                 if (p.fused) {
                     store_v4(push_address(c, x, row, t * kVec), packed);
                 } else {
@@ -394,7 +427,12 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
         stamp(c, x, 1);
         pdl_launch_dependents();
         rearm_early(c, x);
-        own_and_collect(c, x, sm->scratch);
+        if (local_rows) {
+            stamp(c, x, 2);
+            stamp(c, x, 3);
+        } else {
+            own_and_collect(c, x, sm->scratch);
+        }
         rearm_late(c, x);
         comm_end(c, x);
     } else {
