@@ -48,6 +48,18 @@ class DlmStatus(C.Structure):
                 ("epoch", C.c_int32)]
 
 
+class DlmLoopPart(C.Structure):
+    _fields_ = [("graph", C.c_void_p), ("flag", C.c_void_p)]
+
+
+class DlmLoop(C.Structure):
+    _fields_ = [("parts", C.POINTER(DlmLoopPart)), ("n_parts", C.c_int32), ("limit", C.c_int32),
+                ("remaining", C.c_void_p), ("step", C.c_void_p)]
+
+
+MAX_LOOPS, MAX_LOOP_PARTS = 8, 16
+
+
 class DlmError(RuntimeError):
     """A DLM_ERR_* return code from the library; `.code` holds it."""
 
@@ -81,6 +93,9 @@ SIGNATURES = {
     "dlm_device_sms": (C.c_int, []),
     "dlm_device_arch": (C.c_int, []),
     "dlm_launch_count": (C.c_int64, []),
+    "dlm_device_loop_create": (C.c_int, [C.c_void_p, C.POINTER(DlmLoop), C.c_int, C.c_void_p, C.POINTER(C.c_void_p)]),
+    "dlm_device_loop_launch": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "dlm_device_loop_destroy": (None, [C.c_void_p]),
 }
 
 

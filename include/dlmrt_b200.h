@@ -238,6 +238,42 @@ DLM_API int dlm_device_arch(void);
 /* Number of kernel launches this library has issued in this process (for the benchmark's gpu_launches). */
 DLM_API int64_t dlm_launch_count(void);
 
+/* ---- device-side loop around captured graphs ------------------------------------------------------------------
+ * Replaces the reference's block-graph module (dlmrt/ops/csrc/block_graph.cu: BlockGraph :29-77, LoopGraph :80-129,
+ * StagedLoopGraph :137-207, built by Engine._capture, dlmrt/models/sdar/engine.py:92-120): the captured stages of a
+ * block (begin, round, commit) are tied into ONE graph whose rounds are decided on the device,
+ *
+ *     head -> WHILE(*remaining > 0 && *step < limit){ part_0 -> part_1 -> ... } -> ... next loop ... -> tail
+ *
+ * A part with a non-NULL `flag` runs only in passes where *flag > 0 (an IF evaluated when the part is reached). The
+ * WHILE condition is evaluated before the first pass and after every pass, and one execution makes at most `limit`
+ * passes of a loop even if its body fails to advance *step (the GPU is never left spinning). Graph
+ * handles are cudaGraph_t values (torch: CUDAGraph(keep_graph=True).raw_cuda_graph()); they are cloned, so the
+ * caller may destroy them afterwards. `head` and `tail` may be NULL. The fused kernels of this library are loop-safe:
+ * all their state lives in device memory and advances with every execution, captured or not. */
+#define DLM_MAX_LOOPS 8
+#define DLM_MAX_LOOP_PARTS 16
+
+typedef struct DlmLoopPart {
+    void* graph;     /* cudaGraph_t of the part */
+    const int* flag; /* device int32; NULL = the part always runs */
+} DlmLoopPart;
+
+typedef struct DlmLoop {
+    const DlmLoopPart* parts;
+    int32_t n_parts;
+    int32_t limit;        /* upper bound on *step for the body to run */
+    const int* remaining; /* device int32, written by the body (work left) */
+    const int* step;      /* device int32, advanced by the body */
+} DlmLoop;
+
+typedef struct DlmDeviceLoop DlmDeviceLoop;
+
+DLM_API int dlm_device_loop_create(void* head, const DlmLoop* loops, int n_loops, void* tail, DlmDeviceLoop** out);
+/* One launch runs the whole program on `stream` (cudaStream_t). */
+DLM_API int dlm_device_loop_launch(DlmDeviceLoop* loop, void* stream);
+DLM_API void dlm_device_loop_destroy(DlmDeviceLoop* loop);
+
 #ifdef __cplusplus
 }
 #endif

@@ -105,6 +105,30 @@ def test_fused_requires_matching_shapes():
     assert _lib.lib().dlm_rowpar_bf16(C.byref(gemm(n=512)), C.byref(c), None) == _lib.ERR_SHAPE
 
 
+def test_device_loop_rejects_bad_programs_before_touching_cuda():
+    from dlmrt_b200._lib import DlmLoop, DlmLoopPart
+    from dlmrt_b200.ops.block_graph import BlockGraph, StagedLoopGraph
+
+    lib, out = _lib.lib(), C.c_void_p()
+    assert lib.dlm_device_loop_create(None, None, 1, None, C.byref(out)) == _lib.ERR_SHAPE
+    assert lib.dlm_device_loop_create(None, None, _lib.MAX_LOOPS + 1, None, C.byref(out)) == _lib.ERR_SHAPE
+    assert lib.dlm_device_loop_create(None, None, 0, None, None) == _lib.ERR_NULL
+    parts = (DlmLoopPart * 1)()
+    loop = (DlmLoop * 1)()
+    loop[0].parts, loop[0].n_parts, loop[0].limit = parts, 1, 4
+    assert lib.dlm_device_loop_create(None, loop, 1, None, C.byref(out)) == _lib.ERR_NULL  # no counters, no graph
+    loop[0].remaining = loop[0].step = 8
+    assert lib.dlm_device_loop_create(None, loop, 1, None, C.byref(out)) == _lib.ERR_NULL  # part without a graph
+    loop[0].limit = -1
+    assert lib.dlm_device_loop_create(None, loop, 1, None, C.byref(out)) == _lib.ERR_SHAPE
+    assert lib.dlm_device_loop_launch(None, None) == _lib.ERR_NULL
+    lib.dlm_device_loop_destroy(None)
+    with pytest.raises(_lib.DlmError):
+        BlockGraph(1, 0, 3, 8, 16, 4)  # no round graph
+    with pytest.raises(ValueError):
+        StagedLoopGraph(0, [], 8, 16, 4)
+
+
 def test_missing_library_is_an_import_error(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "_lib", None)
     monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "libdlmrt_b200.so")
