@@ -26,7 +26,8 @@ class DlmComm(C.Structure):
                 ("recv", C.c_void_p * MAX_WORLD), ("out", C.c_void_p), ("out_mc", C.c_void_p),
                 ("out_peers", C.c_void_p * MAX_WORLD), ("rearm", C.c_void_p), ("rearm_bytes", C.c_int64),
                 ("epochs", C.c_void_p), ("h", C.c_void_p), ("weight", C.c_void_p), ("status", C.c_void_p),
-                ("stamps", C.c_void_p), ("timeout_ns", C.c_int64), ("pdl", C.c_int32), ("max_ctas", C.c_int32)]
+                ("stamps", C.c_void_p), ("timeout_ns", C.c_int64), ("pdl", C.c_int32), ("max_ctas", C.c_int32),
+                ("one_shot", C.c_int32), ("reserved", C.c_int32), ("recv_mc", C.c_void_p)]
 
 
 class DlmGemm(C.Structure):

@@ -56,6 +56,9 @@ int check_comm(const DlmComm* c) {
             if (!aligned16(c->out_peers[s])) return DLM_ERR_ALIGN;
         }
     }
+    // One-shot: a plain sum only (the residual stream of modes 1 and 2 is kept per owner), and only between ranks.
+    if (c->one_shot != 0 && (c->one_shot != 1 || c->mode != DLM_REDUCE)) return DLM_ERR_SHAPE;
+    if (!aligned16(c->recv_mc)) return DLM_ERR_ALIGN;
     if (c->mode != DLM_REDUCE && c->weight == nullptr) return DLM_ERR_NULL;
     if (c->mode == DLM_REDUCE_NORM_RESIDUAL && c->h == nullptr) return DLM_ERR_NULL;
     if (!aligned16(c->out) || !aligned16(c->out_mc) || !aligned16(c->rearm) || !aligned16(c->h) || !aligned16(c->weight))
@@ -86,6 +89,9 @@ void fill_comm(CommDev* d, const DlmComm* c) {
     d->rows = c->rows;
     d->n = c->n;
     d->R = c->rows / c->world;
+    d->one_shot = c->one_shot != 0 && c->world > 1;
+    d->slot_rows = d->one_shot ? c->rows : d->R;
+    d->recv_mc = d->one_shot ? static_cast<__nv_bfloat16*>(c->recv_mc) : nullptr;
     d->mode = c->mode;
     d->eps = c->eps;
     d->scale = c->scale;

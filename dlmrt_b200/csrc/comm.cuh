@@ -12,6 +12,10 @@
 //             multimem.st through the NVSwitch, or one store per rank).
 //   collect   every CTA polls the rows of its own OUT copy that correspond to the rows it owned, so OUT is complete on
 //             this rank when the kernel ends.
+// One-shot variant (plain sums of small partials, c.one_shot): every rank stores its WHOLE partial into every rank's
+// slots [e % 3][rank][row] (one multimem.st per vector, or one store per rank) and every rank then sums all rows itself,
+// in the same rank order, into its own OUT: one NVLink hop instead of two, no broadcast, no collect; the result is
+// the same on every rank, bit for bit, because every rank adds the same BF16 partials in the same order.
 // Differences from the reference kernel, by design: there are no dedicated pusher CTAs (every CTA pushes, re-arms,
 // then owns rows, so a fused GEMM's tiles can be pushed by the CTA that produced them); address tables live in
 // kernel parameters; every wait is bounded and reports through status words instead of trapping; invocation
@@ -34,6 +38,7 @@ struct CommDev {
     __nv_bfloat16* out_peers[kMaxWorld];
     __nv_bfloat16* out;
     __nv_bfloat16* out_mc;
+    __nv_bfloat16* recv_mc;  // one-shot: multicast address of the receive buffer, or null (one store per rank)
     __nv_bfloat16* rearm;
     __nv_bfloat16* h;
     const __nv_bfloat16* weight;
@@ -43,6 +48,8 @@ struct CommDev {
     long long timeout_ns;
     int rearm_vecs;
     int rank, world, rows, n, R;
+    int one_shot;   // every rank receives every row and sums all rows itself
+    int slot_rows;  // rows of one sender's slot, = rows summed by this rank: R, or rows when one_shot
     int mode;
     float eps, scale;
 };
@@ -66,7 +73,7 @@ __device__ __forceinline__ CommCtx comm_begin(const CommDev& c, int block, int b
     x.e = previous + 1;
     x.buf = x.e % 3;
     x.deadline = globaltimer() + c.timeout_ns;
-    x.slot_elems = static_cast<size_t>(c.R) * c.n;
+    x.slot_elems = static_cast<size_t>(c.slot_rows) * c.n;
     x.buf_elems = static_cast<size_t>(c.world) * x.slot_elems;
     return x;
 }
@@ -75,6 +82,21 @@ __device__ __forceinline__ CommCtx comm_begin(const CommDev& c, int block, int b
 __device__ __forceinline__ __nv_bfloat16* push_address(const CommDev& c, const CommCtx& x, int row, int col) {
     const int s = row / c.R, r = row - s * c.R;
     return c.recv[s] + x.buf * x.buf_elems + c.rank * x.slot_elems + static_cast<size_t>(r) * c.n + col;
+}
+
+// Stores one 16-byte vector of this rank's partial (row, col) where the protocol wants it: into the owner's slot, or
+// (one-shot) into this rank's slot on every rank.
+__device__ __forceinline__ void push_store(const CommDev& c, const CommCtx& x, int row, int col, uint4 v) {
+    if (!c.one_shot) {
+        store_v4(push_address(c, x, row, col), v);
+        return;
+    }
+    const size_t off = x.buf * x.buf_elems + c.rank * x.slot_elems + static_cast<size_t>(row) * c.n + col;
+    if (c.recv_mc) {
+        multicast_store(c.recv_mc + off, v);
+    } else {
+        for (int s = 0; s < c.world; ++s) store_v4(c.recv[(c.rank + s) % c.world] + off, v);
+    }
 }
 
 // Push phase of the stand-alone reduction: the whole partial, spread over all threads of all CTAs of the rank.
@@ -87,9 +109,9 @@ __device__ __forceinline__ void push_partial(const CommDev& c, const CommCtx& x,
     for (int i = x.block * blockDim.x + threadIdx.x; i < total; i += stride) {
         const int l = i / vpr, col = (i - l * vpr) * kVec;
         const int r = l / c.world, s = (c.rank + l % c.world) % c.world;
-        const int row = s * c.R + r;
+        const int row = c.one_shot ? l : s * c.R + r;
         const uint4 v = *reinterpret_cast<const uint4*>(partial + static_cast<size_t>(row) * c.n + col);
-        store_v4(push_address(c, x, row, col), v);
+        push_store(c, x, row, col, v);
     }
 }
 
@@ -216,7 +238,9 @@ __device__ __forceinline__ void finish_rows(const CommDev& c, float (&v)[NROWS][
     for (int i = 0; i < NROWS; ++i) {
         if (active && store[i]) {
             const uint4 packed = pack_bf16x8(v[i]);
-            if (c.out_mc) {
+            if (c.one_shot) {
+                store_v4(c.out + off[i], packed);  // every rank computes every row: nothing to broadcast
+            } else if (c.out_mc) {
                 multicast_store(c.out_mc + off[i], packed);
             } else {
                 for (int s = 0; s < c.world; ++s) store_v4(c.out_peers[s] + off[i], packed);
@@ -251,8 +275,9 @@ __device__ __forceinline__ void own_and_collect(const CommDev& c, const CommCtx&
     // this row is being normalised, so that consecutive rows do not each pay a full round trip to L2.
     uint4 early[2];
     bool have_early = false;
-    for (int r = x.block; r < c.R; r += x.blocks) {
-        const size_t off = static_cast<size_t>(c.rank * c.R + r) * c.n + col;
+    const int first_row = c.one_shot ? 0 : c.rank * c.R;  // row of OUT that slot row 0 holds
+    for (int r = x.block; r < c.slot_rows; r += x.blocks) {
+        const size_t off = static_cast<size_t>(first_row + r) * c.n + col;
         // Local operands first, so their latency overlaps the wait for the peers (tp_comm.cu:225-228).
         uint4 hraw = make_uint4(0, 0, 0, 0), wraw = make_uint4(0, 0, 0, 0);
         if (MODE == kReduceNormResidual && active) hraw = *reinterpret_cast<const uint4*>(c.h + off);
@@ -271,7 +296,7 @@ __device__ __forceinline__ void own_and_collect(const CommDev& c, const CommCtx&
                 }
             }
             ok = poll_all(mine + static_cast<size_t>(r) * c.n + col, x.slot_elems, c.world, slots, c, x, kPhaseReceive, pending);
-            have_early = c.world <= 2 && r + x.blocks < c.R;
+            have_early = c.world <= 2 && r + x.blocks < c.slot_rows;
             if (have_early) {
 #pragma unroll
                 for (int s = 0; s < 2; ++s)
@@ -287,9 +312,9 @@ __device__ __forceinline__ void own_and_collect(const CommDev& c, const CommCtx&
         finish_row<MODE>(c, v, hraw, wraw, off, active, ok, scratch, threads);
     }
     stamp(c, x, 2);
-    // Collect: rows s * R + r of this rank's OUT copy, from every owner s. With one rank every row of OUT was stored
-    // by this very grid, so it is complete when the kernel ends and there is nothing to wait for.
-    if (active && c.world > 1) {
+    // Collect: rows s * R + r of this rank's OUT copy, from every owner s. With one rank, or one-shot, every row of
+    // OUT was stored by this very grid, so it is complete when the kernel ends and there is nothing to wait for.
+    if (active && c.world > 1 && !c.one_shot) {
         for (int r = x.block; r < c.R; r += x.blocks)
             if (!poll_all(c.out + static_cast<size_t>(r) * c.n + col, x.slot_elems, c.world, slots, c, x, kPhaseOut)) break;
     }
@@ -306,10 +331,10 @@ __device__ __forceinline__ void own_and_collect(const CommDev& c, const CommCtx&
 // CTAs that own no row (block >= R) re-arm at once, on behalf of everyone; only when every CTA owns rows does each
 // re-arm its share, and then after its own and collect phases.
 __device__ __forceinline__ void rearm_early(const CommDev& c, const CommCtx& x) {
-    if (x.blocks > c.R && x.block >= c.R) rearm(c, x, x.block - c.R, x.blocks - c.R);
+    if (x.blocks > c.slot_rows && x.block >= c.slot_rows) rearm(c, x, x.block - c.slot_rows, x.blocks - c.slot_rows);
 }
 __device__ __forceinline__ void rearm_late(const CommDev& c, const CommCtx& x) {
-    if (x.blocks <= c.R) rearm(c, x, x.block, x.blocks);
+    if (x.blocks <= c.slot_rows) rearm(c, x, x.block, x.blocks);
 }
 
 // Advance the invocation counters: every entry of the table ends equal to e, whatever the grid size.

@@ -392,7 +392,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
             const uint4 packed = pack_bf16x8(acc);
             const int col = f * kBlockF + j * kVec;
             if (p.fused) {
-                store_v4(push_address(c, x, token0 + token, col), packed);
+                push_store(c, x, token0 + token, col, packed);
             } else {
                 store_v4(g.out + static_cast<size_t>(token0 + token) * g.ldo + col, packed);
             }
@@ -462,7 +462,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
             const uint4 packed = pack_bf16x8(acc);
             const int col = f * kBlockF + j * kVec;
             if (p.fused) {
-                store_v4(push_address(c, x, token0 + token, col), packed);
+                push_store(c, x, token0 + token, col, packed);
             } else {
                 store_v4(g.out + static_cast<size_t>(token0 + token) * g.ldo + col, packed);
             }
@@ -474,7 +474,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
             const uint4 packed = staged[v];
             const int col = f * kBlockF + j * kVec;
             if (p.fused) {
-                store_v4(push_address(c, x, token0 + token, col), packed);
+                push_store(c, x, token0 + token, col, packed);
             } else {
                 store_v4(g.out + static_cast<size_t>(token0 + token) * g.ldo + col, packed);
             }

@@ -416,7 +416,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
             if (t < threads) {
                 const uint4 packed = combine_row(g, row, t);
                 if (p.fused) {
-                    store_v4(push_address(c, x, row, t * kVec), packed);
+                    push_store(c, x, row, t * kVec, packed);
                 } else {
                     store_v4(g.out + static_cast<size_t>(row) * g.ldo + t * kVec, packed);
                 }

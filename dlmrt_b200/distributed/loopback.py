@@ -51,12 +51,15 @@ class _RankView:
 
 
 class LoopbackWorld:
-    def __init__(self, nranks, device="cuda:0", max_ctas=0):
+    def __init__(self, nranks, device="cuda:0", max_ctas=0, one_shot_bytes=None):
         self.device = torch.device(device)
         self.world = nranks
         shared = _SharedAllocator(nranks, self.device)
         self.groups = [Group(self.device, rank=r, world=nranks, allocator=shared.view(r), max_ctas=max_ctas)
                        for r in range(nranks)]
+        if one_shot_bytes is not None:  # 0: always reduce-scatter + all-gather; large: one hop wherever allowed
+            for g in self.groups:
+                g.one_shot_bytes = one_shot_bytes
 
     def _mode(self, hs, weight):
         if weight is None:

@@ -97,6 +97,8 @@ class Group:
         self.rank, self.world = rank, world
         self.device = device
         self.max_ctas = max_ctas  # cap on every launch's grid (calls on concurrent chains must fit together)
+        # Plain sums whose incoming partials total at most this many bytes per rank run as one NVLink hop.
+        self.one_shot_bytes = int(os.environ.get("DLMRT_ONE_SHOT_BYTES", 1 << 20))
         self._alloc = allocator
         self._buffers = {}
         self._handles = {}
@@ -156,14 +158,22 @@ class Group:
                                                               dtype=torch.int64)
         return self._out_peers[key, t.data_ptr()]
 
-    def _receive(self, rows, n, chain):
-        """Triple-buffered receive slots (symmetric, armed), every rank's slot address, invocation counters."""
-        if (rows, n, chain) not in self._recv:
-            key = f"recv{rows}x{n}.{chain}"
-            self.symmetric(key, (3, self.world, rows // self.world, n), armed=True)
+    def _receive(self, rows, n, chain, one_shot=False):
+        """Triple-buffered receive slots (symmetric, armed), every rank's slot address, invocation counters and the
+        buffer's multicast address. One-shot calls have slots of their own, a whole partial per sender."""
+        if (rows, n, chain, one_shot) not in self._recv:
+            key = f"recv{rows}x{n}.{chain}" + (".all" if one_shot else "")
+            t = self.symmetric(key, (3, self.world, rows if one_shot else rows // self.world, n), armed=True)
             epochs = torch.zeros(_lib.EPOCH_SLOTS, device=self.device, dtype=torch.int32)
-            self._recv[rows, n, chain] = list(self._handles[key].buffer_ptrs), epochs
-        return self._recv[rows, n, chain]
+            self._recv[rows, n, chain, one_shot] = list(self._handles[key].buffer_ptrs), epochs, self.multicast(t)
+        return self._recv[rows, n, chain, one_shot]
+
+    def one_shot(self, rows, n, mode):
+        """Whether a reduction runs as one NVLink hop (every rank receives every partial whole and sums all rows
+        itself) instead of reduce-scatter + all-gather: plain sums whose incoming partials stay under
+        `one_shot_bytes` per rank (32-row blocks); residual modes keep their residual stream per owner and never do."""
+        return (self.world > 1 and mode == _lib.REDUCE
+                and (self.world - 1) * rows * n * 2 <= self.one_shot_bytes)
 
     def partial(self, site, shape):
         """Where a row-parallel GEMM writes its partial product: one buffer shared by every call site (`site` is not
@@ -206,7 +216,8 @@ class Group:
     def _comm(self, rows, n, site, chain, mode, h, weight, eps, scale):
         """The DlmComm of one call and its output buffer (the bookkeeping of parallel.py:119-132)."""
         out = self.symmetric(f"out:{site}", (rows, n), armed=True)
-        ptrs, epochs = self._receive(rows, n, chain)
+        one_shot = self.one_shot(rows, n, mode)
+        ptrs, epochs, recv_mc = self._receive(rows, n, chain, one_shot)
         last = self._last.get(chain)
         if last is out:
             raise ValueError(f"call site {site} ran twice in a row; its buffer would never be re-armed")
@@ -230,6 +241,7 @@ class Group:
         c.timeout_ns = TIMEOUT_NS
         c.pdl = int(PDL)
         c.max_ctas = self.max_ctas
+        c.one_shot, c.recv_mc = int(one_shot), (recv_mc or None) if one_shot else None
         return c, out
 
     def _gemm(self, linear, x, chain):

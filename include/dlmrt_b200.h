@@ -95,6 +95,12 @@ typedef struct DlmComm {
     int32_t pdl;                   /* launch as a programmatic dependent launch (tp_comm.cu:304-309) */
     int32_t max_ctas;              /* cap on the grid, 0 = one CTA per SM. Calls that may run concurrently (different
                                       chains on different streams) must together fit on the GPU. */
+    int32_t one_shot;              /* 1 (mode DLM_REDUCE only): every rank stores its whole partial into every rank's
+                                      slots and sums all rows itself, in rank order, into its own `out`: one NVLink hop,
+                                      no broadcast; meant for small partials (32-row blocks). `recv` buffers are then
+                                      [3][world][rows][n]. Same bits as the two-hop protocol. Ignored when world == 1. */
+    int32_t reserved;
+    void* recv_mc;                 /* one_shot: NVLS multicast address of the receive buffer, or NULL (one store per rank) */
 } DlmComm;
 
 /* The GEMM half of a fused call: out[M, N] = x[M, K] * W[N, K]^T, this rank's K shard (linear.py:41-51). */

@@ -10,6 +10,9 @@ sentinel (0xFFFF lanes); an invocation `e` on a rank
      into OUT on every rank,
   4. waits until its own OUT copy is complete.
 
+`one_shot=True` models the one-hop variant for small partials: slots are `[buffers][world][rows][n]`, every rank stores
+its whole partial into every rank's slots and then sums ALL rows itself into its own OUT (no broadcast, no wait on OUT).
+
 Ranks run as generators; a scheduler interleaves their steps in any order (seeded random, or a caller-supplied
 priority), which is how the protocol's claim is tested: with three buffers no interleaving loses data, with two some
 do. A rank that never pushes makes the others exhaust their wait budget: `ProtocolTimeout` names the waiting rank,
@@ -31,9 +34,10 @@ class ProtocolTimeout(RuntimeError):
 
 
 class Rank:
-    def __init__(self, rank, world, rows, n, buffers, sites):
+    def __init__(self, rank, world, rows, n, buffers, sites, one_shot=False):
         self.rank, self.world, self.R, self.n, self.buffers = rank, world, rows // world, n, buffers
-        self.recv = np.full((buffers, world, self.R, n), SENTINEL, dtype=np.uint16)
+        self.rows, self.one_shot = rows, one_shot
+        self.recv = np.full((buffers, world, rows if one_shot else self.R, n), SENTINEL, dtype=np.uint16)
         self.out = {s: np.full((rows, n), SENTINEL, dtype=np.uint16) for s in sites}
         self.epoch = 0
         self.last_site = None
@@ -50,10 +54,16 @@ def invocation(me, ranks, partial, site, late_rearm, silent=False):
     e = me.epoch + 1
     buf = e % me.buffers
     if not silent:  # a silent rank runs the kernel but its pushes go nowhere (fault injection)
-        for l in range(world * R):  # destinations rotate so that first stores spread over the peers
-            r, s = l // world, (me.rank + l % world) % world
-            ranks[s].recv[buf, me.rank, r] = partial[s * R + r]
-            yield True
+        if me.one_shot:
+            for row in range(me.rows):  # the whole partial, to every rank (peers first, as the stores rotate)
+                for d in range(world):
+                    ranks[(me.rank + d) % world].recv[buf, me.rank, row] = partial[row]
+                    yield True
+        else:
+            for l in range(world * R):  # destinations rotate so that first stores spread over the peers
+                r, s = l // world, (me.rank + l % world) % world
+                ranks[s].recv[buf, me.rank, r] = partial[s * R + r]
+                yield True
 
     def rearm():
         me.recv[(e + me.buffers - 1) % me.buffers] = SENTINEL
@@ -63,14 +73,17 @@ def invocation(me, ranks, partial, site, late_rearm, silent=False):
     if not late_rearm:
         rearm()
         yield True
-    for r in range(R):
+    for r in range(me.rows if me.one_shot else R):
         while not all(arrived(me.recv[buf, s, r]) for s in range(world)):
             yield False
         row = f32_to_bf16(red.rank_order_sum(me.recv[buf, :, r][:, None, :]))[0]  # rank order, FP32, from +0.0f
-        for peer in ranks:
-            peer.out[site][me.rank * R + r] = row
+        if me.one_shot:
+            me.out[site][r] = row  # every rank computes every row: nothing to broadcast
+        else:
+            for peer in ranks:
+                peer.out[site][me.rank * R + r] = row
         yield True
-    while not all(arrived(me.out[site][j]) for j in range(world * R)):
+    while not me.one_shot and not all(arrived(me.out[site][j]) for j in range(world * R)):
         yield False
     me.results.append(me.out[site].copy())
     if late_rearm:
@@ -80,11 +93,12 @@ def invocation(me, ranks, partial, site, late_rearm, silent=False):
     me.last_site = site
 
 
-def run(world, rows, n, calls, buffers=3, seed=0, late_rearm=False, priority=None, silent_rank=None, budget=20000):
+def run(world, rows, n, calls, buffers=3, seed=0, late_rearm=False, priority=None, silent_rank=None, budget=20000,
+        one_shot=False):
     """Runs `calls` = [(site, partials [world, rows, n])] on all ranks under a random (or prioritised) interleaving.
     Returns each rank's list of OUT snapshots. Raises ProtocolTimeout when ranks stay blocked for `budget` picks."""
     sites = sorted({s for s, _ in calls})
-    ranks = [Rank(r, world, rows, n, buffers, sites) for r in range(world)]
+    ranks = [Rank(r, world, rows, n, buffers, sites, one_shot) for r in range(world)]
     rng = random.Random(seed)
     todo = [list(calls) for _ in range(world)]
     running = [None] * world

@@ -86,11 +86,26 @@ def main():
     e_local = 64 // world
     args = device_args(case, rank * e_local, e_local, dev)
     want = red.reduce(np.stack([oracle_out(case, r * e_local, e_local)[0] for r in range(world)]))
-    for rep in range(3):
-        out = nvfp4.moe_down(out=None, group=group, site=f"moe.{rep % 2}", chain=32, **args)
-        torch.cuda.synchronize()
-        group.check()
-        assert_same_bits(bits(out), want, f"moe {rep}")
+    one_hop = 0
+    for limit in (group.one_shot_bytes, 0):  # 32 rows: one NVLink hop by default; then forced onto the two-hop protocol
+        group.one_shot_bytes = limit
+        one_hop += int(group.one_shot(32, 2048, 0))
+        for rep in range(3):
+            out = nvfp4.moe_down(out=None, group=group, site=f"moe.{limit}.{rep % 2}", chain=32, **args)
+            torch.cuda.synchronize()
+            group.check()
+            assert_same_bits(bits(out), want, f"moe {rep} (one-shot limit {limit})")
+            for r, other in enumerate(gather(out)):
+                assert_same_bits(bits(other), bits(out), f"moe {rep}: rank {r} vs rank {rank}")
+        # the reduction of given small partials, same two ways
+        for rep in range(3):
+            p = randn_bf16(32, 2048, seed=900 + 10 * rep + rank, device=dev)
+            all_p = np.stack([bits(t) for t in gather(p)])
+            out = group.reduce(p, site=f"small.{limit}.{rep % 2}", chain=33)
+            torch.cuda.synchronize()
+            group.check()
+            assert_same_bits(bits(out), red.reduce(all_p), f"small reduce {rep} (one-shot limit {limit})")
+    assert one_hop == 1
     dist.barrier()
     if rank == 0:
         print(f"MULTIGPU_OK world={world} multicast={report['multicast']}")

@@ -110,8 +110,8 @@ def test_gaussian_operands_within_tolerance(rows, hidden, f, e_total, top_k, ske
         assert rel.max() <= onv.GEMM2_REL_L2, rel.max()
 
 
-@pytest.mark.parametrize("world", [1, 2, 8])
-def test_expert_parallel_loopback_matches_oracle(world):
+@pytest.mark.parametrize("world, one_shot_bytes", [(1, None), (2, 0), (2, None), (8, 0), (8, None)])
+def test_expert_parallel_loopback_matches_oracle(world, one_shot_bytes):
     """Experts split whole across emulated ranks; each rank's partial is exact (integer-like operands), so the fused
     reduction must equal the oracle's rank-ordered sum of the per-rank combines bit for bit, on every rank."""
     from dlmrt_b200.distributed.loopback import LoopbackWorld
@@ -120,7 +120,7 @@ def test_expert_parallel_loopback_matches_oracle(world):
     rows, hidden, f, e_total, top_k = 32, 2048, 512, 64, 8
     case = make_case(rows, hidden, f, e_total, top_k, seed=world, exact=True)
     e_local = e_total // world
-    lw = LoopbackWorld(world)
+    lw = LoopbackWorld(world, one_shot_bytes=one_shot_bytes)  # None: 32 rows go over one NVLink hop; 0: two hops
     keep = []
     for rep in range(2):
         descs, partials = [], []

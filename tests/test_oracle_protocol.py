@@ -20,11 +20,12 @@ def calls(world, rows, n, count, seed):
 
 @pytest.mark.parametrize("world", [1, 2, 4, 8])
 @pytest.mark.parametrize("late_rearm", [False, True])
-def test_every_interleaving_gives_the_oracle_result(world, late_rearm):
+@pytest.mark.parametrize("one_shot", [False, True])
+def test_every_interleaving_gives_the_oracle_result(world, late_rearm, one_shot):
     rows, n = 2 * world, 256
     work = calls(world, rows, n, 7, seed=world)
     for seed in range(6):
-        results = protocol.run(world, rows, n, work, seed=seed, late_rearm=late_rearm)
+        results = protocol.run(world, rows, n, work, seed=seed, late_rearm=late_rearm, one_shot=one_shot)
         for i, (_, partials) in enumerate(work):
             want = red.reduce(partials)
             for r in range(world):
@@ -57,6 +58,19 @@ def test_two_buffers_lose_data_three_do_not():
         except protocol.ProtocolTimeout:
             failures += 1
     assert failures > 0
+
+
+def test_one_hop_variant_survives_a_hurried_rank_with_three_buffers():
+    """One hop has no wait on OUT, so a fast rank runs further ahead of a slow one than in the two-hop protocol; three
+    buffers still suffice because finishing invocation e needs every peer's push of e, made after that peer's e - 1."""
+    world, rows, n = 4, 4, 256
+    work = calls(world, rows, n, 9, seed=3)
+    for fast in range(world):
+        for late in (False, True):
+            got = protocol.run(world, rows, n, work, late_rearm=late, priority=hurry(fast), one_shot=True)
+            for i, (_, partials) in enumerate(work):
+                for r in range(world):
+                    assert np.array_equal(got[r][i], red.reduce(partials)), (fast, late, i, r)
 
 
 def test_a_rank_that_never_pushes_is_reported():

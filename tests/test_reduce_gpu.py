@@ -18,11 +18,12 @@ def short_timeouts(monkeypatch):
     monkeypatch.setattr(parallel, "TIMEOUT_NS", 500_000_000)
 
 
-def run_sequence(world, rows, n, calls, seed=0):
-    """`calls` reductions alternating over two call sites and all three modes; returns nothing, asserts parity."""
+def run_sequence(world, rows, n, calls, seed=0, one_shot_bytes=None):
+    """`calls` reductions alternating over two call sites and all three modes; returns nothing, asserts parity.
+    `one_shot_bytes`: 0 keeps every plain sum on the two-hop protocol, a large value sends them all over one hop."""
     from dlmrt_b200.distributed.loopback import LoopbackWorld
 
-    lw = LoopbackWorld(world)
+    lw = LoopbackWorld(world, one_shot_bytes=one_shot_bytes)
     weight = randn_bf16(n, seed=seed + 99, std=0.1) + 1
     hs = [randn_bf16(rows, n, seed=seed + 50 + r) for r in range(world)]
     for i in range(calls):
@@ -56,8 +57,9 @@ def run_sequence(world, rows, n, calls, seed=0):
 
 @pytest.mark.parametrize("world, rows, n", [(1, 32, 256), (1, 256, 2560), (2, 32, 2048), (2, 256, 2560),
                                             (4, 64, 2816), (8, 32, 2048), (8, 256, 2560), (4, 16, 8192)])
-def test_loopback_sequences_match_oracle(world, rows, n):
-    run_sequence(world, rows, n, calls=7)
+@pytest.mark.parametrize("one_shot_bytes", [0, 1 << 30])
+def test_loopback_sequences_match_oracle(world, rows, n, one_shot_bytes):
+    run_sequence(world, rows, n, calls=7, one_shot_bytes=one_shot_bytes)
 
 
 def test_special_values_survive():
@@ -95,7 +97,8 @@ def test_group_local_world_one_matches_oracle_and_rejects_repeated_site():
         g.symmetric("out:a", (64, 2048))
 
 
-def test_withheld_push_times_out_without_trapping():
+@pytest.mark.parametrize("one_shot", [False, True])
+def test_withheld_push_times_out_without_trapping(one_shot):
     """A rank whose pushes never reach their destination: the owners' bounded waits run out, the status words say
     so on every rank, the kernel returns normally and the GPU stays usable."""
     import ctypes as C
@@ -105,16 +108,24 @@ def test_withheld_push_times_out_without_trapping():
     from dlmrt_b200.distributed.loopback import LoopbackWorld
 
     parallel.TIMEOUT_NS = 2_000_000  # 2 ms
-    lw = LoopbackWorld(2)
+    lw = LoopbackWorld(2, one_shot_bytes=(1 << 30) if one_shot else 0)
     rows, n = 8, 256
     partials = [randn_bf16(rows, n, seed=r) for r in range(2)]
     comms, outs = lw._comms(rows, n, "lost", 0, None, None, 0.0, 1.0)
-    lost = torch.full((3, 2, rows // 2, n), -1, dtype=torch.int16, device="cuda")
+    assert bool(comms[1].one_shot) == one_shot
+    # a stand-in for rank 0's receive buffer, of the same size (one-shot slots hold a whole partial per sender)
+    lost = torch.full((3, 2, rows if one_shot else rows // 2, n), -1, dtype=torch.int16, device="cuda")
     comms[1].recv[0] = lost.data_ptr()  # rank 1's pushes to rank 0 land in a buffer nobody reads
     ptrs = (C.c_void_p * 2)(*[p.data_ptr() for p in partials])
     _lib.check(_lib.lib().dlm_reduce_bf16_loopback(ptrs, comms, 2, None), "loopback")
     torch.cuda.synchronize()
-    for g in lw.groups:
+    for r, g in enumerate(lw.groups):
+        if one_shot and r == 1:
+            # One hop has no broadcast to withhold: the rank that received everything finishes, with the right sum;
+            # the rank that misses a partial reports it.
+            g.check()
+            assert_same_bits(bits(outs[1]), red.reduce(np.stack([bits(p) for p in partials])), "rank 1")
+            continue
         with pytest.raises(TimeoutError, match="never arrived"):
             g.check()
     # the context is alive and a fresh world works
