@@ -144,15 +144,18 @@ bool cluster_fits(int mt, int splits, int clusters) {
 }
 
 // Picks (token tiles, K splits) for a [m, n, k] GEMM on `avail` CTAs with a cost model fitted to measurements on B200
-// (256 x 2560 outputs, K from 512 to 9728, every tiling; microseconds):
+// (256 x 2560 outputs, K from 512 to 9728, every tiling, and phase stamps of the fused kernel at one and two ranks;
+// microseconds):
 //   4.8                          launch, prologue, first loads, epilogue and push
 //   + kb * (0.24 + 0.0009 * mt)  kb k-blocks per CTA; a k-block costs more the more tokens (mt) the tile holds
-//   + 0.4 + 0.022 * mt           if K is split: partial tiles through L2 and the rendezvous (a cluster: about 1)
-//   + ceil(R / CTAs) * 1.3       owner phase of the reduction: each CTA takes its rows one after the other
+//   + 2.8 + 0.019 * mt           if K is split: FP32 partial tiles out to L2, the rendezvous, and the tiles read back
+//                                (5.2 at 128 tokens, 7.7 at 256; a cluster: about 1). Fused at ONE rank the rows'
+//                                owners read the partials themselves, one rendezvous less: 0.3 + 0.0176 * mt
+//   + 1.3 + 0.5 * (rows - 1)     owner phase of the reduction, rows = ceil(R / CTAs) per CTA (later rows overlap)
 // and never less than the weight shard takes to stream from HBM. Long K (TP = 1) ends up split seven ways over 140 SMs,
 // short K (TP = 8) tiled along the tokens, in between a mix of both.
 void choose_tiling(int m, int n, int k, int avail, int* tiles_out, int* splits_out, bool clusters = false, int ranks = 1,
-                   int owner_rows = 0) {
+                   int owner_rows = 0, bool single_rank = false) {
     const double hbm_bytes_per_us = 6.0e6;
     const int feature_tiles = n / kBlockF, nkb = (k + kBlockK - 1) / kBlockK;
     double best = 1e30;
@@ -170,8 +173,12 @@ void choose_tiling(int m, int n, int k, int avail, int* tiles_out, int* splits_o
             const double hbm = static_cast<double>(n) * k * 2 / hbm_bytes_per_us;
             if (us < hbm) us = hbm;
             us += 4.8;
-            if (sp > 1) us += clusters && cluster_fits(mt, sp, feature_tiles * t * ranks) ? 1.0 : 0.4 + 0.022 * mt;
-            if (owner_rows > 0) us += ((owner_rows + ctas - 1) / ctas) * 1.3;
+            if (sp > 1) {
+                if (clusters && cluster_fits(mt, sp, feature_tiles * t * ranks)) us += 1.0;
+                else if (single_rank && owner_rows > 0) us += 0.3 + 0.0176 * mt;
+                else us += 2.8 + 0.019 * mt;
+            }
+            if (owner_rows > 0) us += 1.3 + 0.5 * ((owner_rows + ctas - 1) / ctas - 1);
             if (us < best - 1e-9) {
                 best = us;
                 *tiles_out = t;
@@ -197,7 +204,8 @@ int check_gemm(const DlmGemm* g) {
 }
 
 // Fills the device-side GEMM block; returns the per-rank grid in *grid.
-int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid, int ranks = 1, int owner_rows = 0) {
+int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid, int ranks = 1, int owner_rows = 0,
+              bool single_rank = false) {
     std::memset(d, 0, sizeof(*d));
     const int avail = max_ctas > 0 && max_ctas < sms ? max_ctas : sms;
     const int feature_tiles = g->n / kBlockF, nkb = (g->k + kBlockK - 1) / kBlockK;
@@ -212,7 +220,7 @@ int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid, in
     }
     if (token_tiles == 0 || splits == 0) {
         int t = 1, sp = 1;
-        choose_tiling(g->m, g->n, g->k, avail, &t, &sp, g->use_cluster, ranks, owner_rows);
+        choose_tiling(g->m, g->n, g->k, avail, &t, &sp, g->use_cluster, ranks, owner_rows, single_rank);
         if (token_tiles == 0 && splits == 0) {
             token_tiles = t;
             splits = sp;
@@ -400,7 +408,7 @@ int dlm_rowpar_bf16(const DlmGemm* gemm, const DlmComm* comm, dlm_stream_t strea
     RowparParams<1> p;
     std::memset(&p, 0, sizeof(p));
     int grid = 0;
-    rc = fill_gemm(&p.g[0], gemm, comm->max_ctas, info.sms, &grid, 1, comm->rows / comm->world);
+    rc = fill_gemm(&p.g[0], gemm, comm->max_ctas, info.sms, &grid, 1, comm->rows / comm->world, comm->world == 1);
     if (rc != DLM_OK) return rc;
     fill_comm(&p.c[0], comm);
     p.fused = 1;
@@ -548,7 +556,7 @@ int dlm_rowpar_bf16_loopback(const DlmGemm* gemm, const DlmComm* comm, int nrank
         if (gemm[i].m != gemm[0].m || gemm[i].n != gemm[0].n || gemm[i].k != gemm[0].k) return DLM_ERR_SHAPE;
         int cap = comm[0].max_ctas > 0 && comm[0].max_ctas < per_rank ? comm[0].max_ctas : per_rank;
         int gi = 0;
-        rc = fill_gemm(&p.g[i], &gemm[i], cap, per_rank, &gi, nranks, comm[i].rows / comm[i].world);
+        rc = fill_gemm(&p.g[i], &gemm[i], cap, per_rank, &gi, nranks, comm[i].rows / comm[i].world, comm[i].world == 1);
         if (rc != DLM_OK) return rc;
         if (i > 0 && gi != grid) return DLM_ERR_SHAPE;
         grid = gi;
