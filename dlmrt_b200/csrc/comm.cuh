@@ -261,57 +261,87 @@ __device__ __forceinline__ void finish_row(const CommDev& c, float (&v)[kVec], u
     finish_rows<MODE, 1>(c, vv, hh, wraw, oo, active, st, scratch, threads);
 }
 
-// Owner phase + collect phase. Thread t < n / 8 holds columns [8t, 8t + 8) of the row being reduced; threads beyond
-// that only take part in the block-wide synchronisation. `scratch` is 32 floats of shared memory.
-template <int MODE>
-__device__ __forceinline__ void own_and_collect(const CommDev& c, const CommCtx& x, float* scratch) {
+// Owner phase: CTA `block` owns slot rows block, block + blocks, ... and takes them NROWS at a time (the rows' waits,
+// sums and block-wide reductions overlap; NROWS = 2 where CTAs own several rows, i.e. one or two ranks). Thread
+// t < n / 8 holds columns [8t, 8t + 8) of the rows being reduced; threads beyond that only take part in the block-wide
+// synchronisation. `scratch` is 32 * NROWS floats of shared memory.
+template <int MODE, int NROWS>
+__device__ __forceinline__ void own_rows(const CommDev& c, const CommCtx& x, float* scratch) {
     const int t = threadIdx.x;
     const int threads = c.n / kVec;
     const bool active = t < threads;
     const size_t col = static_cast<size_t>(active ? t : 0) * kVec;
     const __nv_bfloat16* mine = c.recv[c.rank] + x.buf * x.buf_elems;
-    uint4 slots[kMaxWorld];
-    // With one or two ranks a CTA may own several rows (R > CTAs): the next row's slots are then read early, while
-    // this row is being normalised, so that consecutive rows do not each pay a full round trip to L2.
-    uint4 early[2];
-    bool have_early = false;
     const int first_row = c.one_shot ? 0 : c.rank * c.R;  // row of OUT that slot row 0 holds
-    for (int r = x.block; r < c.slot_rows; r += x.blocks) {
-        const size_t off = static_cast<size_t>(first_row + r) * c.n + col;
+    uint4 wraw = make_uint4(0, 0, 0, 0);
+    if (MODE != kReduce && active) wraw = *reinterpret_cast<const uint4*>(c.weight + col);
+    for (int r0 = x.block; r0 < c.slot_rows; r0 += NROWS * x.blocks) {
+        size_t off[NROWS];
+        uint4 hraw[NROWS];
+        bool store[NROWS];
         // Local operands first, so their latency overlaps the wait for the peers (tp_comm.cu:225-228).
-        uint4 hraw = make_uint4(0, 0, 0, 0), wraw = make_uint4(0, 0, 0, 0);
-        if (MODE == kReduceNormResidual && active) hraw = *reinterpret_cast<const uint4*>(c.h + off);
-        if (MODE != kReduce && active) wraw = *reinterpret_cast<const uint4*>(c.weight + col);
-        bool ok = true;
-        if (active) {
-            unsigned pending = ~0u;
-            if (have_early) {
-                pending = 0;
 #pragma unroll
-                for (int s = 0; s < 2; ++s) {
-                    if (s < c.world) {
-                        slots[s] = early[s];
-                        if (!arrived(early[s])) pending |= 1u << s;
+        for (int i = 0; i < NROWS; ++i) {
+            const int r = r0 + i * x.blocks;
+            store[i] = r < c.slot_rows;
+            off[i] = static_cast<size_t>(first_row + (store[i] ? r : 0)) * c.n + col;
+            hraw[i] = make_uint4(0, 0, 0, 0);
+            if (MODE == kReduceNormResidual && active && store[i]) hraw[i] = *reinterpret_cast<const uint4*>(c.h + off[i]);
+        }
+        // With one or two ranks the second row's slots are read before the first row is waited for, so that the rows
+        // do not each pay a round trip to L2.
+        uint4 early[2];
+        const bool have_early = NROWS > 1 && c.world <= 2 && active && store[NROWS - 1];
+        if (have_early) {
+#pragma unroll
+            for (int s = 0; s < 2; ++s)
+                if (s < c.world)
+                    early[s] = load_volatile(mine + static_cast<size_t>(r0 + (NROWS - 1) * x.blocks) * c.n + col + s * x.slot_elems);
+        }
+        float v[NROWS][kVec] = {};
+#pragma unroll
+        for (int i = 0; i < NROWS; ++i) {
+            if (active && store[i]) {
+                uint4 slots[kMaxWorld];
+                unsigned pending = ~0u;
+                if (have_early && i == NROWS - 1) {
+                    pending = 0;
+#pragma unroll
+                    for (int s = 0; s < 2; ++s) {
+                        if (s < c.world) {
+                            slots[s] = early[s];
+                            if (!arrived(early[s])) pending |= 1u << s;
+                        }
                     }
                 }
-            }
-            ok = poll_all(mine + static_cast<size_t>(r) * c.n + col, x.slot_elems, c.world, slots, c, x, kPhaseReceive, pending);
-            have_early = c.world <= 2 && r + x.blocks < c.slot_rows;
-            if (have_early) {
+                const int r = r0 + i * x.blocks;
+                store[i] = poll_all(mine + static_cast<size_t>(r) * c.n + col, x.slot_elems, c.world, slots, c, x, kPhaseReceive,
+                                    pending);
 #pragma unroll
-                for (int s = 0; s < 2; ++s)
-                    if (s < c.world) early[s] = load_volatile(mine + static_cast<size_t>(r + x.blocks) * c.n + col + s * x.slot_elems);
+                for (int s = 0; s < kMaxWorld; ++s)
+                    if (s < c.world) add_bf16x8(v[i], slots[s]);
             }
         }
-        float v[kVec] = {};
-        if (active) {
-#pragma unroll
-            for (int s = 0; s < kMaxWorld; ++s)
-                if (s < c.world) add_bf16x8(v, slots[s]);
-        }
-        finish_row<MODE>(c, v, hraw, wraw, off, active, ok, scratch, threads);
+        finish_rows<MODE, NROWS>(c, v, hraw, wraw, off, active, store, scratch, threads);
     }
+}
+
+__device__ __forceinline__ void rearm_late(const CommDev& c, const CommCtx& x);
+
+// Owner phase + late re-arm + collect phase. `scratch`: 64 floats.
+// PAIRS: rows are taken two at a time where CTAs own several (off for the 1024-thread kernel, whose 64 registers per
+// thread do not hold two rows).
+template <int MODE, bool PAIRS>
+__device__ __forceinline__ void own_and_collect(const CommDev& c, const CommCtx& x, float* scratch) {
+    if (PAIRS && c.slot_rows > x.blocks) own_rows<MODE, PAIRS ? 2 : 1>(c, x, scratch);
+    else own_rows<MODE, 1>(c, x, scratch);
+    const bool active = static_cast<int>(threadIdx.x) < c.n / kVec;
+    const size_t col = static_cast<size_t>(active ? threadIdx.x : 0) * kVec;
+    uint4 slots[kMaxWorld];
     stamp(c, x, 2);
+    // The late re-arm goes here, between the broadcast of the owned rows and the wait for everyone else's: its stores
+    // fill the time the broadcasts are in flight instead of lengthening the kernel's tail.
+    rearm_late(c, x);
     // Collect: rows s * R + r of this rank's OUT copy, from every owner s. With one rank, or one-shot, every row of
     // OUT was stored by this very grid, so it is complete when the kernel ends and there is nothing to wait for.
     if (active && c.world > 1 && !c.one_shot) {
@@ -321,15 +351,16 @@ __device__ __forceinline__ void own_and_collect(const CommDev& c, const CommCtx&
     stamp(c, x, 3);
 }
 
+template <bool PAIRS = true>
 __device__ __forceinline__ void own_and_collect(const CommDev& c, const CommCtx& x, float* scratch) {
-    if (c.mode == kReduce) own_and_collect<kReduce>(c, x, scratch);
-    else if (c.mode == kReduceNorm) own_and_collect<kReduceNorm>(c, x, scratch);
-    else own_and_collect<kReduceNormResidual>(c, x, scratch);
+    if (c.mode == kReduce) own_and_collect<kReduce, PAIRS>(c, x, scratch);
+    else if (c.mode == kReduceNorm) own_and_collect<kReduceNorm, PAIRS>(c, x, scratch);
+    else own_and_collect<kReduceNormResidual, PAIRS>(c, x, scratch);
 }
 
 // Nothing waits for the re-arm inside this launch, but the owners' sums are on the critical path of every rank. So
 // CTAs that own no row (block >= R) re-arm at once, on behalf of everyone; only when every CTA owns rows does each
-// re-arm its share, and then after its own and collect phases.
+// re-arm its share, and then after its own phase (own_and_collect calls rearm_late before it collects).
 __device__ __forceinline__ void rearm_early(const CommDev& c, const CommCtx& x) {
     if (x.blocks > c.slot_rows && x.block >= c.slot_rows) rearm(c, x, x.block - c.slot_rows, x.blocks - c.slot_rows);
 }

@@ -17,15 +17,14 @@ template <int NR, int MAXT>
 __global__ void __launch_bounds__(MAXT, 1) reduce_kernel(const __grid_constant__ ReduceParams<NR> p) {
     const int slot = NR == 1 ? 0 : static_cast<int>(blockIdx.y);
     const CommDev& c = p.c[slot];
-    __shared__ float scratch[32];
+    __shared__ float scratch[64];
     pdl_wait();
     const CommCtx x = comm_begin(c, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), c.epochs[blockIdx.x]);
     stamp(c, x, 0);
     push_partial(c, x, p.partial[slot]);
     stamp(c, x, 1);
     rearm_early(c, x);
-    own_and_collect(c, x, scratch);
-    rearm_late(c, x);
+    own_and_collect<(MAXT <= 512)>(c, x, scratch);  // re-arms late shares between its own and collect phases
     comm_end(c, x);
     pdl_launch_dependents();
 }

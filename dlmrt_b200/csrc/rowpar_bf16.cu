@@ -490,10 +490,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
             if (c.mode == kReduce) own_rows_from_splits<kReduce>(g, c, x, counter, mt, sm->scratch);
             else if (c.mode == kReduceNorm) own_rows_from_splits<kReduceNorm>(g, c, x, counter, mt, sm->scratch);
             else own_rows_from_splits<kReduceNormResidual>(g, c, x, counter, mt, sm->scratch);
+            rearm_late(c, x);
         } else {
-            own_and_collect(c, x, sm->scratch);
+            own_and_collect(c, x, sm->scratch);  // re-arms late shares between its own and collect phases
         }
-        rearm_late(c, x);
         comm_end(c, x);
     } else {
         pdl_launch_dependents();

@@ -46,7 +46,7 @@ struct MoeSmem {
     uint32_t tmem_base;
     int n_active, epoch, gen;
     int warp_count[8];
-    float scratch[32];
+    float scratch[64];
     short active[kMaxEntries];  // expert | row block << 8
     short rows[kMaxEntries];    // rows of that block
 };
@@ -430,10 +430,10 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
         if (local_rows) {
             stamp(c, x, 2);
             stamp(c, x, 3);
+            rearm_late(c, x);
         } else {
-            own_and_collect(c, x, sm->scratch);
+            own_and_collect(c, x, sm->scratch);  // re-arms late shares between its own and collect phases
         }
-        rearm_late(c, x);
         comm_end(c, x);
     } else {
         pdl_launch_dependents();
