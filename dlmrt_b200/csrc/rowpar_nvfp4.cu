@@ -62,26 +62,54 @@ int moe_stages(int rows_cap) {
     return s > kMaxStages ? kMaxStages : s;
 }
 
+// A token's expert list for the combine step, eight entries at a time: local expert index (or -1) and routing weight.
+constexpr int kCombineBatch = 8;
+struct CombineMeta {
+    int e[kCombineBatch];
+    float w[kCombineBatch];
+};
+
+// Entries [k0, k0 + 8) of row `row`: all loads are independent, so they cost one round trip, and they depend on
+// nothing this launch computes (callers issue them before waiting for the expert outputs).
+__device__ __forceinline__ CombineMeta combine_meta(const MoeDev& g, int row, int k0) {
+    CombineMeta m;
+#pragma unroll
+    for (int j = 0; j < kCombineBatch; ++j) {
+        const bool have = k0 + j < g.top_k;
+        const int e = have ? g.ids[row * g.top_k + k0 + j] - g.lo : -1;
+        m.e[j] = e >= 0 && e < g.e_local ? e : -1;
+        m.w[j] = have ? g.weights[row * g.top_k + k0 + j] : 0.f;
+    }
+    return m;
+}
+
 // One output row of the combine step for thread t's eight columns: FP32 sum over the token's expert list, in list
 // order, of weight * y (fused multiply-add; experts of other ranks contribute 0 * 0), rounded to BF16, then the
-// shared expert's BF16 row added and rounded again (dlmrt/ops/triton/nvfp4_moe.py:134-150).
-__device__ __forceinline__ uint4 combine_row(const MoeDev& g, int row, int t) {
+// shared expert's BF16 row added and rounded again (dlmrt/ops/triton/nvfp4_moe.py:134-150). `first` holds entries
+// [0, 8) of the row, fetched early; the expert outputs of a batch are loaded together and added in list order.
+__device__ __forceinline__ uint4 combine_row(const MoeDev& g, int row, int t, const CombineMeta& first) {
     float acc[kVec] = {};
-    for (int k = 0; k < g.top_k; ++k) {
-        const int e = g.ids[row * g.top_k + k] - g.lo;
-        const bool local = e >= 0 && e < g.e_local;
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        float w = 0.f;
-        if (local) {
-            w = g.weights[row * g.top_k + k];
-            raw = __ldcg(reinterpret_cast<const uint4*>(g.y + static_cast<size_t>(row * g.top_k + k) * g.n) + t);
-        }
-        const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    for (int k0 = 0; k0 < g.top_k; k0 += kCombineBatch) {
+        const CombineMeta m = k0 == 0 ? first : combine_meta(g, row, k0);
+        uint4 raw[kCombineBatch];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 f = __bfloat1622float2(b[i]);
-            acc[2 * i] = fmaf(w, f.x, acc[2 * i]);
-            acc[2 * i + 1] = fmaf(w, f.y, acc[2 * i + 1]);
+        for (int j = 0; j < kCombineBatch; ++j) {
+            raw[j] = make_uint4(0, 0, 0, 0);
+            if (m.e[j] >= 0)
+                raw[j] = __ldcg(reinterpret_cast<const uint4*>(g.y + static_cast<size_t>(row * g.top_k + k0 + j) * g.n) + t);
+        }
+#pragma unroll
+        for (int j = 0; j < kCombineBatch; ++j) {
+            if (k0 + j < g.top_k) {
+                const float w = m.e[j] >= 0 ? m.w[j] : 0.f;
+                const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(b[i]);
+                    acc[2 * i] = fmaf(w, f.x, acc[2 * i]);
+                    acc[2 * i + 1] = fmaf(w, f.y, acc[2 * i + 1]);
+                }
+            }
         }
     }
     uint4 packed = pack_bf16x8(acc);
@@ -96,7 +124,8 @@ __device__ __forceinline__ uint4 combine_row(const MoeDev& g, int row, int t) {
 
 // Single rank: combine each owned row and finish it (residual + RMSNorm by mode, store into OUT) in one go.
 template <int MODE>
-__device__ __forceinline__ void combine_and_finish(const MoeDev& g, const CommDev& c, int block, int blocks, float* scratch) {
+__device__ __forceinline__ void combine_and_finish(const MoeDev& g, const CommDev& c, int block, int blocks, float* scratch,
+                                                   const CombineMeta& first) {
     const int t = threadIdx.x, threads = g.n / kVec;
     const bool active = t < threads;
     const int col = (active ? t : 0) * kVec;
@@ -107,7 +136,9 @@ __device__ __forceinline__ void combine_and_finish(const MoeDev& g, const CommDe
         uint4 hraw = make_uint4(0, 0, 0, 0);
         if (MODE == kReduceNormResidual && active) hraw = *reinterpret_cast<const uint4*>(c.h + off);
         float v[kVec] = {};
-        if (active) add_bf16x8(v, combine_row(g, row, t));  // +0.0f + partial: the rank-ordered sum over one rank
+        if (active) {  // +0.0f + partial: the rank-ordered sum over one rank
+            add_bf16x8(v, combine_row(g, row, t, row == block ? first : combine_meta(g, row, 0)));
+        }
         finish_row<MODE>(c, v, hraw, wraw, off, active, true, scratch, threads);
     }
 }
@@ -379,6 +410,9 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
     }
     CommCtx x{};
     if (p.fused) x = comm_begin(c, block, blocks, sm->epoch);
+    // The expert list of this CTA's first output row is fetched now, ahead of the wait for the experts' outputs.
+    CombineMeta first;
+    if (block < g.m) first = combine_meta(g, block, 0);
     {
         const int gen = sm->gen + 1;
         int* counter = g.counters + (gen & 1) * kMaxTiles;
@@ -407,14 +441,14 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
     // block + blocks, ... in both roles), so the row is finished here and never travels through the receive slots.
     const bool local_rows = p.fused && c.world == 1;
     if (local_rows) {
-        if (c.mode == kReduce) combine_and_finish<kReduce>(g, c, block, blocks, sm->scratch);
-        else if (c.mode == kReduceNorm) combine_and_finish<kReduceNorm>(g, c, block, blocks, sm->scratch);
-        else combine_and_finish<kReduceNormResidual>(g, c, block, blocks, sm->scratch);
+        if (c.mode == kReduce) combine_and_finish<kReduce>(g, c, block, blocks, sm->scratch, first);
+        else if (c.mode == kReduceNorm) combine_and_finish<kReduceNorm>(g, c, block, blocks, sm->scratch, first);
+        else combine_and_finish<kReduceNormResidual>(g, c, block, blocks, sm->scratch, first);
     } else {
         const int t = threadIdx.x, threads = g.n / kVec;
         for (int row = block; row < g.m; row += blocks) {
             if (t < threads) {
-                const uint4 packed = combine_row(g, row, t);
+                const uint4 packed = combine_row(g, row, t, row == block ? first : combine_meta(g, row, 0));
                 if (p.fused) {
                     push_store(c, x, row, t * kVec, packed);
                 } else {
