@@ -183,10 +183,11 @@ def run_gpu(args, rank, world):
 
     g = torch.Generator().manual_seed(1 + rank)
     ko, kd = K_O // world, K_DOWN // world
+    weights = 0 if args.workload in ("k1", "k3") else LAYERS  # the reduction-only workloads have no GEMM
     lin_o = [Linear((torch.randn(HIDDEN, ko, generator=g) * 0.02).to(torch.bfloat16).to(device), group=group)
-             for _ in range(LAYERS)]
+             for _ in range(weights)]
     lin_d = [Linear((torch.randn(HIDDEN, kd, generator=g) * 0.02).to(torch.bfloat16).to(device), group=group)
-             for _ in range(LAYERS)]
+             for _ in range(weights)]
     gs = torch.Generator().manual_seed(7)  # identical on every rank
     norms = [(torch.randn(HIDDEN, generator=gs) * 0.1 + 1).to(torch.bfloat16).to(device) for _ in range(2 * LAYERS)]
     h0 = torch.randn(ROWS, HIDDEN, generator=gs).to(torch.bfloat16)
@@ -196,16 +197,21 @@ def run_gpu(args, rank, world):
     x_o, x_d = host_xo.to(device), host_xd.to(device)
     host_out = torch.empty(ROWS, HIDDEN, dtype=torch.bfloat16).pin_memory()
     flush = None
-    if sum(weight_bytes(world)) * LAYERS <= 130e6 or args.workload == "k3":
+    if sum(weight_bytes(world)) * LAYERS <= 130e6 or args.workload in ("k1", "k3"):
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
 
-    only_reduce = args.workload == "k3"  # the reduction of GIVEN partials alone (dlm_reduce_bf16), no GEMM
+    only_reduce = args.workload in ("k1", "k3")  # the reduction of GIVEN partials alone (dlm_reduce_bf16), no GEMM
+    plain_sum = args.workload == "k1"           # K1 (no residual, no norm) on a 32-row block: LLaDA2's call pattern
     given = group.symmetric("given", (ROWS, HIDDEN))
     given.copy_(torch.randn(ROWS, HIDDEN, generator=g).to(torch.bfloat16))
 
     def step():
         out = None
         for i in range(LAYERS):
+            if plain_sum:
+                group.reduce(given, site=f"{i}.post")
+                out = group.reduce(given, site=f"{i + 1}.input")
+                continue
             p = given if only_reduce else lin_o[i](x_o, out=group.partial(f"{i}.o", (ROWS, HIDDEN)))
             group.reduce_norm(p, h, norms[2 * i], EPS, site=f"{i}.post")
             p = given if only_reduce else lin_d[i](x_d, out=group.partial(f"{i}.down", (ROWS, HIDDEN)))
@@ -292,8 +298,8 @@ def run_gpu(args, rank, world):
                 "unit": "GB/s"}
     roof["frac"] = round(roof["achieved"] / roof["peak"], 4)
     roof["peak_source"] = f"of {which}"
-    roof["kernel"] = "reduce_kernel" if args.workload == "k3" else "rowpar_kernel"
-    if args.workload == "k3":  # no weights: the bytes are the partial read, the slot write+read and the output write
+    roof["kernel"] = "reduce_kernel" if only_reduce else "rowpar_kernel"
+    if only_reduce:  # no weights: the bytes are the partial read, the slot write+read and the output write
         moved = 4 * ROWS * HIDDEN * 2
         roof.update(bound="latency", achieved=round(moved / avg_launch_s / 1e9, 1), peak=hbm, unit="GB/s",
                     algorithmic_bytes_per_launch=moved)
@@ -305,8 +311,9 @@ def run_gpu(args, rank, world):
 
     cpu_sec, cores = cpu_layer_seconds(world, 5) if world == 1 else (None, None)
     line = {
-        "metric": METRIC if args.workload == "c2" else "reduction of given partials (reduce + residual + RMSNorm), "
-        "latency per pair of reductions", "value": round(ms * 1e3 / LAYERS, 2), "unit": "us", "n_gpus": world, "steps": args.steps,
+        "metric": METRIC if args.workload == "c2" else "reduction of given partials (plain sum of a 32-row block), latency "
+        "per pair of reductions" if plain_sum else "reduction of given partials (reduce + residual + RMSNorm), latency per "
+        "pair of reductions", "value": round(ms * 1e3 / LAYERS, 2), "unit": "us", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": False, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config(world),
         "e2e": {"value": round(e2e_ms * 1e3 / LAYERS, 2), "unit": "us",
@@ -465,13 +472,14 @@ def reference_gpu_path(torch, group, lin_o, lin_d, norms, x_o, x_d, h, stream, t
 
     def step():
         for i in range(2 * LAYERS):
-            lin, x = (lin_o[i // 2], x_o) if i % 2 == 0 else (lin_d[i // 2], x_d)
-            if args.workload != "k3":
+            if args.workload == "c2":
+                lin, x = (lin_o[i // 2], x_o) if i % 2 == 0 else (lin_d[i // 2], x_d)
                 torch.mm(x, lin.weight.t(), out=partial)
             last = state["last"]
             rearm, numel = (last.data_ptr(), last.numel()) if last is not None else (0, 0)
-            ref.reduce_norm_residual(partial, recv_ptrs, h, norms[i], outs[i], mcs[i], peers[i], rearm, numel, epochs,
-                                     group.rank, world, EPS, 1.0, 96, 0, True)
+            fn = ref.reduce if args.workload == "k1" else ref.reduce_norm_residual
+            fn(partial, recv_ptrs, h, norms[i], outs[i], mcs[i], peers[i], rearm, numel, epochs, group.rank, world, EPS, 1.0,
+               96, 0, True)
             state["last"] = outs[i]
 
     with torch.cuda.stream(stream):
@@ -485,7 +493,8 @@ def reference_gpu_path(torch, group, lin_o, lin_d, norms, x_o, x_d, h, stream, t
             graph.replay()
     ms = timed(graph.replay, args.steps) / args.steps
     return {"value": round(ms * 1e3 / LAYERS, 2), "unit": "us",
-            "what": "torch.mm (cuBLAS) + the reference's tp_comm reduce_norm_residual kernel, same 72 ops in a CUDA graph"}
+            "what": "the reference's tp_comm reduce kernel, same 72 reductions in a CUDA graph" if args.workload == "k1" else
+            "torch.mm (cuBLAS) + the reference's tp_comm reduce_norm_residual kernel, same 72 ops in a CUDA graph"}
 
 
 def main():
@@ -495,7 +504,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=36, help="layers per step; fewer only for profiler captures")
-    ap.add_argument("--workload", default="c2", choices=["c2", "k3", "c4", "c5"], help="c2 is the bench line; k3 times "
+    ap.add_argument("--workload", default="c2", choices=["c2", "k1", "k3", "c4", "c5"], help="c2 is the bench line; k3 times "
                     "the reduction of given partials alone; c4/c5 time the NVFP4 expert path of BASELINE configs 4 and 5")
     ap.add_argument("--routing", default="uniform", choices=["uniform", "zipf"])
     ap.add_argument("--shard-of", type=int, default=1, help="profiling aid: run the K shard of a TP=<n> rank on the GPUs "
@@ -512,7 +521,10 @@ def main():
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (torchrun --nproc-per-node {args.gpus}); "
                          f"WORLD_SIZE is {world}")
-    (run_gpu if args.workload in ("c2", "k3") else run_gpu_moe)(args, rank, world)
+    if args.workload == "k1":  # LLaDA2's block: 32 rows of hidden 2048
+        global ROWS, HIDDEN
+        ROWS, HIDDEN = 32, 2048
+    (run_gpu if args.workload in ("c2", "k1", "k3") else run_gpu_moe)(args, rank, world)
     if world > 1:
         import torch.distributed as dist
 
