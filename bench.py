@@ -149,7 +149,12 @@ def run_reference(args, rank):
 METRIC = "fused row-parallel projection+reduction latency per decoder layer (o_proj + down_proj), denoise round"
 
 
-def config(world):
+def config(world, workload="c2"):
+    if workload in ("k1", "k3"):
+        what = "plain sums (K1)" if workload == "k1" else "reduce+residual+RMSNorm (K3)"
+        return {"workload": f"reduction of given BF16 partials [{ROWS}, {HIDDEN}], {what}, TP={world}; a step = {LAYERS} x 2 "
+                            "reductions on alternating call sites", "tp": world, "rows": ROWS, "hidden": HIDDEN,
+                "layers": LAYERS, "l2": "L2 flushed by a 256 MB write between steps"}
     return {"workload": f"BASELINE config 2: Qwen3-style layer, hidden {HIDDEN}, o_proj K {K_O}, down_proj K {K_DOWN}, "
                         f"{ROWS}-token block, BF16, TP={world}; a step = {LAYERS} layers x 2 fused "
                         "projection+reduce+residual+RMSNorm launches with per-layer weights",
@@ -315,7 +320,7 @@ def run_gpu(args, rank, world):
         "per pair of reductions" if plain_sum else "reduction of given partials (reduce + residual + RMSNorm), latency per "
         "pair of reductions", "value": round(ms * 1e3 / LAYERS, 2), "unit": "us", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": False, "scaling": "strong",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config(world),
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config(world, args.workload),
         "e2e": {"value": round(e2e_ms * 1e3 / LAYERS, 2), "unit": "us",
                 "h2d_bytes_per_step": host_xo.numel() * 2 + host_xd.numel() * 2, "d2h_bytes_per_step": host_out.numel() * 2},
         "gpu_launches": int(launches_per_step * args.steps), "roofline": roof, "clocks": clock_report,
