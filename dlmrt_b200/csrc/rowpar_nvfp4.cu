@@ -33,8 +33,8 @@ constexpr int kAtom = 512;             // one 128-row x 4-scale atom
 constexpr int kStepsPerBlock = 4;      // K = 64 instructions per 256-element k-block
 constexpr int kItemRows = 128;         // rows of one work item: the MMA's N; experts with more rows take several items
 constexpr int kTmemAcc = 0, kTmemSfa = 256, kTmemSfb = 384, kTmemCols = 512;  // two 128-column accumulators, then scales
-constexpr int kSfSets = 4;             // scale columns rotate over four sets, so copying a k-block's scales in does not
-                                       // have to wait for the previous k-block's MMAs to finish reading theirs
+// Scale columns rotate over four sets (two per issuer: (2 * who + set) below), so copying a k-block's scales in does
+// not have to wait for the previous k-block's MMAs to finish reading theirs.
 constexpr int kMaxLocalExperts = 256;
 constexpr int kMaxEntries = 2 * kMaxLocalExperts;  // (expert, row block) pairs: m_max <= 256 gives at most two blocks
 
