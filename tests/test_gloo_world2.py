@@ -79,6 +79,17 @@ def worker(rank, world, port, results):
         gathered = [torch.empty(R, n // 2, dtype=torch.int32) for _ in range(world)]
         dist.all_gather(gathered, mine.view(torch.int32))
         results[rank] = from_torch(torch.cat(gathered).view(torch.bfloat16))
+        # Small plain sums go over one hop: every rank keeps every pushed partial whole and sums all rows itself, in the
+        # same rank order, so it must reach the same bits without the gather. Its slots hold whole partials.
+        assert c1.one_shot == 1 and g.one_shot(rows, n, _lib.REDUCE) and not g.one_shot(rows, n, _lib.REDUCE_NORM)
+        assert g._buffers[f"recv{rows}x{n}.0.all"].shape == (3, world, rows, n)
+        one_hop = red.reduce(np.stack([from_torch(t.view(torch.bfloat16)) for t in pushed]))
+        assert np.array_equal(one_hop, results[rank])
+        g.one_shot_bytes = 0  # and none do when the threshold says so: slots of a row share per sender
+        g._last[0] = out1
+        c3, _ = g._comm(rows, n, "c", 0, _lib.REDUCE, None, None, 0.0, 1.0)
+        assert c3.one_shot == 0 and c3.recv_mc is None and c3.recv[rank] != c1.recv[rank]
+        assert g._buffers[f"recv{rows}x{n}.0"].shape == (3, world, R, n)
     finally:
         dist.destroy_process_group()
 
