@@ -341,7 +341,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
         tcgen05_fence_before();
     }
     pdl_wait();
-    if (g.splits > 1 && !g.cluster) __threadfence();
     __syncthreads();
     if (warp == 2) {
         tcgen05_fence_after();
@@ -403,6 +402,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
         const int gen = sm->gen + 1;
         if (threadIdx.x == 0) {
             for (int j = block; j < kMaxTiles; j += blocks) g.counters[((gen + 1) & 1) * kMaxTiles + j] = 0;
+            __threadfence();  // after the block barrier: orders every thread's partial-tile stores before the announce
             atomicAdd(g.counters + (gen & 1) * kMaxTiles + t, 1);
             for (int j = block; j < kEpochSlots; j += blocks) g.gen[j] = gen;
         }
@@ -415,6 +415,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
         int* counter = g.counters + (gen & 1) * kMaxTiles + tile;
         if (threadIdx.x == 0) {
             for (int j = block; j < kMaxTiles; j += blocks) g.counters[((gen + 1) & 1) * kMaxTiles + j] = 0;
+            __threadfence();  // after the block barrier: orders every thread's partial-tile stores before the announce
             atomicAdd(counter, 1);
             int seen;
             do {
