@@ -400,7 +400,6 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
     }
     // Every Y row this CTA produced is written; announce it and wait for the rest of the grid (the combine reads rows
     // written by other CTAs). Counters are banked by launch generation as in the BF16 kernel.
-    __threadfence();
     tcgen05_fence_before();
     __syncthreads();
     if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 4] = globaltimer();
@@ -418,6 +417,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
         int* counter = g.counters + (gen & 1) * kMaxTiles;
         if (threadIdx.x == 0) {
             if (block == 0) g.counters[((gen + 1) & 1) * kMaxTiles] = 0;
+            __threadfence();  // after the block barrier: orders every thread's Y stores before the announce
             atomicAdd(counter, 1);
             // Only CTAs that have output rows to combine need the others' Y rows; polling is paced so that the
             // arrivals of the rest of the grid are not queued behind a storm of loads on the same word.
