@@ -9,6 +9,7 @@ EPOCH_SLOTS = 256
 STATUS_WORDS = 4
 FUSED_MAX_N = 3072
 NOALLOC_SCRATCH_BYTES = 8 << 20
+GATHER_MAX_BYTES = 1 << 20
 
 OK, ERR_SHAPE, ERR_ALIGN, ERR_WORLD, ERR_NULL, ERR_GRID, ERR_CUDA, ERR_WORKSPACE, ERR_TIMEOUT, ERR_ARCH, \
     ERR_SCRATCH = 0, -1, -2, -3, -4, -5, -6, -7, -8, -9, -10
@@ -75,6 +76,8 @@ _lib = None
 SIGNATURES = {
     "dlm_reduce_bf16": (C.c_int, [C.c_void_p, C.POINTER(DlmComm), C.c_void_p]),
     "dlm_reduce_bf16_loopback": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(DlmComm), C.c_int, C.c_void_p]),
+    "dlm_all_gather": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(DlmComm), C.c_void_p]),
+    "dlm_all_gather_loopback": (C.c_int, [C.POINTER(C.c_void_p), C.c_int64, C.POINTER(DlmComm), C.c_int, C.c_void_p]),
     "dlm_gemm_bf16": (C.c_int, [C.POINTER(DlmGemm), C.c_void_p, C.c_int64, C.c_int, C.c_void_p]),
     "dlm_gemm_bf16_noalloc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int64,
                                         C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_void_p]),

@@ -300,6 +300,81 @@ int dlm_reduce_bf16_loopback(const void* const* partial, const DlmComm* comm, in
     return launch_reduce_loopback(p, grid, nranks, comm[0].n / kVec, {static_cast<cudaStream_t>(stream), false, true});
 }
 
+namespace {
+
+// The DlmComm of an all-gather describes only the exchange: rank, world, recv (+ recv_mc), out, epochs, status.
+int check_gather(const DlmComm* c, const void* x, int64_t bytes) {
+    if (c == nullptr || x == nullptr) return DLM_ERR_NULL;
+    if (c->world < 1 || c->world > DLM_MAX_WORLD || c->rank < 0 || c->rank >= c->world) return DLM_ERR_WORLD;
+    if (bytes <= 0 || bytes % 16 || bytes > DLM_GATHER_MAX_BYTES) return DLM_ERR_SHAPE;
+    if (c->out == nullptr || c->epochs == nullptr) return DLM_ERR_NULL;
+    for (int s = 0; s < c->world; ++s) {
+        if (c->recv[s] == nullptr) return DLM_ERR_NULL;
+        if (!aligned16(c->recv[s])) return DLM_ERR_ALIGN;
+    }
+    if (!aligned16(x) || !aligned16(c->out) || !aligned16(c->recv_mc)) return DLM_ERR_ALIGN;
+    if (c->timeout_ns < 0 || c->max_ctas < 0) return DLM_ERR_SHAPE;
+    return DLM_OK;
+}
+
+void fill_gather(CommDev* d, const DlmComm* c, int64_t bytes) {
+    std::memset(d, 0, sizeof(*d));
+    for (int s = 0; s < c->world; ++s) d->recv[s] = static_cast<__nv_bfloat16*>(c->recv[s]);
+    d->recv_mc = static_cast<__nv_bfloat16*>(c->recv_mc);
+    d->out = static_cast<__nv_bfloat16*>(c->out);
+    d->epochs = c->epochs;
+    d->status = c->status;
+    d->timeout_ns = c->timeout_ns > 0 ? c->timeout_ns : 2000000000ll;
+    d->rank = c->rank;
+    d->world = c->world;
+    d->rows = d->R = d->slot_rows = 1;
+    d->n = static_cast<int>(bytes / 2);
+    d->one_shot = 1;  // every rank receives every block whole (also with one rank: its own)
+}
+
+int gather_grid(int64_t bytes, int cap) {
+    int grid = static_cast<int>((bytes / 16 + 255) / 256);
+    if (grid > cap) grid = cap;
+    return grid < 1 ? 1 : grid;
+}
+
+}  // namespace
+
+int dlm_all_gather(const void* x, int64_t bytes, const DlmComm* comm, dlm_stream_t stream) {
+    int rc = check_gather(comm, x, bytes);
+    if (rc != DLM_OK) return rc;
+    DeviceInfo info;
+    rc = device_info(&info);
+    if (rc != DLM_OK) return rc;
+    ReduceParams<1> p;
+    fill_gather(&p.c[0], comm, bytes);
+    p.partial[0] = static_cast<const __nv_bfloat16*>(x);
+    const int cap = comm->max_ctas > 0 && comm->max_ctas < 32 ? comm->max_ctas : 32;
+    return launch_gather(p, gather_grid(bytes, cap), {static_cast<cudaStream_t>(stream), comm->pdl != 0, false});
+}
+
+int dlm_all_gather_loopback(const void* const* x, int64_t bytes, const DlmComm* comm, int nranks, dlm_stream_t stream) {
+    DeviceInfo info;
+    int rc = device_info(&info);
+    if (rc != DLM_OK) return rc;
+    if (x == nullptr || comm == nullptr) return DLM_ERR_NULL;
+    if (nranks < 1 || nranks > DLM_MAX_WORLD) return DLM_ERR_WORLD;
+    ReduceParams<kMaxWorld> p;
+    std::memset(&p, 0, sizeof(p));
+    for (int i = 0; i < nranks; ++i) {
+        rc = check_gather(&comm[i], x[i], bytes);
+        if (rc != DLM_OK) return rc;
+        if (comm[i].world != nranks || comm[i].rank != i || comm[i].recv_mc != nullptr) return DLM_ERR_WORLD;
+        fill_gather(&p.c[i], &comm[i], bytes);
+        p.partial[i] = static_cast<const __nv_bfloat16*>(x[i]);
+    }
+    int cap = info.sms / nranks;
+    if (cap > 16) cap = 16;
+    if (comm[0].max_ctas > 0 && comm[0].max_ctas < cap) cap = comm[0].max_ctas;
+    if (cap < 1) return DLM_ERR_GRID;
+    return launch_gather_loopback(p, gather_grid(bytes, cap), nranks, {static_cast<cudaStream_t>(stream), false, true});
+}
+
 int dlm_gemm_bf16(const DlmGemm* gemm, void* out, int64_t ldo, int pdl, dlm_stream_t stream) {
     int rc = check_gemm(gemm);
     if (rc != DLM_OK) return rc;

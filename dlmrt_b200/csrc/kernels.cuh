@@ -80,6 +80,8 @@ struct LaunchOpts {
 
 int launch_reduce(const ReduceParams<1>& p, int grid, int threads, const LaunchOpts& o);
 int launch_reduce_loopback(const ReduceParams<kMaxWorld>& p, int grid, int nranks, int threads, const LaunchOpts& o);
+int launch_gather(const ReduceParams<1>& p, int grid, const LaunchOpts& o);
+int launch_gather_loopback(const ReduceParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o);
 int launch_rowpar(const RowparParams<1>& p, int grid, const LaunchOpts& o);
 int launch_rowpar_loopback(const RowparParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o);
 int launch_moe(const MoeParams<1>& p, int grid, const LaunchOpts& o);

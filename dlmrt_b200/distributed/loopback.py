@@ -112,6 +112,31 @@ class LoopbackWorld:
         self._done(chain, outs)
         return outs
 
+    def all_gather(self, xs, key):
+        """All ranks of Group.all_gather in one launch; xs[r] is rank r's block. Returns every rank's [world, ...]."""
+        nbytes = xs[0].numel() * xs[0].element_size()
+        comms = (DlmComm * self.world)()
+        outs = []
+        for r, g in enumerate(self.groups):
+            out = g.symmetric(key, (self.world, *xs[r].shape), xs[r].dtype)
+            if key not in g._gather:
+                g.symmetric(key + ".slots", (3, self.world, nbytes // 2), armed=True)
+                epochs = torch.zeros(_lib.EPOCH_SLOTS, device=self.device, dtype=torch.int32)
+                g._gather[key] = list(g._handles[key + ".slots"].buffer_ptrs), epochs, 0
+            ptrs, epochs, _ = g._gather[key]
+            c = DlmComm()
+            c.rank, c.world = r, self.world
+            for s in range(self.world):
+                c.recv[s] = ptrs[s]
+            c.out, c.epochs, c.status = out.data_ptr(), epochs.data_ptr(), g.status.data_ptr()
+            c.timeout_ns, c.max_ctas = 500_000_000, g.max_ctas
+            comms[r] = c
+            outs.append(out)
+        ptrs = (C.c_void_p * self.world)(*[x.data_ptr() for x in xs])
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _lib.check(_lib.lib().dlm_all_gather_loopback(ptrs, nbytes, comms, self.world, stream), f"loopback all_gather {key}")
+        return outs
+
     def moe(self, descriptors, *, site, chain=0, hs=None, weight=None, eps=0.0, scale=1.0):
         """All ranks of the fused NVFP4 expert down-projection + reduction in one launch; descriptors[r] is rank r's
         DlmMoe (dlmrt_b200.quantization.nvfp4.descriptor)."""

@@ -107,6 +107,7 @@ class Group:
         self._last = {}      # per chain: the previous call's output buffer
         self._pending = {}   # partial data_ptr -> (linear, x): GEMMs deferred into the next reduction
         self._workspaces = {}
+        self._gather = {}    # per key: slot addresses, invocation counters, multicast address of the slots
         self.stamps = 0      # device address of a [grid, 4] int64 buffer to record kernel phase times
         self.status = torch.zeros(_lib.STATUS_WORDS, device=device, dtype=torch.int32)
         _lib.lib()  # fail now, not at the first reduction, when the library is missing
@@ -313,8 +314,28 @@ class Group:
         return x
 
     def all_gather(self, x, key):
-        """[world, *x.shape]: every rank's `x`, stacked in rank order (parallel.py:164-180). Off the hot path."""
+        """[world, *x.shape]: every rank's `x`, stacked in rank order (parallel.py:164-180): the row statistics of the
+        decoders, the one other collective of a round. Blocks of floating-point values whose size is a multiple of
+        16 bytes (up to 1 MiB) go through this library's barrier-free kernel (`dlm_all_gather`: multicast stores into
+        triple-buffered slots, in-band arrival); anything else takes torch's symmetric-memory path, as the reference."""
         out = self.symmetric(key, (self.world, *x.shape), x.dtype)
+        nbytes = x.numel() * x.element_size()
+        if x.is_floating_point() and x.is_contiguous() and nbytes % 16 == 0 and 0 < nbytes <= _lib.GATHER_MAX_BYTES:
+            if key not in self._gather:
+                slots = self.symmetric(key + ".slots", (3, self.world, nbytes // 2), armed=True)
+                epochs = torch.zeros(_lib.EPOCH_SLOTS, device=self.device, dtype=torch.int32)
+                self._gather[key] = list(self._handles[key + ".slots"].buffer_ptrs), epochs, self.multicast(slots)
+            ptrs, epochs, recv_mc = self._gather[key]
+            c = DlmComm()
+            c.rank, c.world = self.rank, self.world
+            for s in range(self.world):
+                c.recv[s] = ptrs[s]
+            c.recv_mc = recv_mc or None
+            c.out, c.epochs, c.status = out.data_ptr(), epochs.data_ptr(), self.status.data_ptr()
+            c.timeout_ns, c.pdl, c.max_ctas = TIMEOUT_NS, int(PDL), self.max_ctas
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            _lib.check(_lib.lib().dlm_all_gather(x.data_ptr(), nbytes, C.byref(c), stream), f"all_gather {key}")
+            return out
         if self.world == 1:
             out[0].copy_(x)
             return out

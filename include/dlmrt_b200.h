@@ -223,6 +223,20 @@ DLM_API size_t dlm_moe_workspace_bytes(int m, int n, int top_k);
 /* Single-GPU loopback of `nranks` ranks of dlm_rowpar_bf16 in one launch (see dlm_reduce_bf16_loopback). */
 DLM_API int dlm_rowpar_bf16_loopback(const DlmGemm* gemm, const DlmComm* comm, int nranks, dlm_stream_t stream);
 
+/* ---- all-gather of a small block (row statistics) ---------------------------------------------------------------
+ * Replaces Group.all_gather (dlmrt/distributed/parallel.py:164-180; callers ops/triton/decoding.py:126,
+ * models/diffusion_gemma/kernels.py:436,590), the one other collective of a round: every rank's `x` (`bytes` bytes, a
+ * multiple of 16, at most DLM_GATHER_MAX_BYTES) ends up in every rank's `comm->out` [world][bytes], in rank order,
+ * without a barrier: one multimem.st (or one store per rank) per 16 bytes into triple-buffered slots, arrival detected
+ * in band. Of `comm` only rank, world, recv (every rank's [3][world][bytes] buffer, armed with all-ones), recv_mc,
+ * out, epochs, status, timeout_ns, pdl and max_ctas are read. The payload must not contain an all-ones 32-bit word
+ * (FP32 / FP16 / BF16 values never do). */
+#define DLM_GATHER_MAX_BYTES (1 << 20)
+DLM_API int dlm_all_gather(const void* x, int64_t bytes, const DlmComm* comm, dlm_stream_t stream);
+/* All ranks in one cooperative launch on one GPU (tests), as the other *_loopback entry points. */
+DLM_API int dlm_all_gather_loopback(const void* const* x, int64_t bytes, const DlmComm* comm, int nranks,
+                                    dlm_stream_t stream);
+
 /* Bytes of workspace (FP32 split-K partial tiles + tile counters) a GEMM of this shape needs. */
 DLM_API size_t dlm_workspace_bytes(int m, int n, int k);
 

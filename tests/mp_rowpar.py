@@ -106,6 +106,15 @@ def main():
             group.check()
             assert_same_bits(bits(out), red.reduce(all_p), f"small reduce {rep} (one-shot limit {limit})")
     assert one_hop == 1
+    # the round's other collective: all-gather of row statistics, several invocations per key
+    for key, shape in (("row_stats", (32, 4)), ("logit_stats", (256, 2))):
+        for call in range(4):
+            stats = torch.randn(*shape, generator=torch.Generator().manual_seed(50 * call + rank)).to(dev)
+            got = group.all_gather(stats, key)
+            torch.cuda.synchronize()
+            group.check()
+            want = torch.stack([t.to(dev) for t in gather(stats)])
+            assert torch.equal(got.view(torch.int32), want.view(torch.int32)), f"all_gather {key} call {call}"
     dist.barrier()
     if rank == 0:
         print(f"MULTIGPU_OK world={world} multicast={report['multicast']}")

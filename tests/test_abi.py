@@ -105,6 +105,23 @@ def test_fused_requires_matching_shapes():
     assert _lib.lib().dlm_rowpar_bf16(C.byref(gemm(n=512)), C.byref(c), None) == _lib.ERR_SHAPE
 
 
+def test_all_gather_rejects_bad_arguments():
+    lib = _lib.lib()
+    c = DlmComm()
+    c.rank, c.world = 0, 2
+    assert lib.dlm_all_gather(None, 64, C.byref(c), None) == _lib.ERR_NULL
+    assert lib.dlm_all_gather(4096, 60, C.byref(c), None) == _lib.ERR_SHAPE          # not a multiple of 16 bytes
+    assert lib.dlm_all_gather(4096, _lib.GATHER_MAX_BYTES + 16, C.byref(c), None) == _lib.ERR_SHAPE
+    assert lib.dlm_all_gather(4096, 64, C.byref(c), None) == _lib.ERR_NULL           # no out, epochs, slots
+    c.out, c.epochs = 8192, 12288
+    c.recv[0] = 16384
+    assert lib.dlm_all_gather(4096, 64, C.byref(c), None) == _lib.ERR_NULL           # rank 1's slots missing
+    c.recv[1] = 16392
+    assert lib.dlm_all_gather(4096, 64, C.byref(c), None) == _lib.ERR_ALIGN
+    c.world = 9
+    assert lib.dlm_all_gather(4096, 64, C.byref(c), None) == _lib.ERR_WORLD
+
+
 def test_device_loop_rejects_bad_programs_before_touching_cuda():
     from dlmrt_b200._lib import DlmLoop, DlmLoopPart
     from dlmrt_b200.ops.block_graph import BlockGraph, StagedLoopGraph

@@ -132,6 +132,50 @@ def test_withheld_push_times_out_without_trapping(one_shot):
     run_sequence(2, 8, 256, calls=3, seed=7)
 
 
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_all_gather_of_row_statistics(world):
+    """The round's other collective (parallel.py:164-180): every rank's block of statistics in every rank's output,
+    in rank order, over several invocations (the slots are triple-buffered and re-armed) and for several payloads."""
+    from dlmrt_b200.distributed.loopback import LoopbackWorld
+
+    lw = LoopbackWorld(world)
+    for key, shape, dtype in (("row_stats32", (32, 4), torch.float32), ("logit_stats", (256, 2), torch.float32),
+                              ("wide", (8, 4096), torch.bfloat16)):
+        for call in range(5):
+            g = torch.Generator().manual_seed(1000 * call + len(key))
+            xs = [(torch.randn(*shape, generator=g) * (r + 1)).to(dtype).cuda() for r in range(world)]
+            if call == 3:  # special values travel too: infinities, NaN, signed zeros
+                for x in xs:
+                    x.view(-1)[:4] = torch.tensor([float("inf"), float("-inf"), float("nan"), -0.0], dtype=dtype)
+            outs = lw.all_gather(xs, key)
+            torch.cuda.synchronize()
+            lw.check()
+            want = torch.stack(xs)
+            view = torch.int32 if dtype == torch.float32 else torch.int16
+            for r, out in enumerate(outs):
+                assert out.shape == (world, *shape) and out.dtype == dtype
+                assert torch.equal(out.view(view), want.view(view)), f"{key} call {call} rank {r}"
+
+
+def test_group_all_gather_world_one_and_fallback():
+    from dlmrt_b200 import _lib
+    from dlmrt_b200.distributed.parallel import Group
+
+    g = Group.local("cuda:0")
+    x = torch.randn(32, 4, device="cuda")
+    before = _lib.lib().dlm_launch_count()
+    for _ in range(4):
+        out = g.all_gather(x, "stats")
+    torch.cuda.synchronize()
+    g.check()
+    assert _lib.lib().dlm_launch_count() == before + 4 and torch.equal(out[0], x)
+    odd = torch.randn(5, 3, device="cuda")  # 60 bytes: not a multiple of 16, takes the plain path
+    assert torch.equal(g.all_gather(odd, "odd")[0], odd)
+    ints = torch.full((8, 4), -1, dtype=torch.int32, device="cuda")  # all-ones words: never through the flagged slots
+    assert torch.equal(g.all_gather(ints, "ints")[0], ints)
+    assert _lib.lib().dlm_launch_count() == before + 4
+
+
 def test_reference_kernel_agrees_bit_for_bit():
     """This library's kernel, the reference's own kernel (built from its sources into oracle/_ref) and the CPU
     oracle on the same seeded inputs, world 1 (one GPU): all three modes, several invocations."""
