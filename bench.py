@@ -98,6 +98,10 @@ def cpu_layer_seconds(world, repeats):
     for o_proj and down_proj. Returns the median seconds per layer over `repeats`."""
     import torch
 
+    # All the host's cores, also under torchrun (which starts every rank with OMP_NUM_THREADS=1).
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    if torch.get_num_threads() < cores:
+        torch.set_num_threads(cores)
     g = torch.Generator().manual_seed(0)
     h = torch.randn(ROWS, HIDDEN, generator=g).to(torch.bfloat16)
     norm = (torch.randn(HIDDEN, generator=g) * 0.1 + 1).to(torch.bfloat16)
