@@ -1,6 +1,6 @@
 """Builds the REFERENCE's own fused-reduction extension into oracle/_ref/ (test infrastructure only).
 
-    python oracle/build_ref.py /path/to/reference
+    python oracle/build_ref.py [/path/to/reference]     (default: $DLMRT_REFERENCE, else ../reference)
 
 The source file dlmrt/ops/csrc/tp_comm.cu is compiled where it lies in the reference tree, with the flags the
 reference's own loader uses (dlmrt/ops/extensions.py:46-50: -O3 -std=c++17 -gencode=arch=compute_100a,code=sm_100a);
@@ -16,6 +16,16 @@ from pathlib import Path
 
 NAME = "dlmrt_tp_comm_sm100a"
 OUT = Path(__file__).resolve().parent / "_ref"
+
+
+def reference_tree():
+    """Where the reference's sources lie: $DLMRT_REFERENCE, else a `reference` folder beside this repository.
+    None when neither exists (a machine that only carries the prebuilt oracle/_ref)."""
+    candidates = [os.environ.get("DLMRT_REFERENCE"), Path(__file__).resolve().parent.parent.parent / "reference"]
+    for c in candidates:
+        if c and (Path(c) / "dlmrt" / "ops" / "csrc" / "tp_comm.cu").exists():
+            return Path(c)
+    return None
 
 
 def build(reference):
@@ -47,4 +57,4 @@ def load_built():
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    print(build(sys.argv[1] if len(sys.argv) > 1 else reference_tree()))
