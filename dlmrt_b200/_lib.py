@@ -12,13 +12,10 @@ NOALLOC_SCRATCH_BYTES = 8 << 20
 GATHER_MAX_BYTES = 1 << 20
 
 OK, ERR_SHAPE, ERR_ALIGN, ERR_WORLD, ERR_NULL, ERR_GRID, ERR_CUDA, ERR_WORKSPACE, ERR_TIMEOUT, ERR_ARCH, \
-    ERR_SCRATCH = 0, -1, -2, -3, -4, -5, -6, -7, -8, -9, -10
+    ERR_SCRATCH, ERR_OVERLAP = 0, -1, -2, -3, -4, -5, -6, -7, -8, -9, -10, -11
 REDUCE, REDUCE_NORM, REDUCE_NORM_RESIDUAL = 0, 1, 2
 
-import os
-
-# DLMRT_B200_LIB points at another build of the same library (kernel experiments); the default is the in-tree build.
-LIB_PATH = Path(os.environ.get("DLMRT_B200_LIB") or Path(__file__).resolve().parent / "libdlmrt_b200.so")
+LIB_PATH = Path(__file__).resolve().parent / "libdlmrt_b200.so"
 
 
 class DlmComm(C.Structure):
@@ -34,7 +31,7 @@ class DlmComm(C.Structure):
 class DlmGemm(C.Structure):
     _fields_ = [("x", C.c_void_p), ("w", C.c_void_p), ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
                 ("ldx", C.c_int64), ("ldw", C.c_int64), ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
-                ("splits", C.c_int32), ("token_tiles", C.c_int32), ("w_tiled", C.c_int32), ("use_cluster", C.c_int32)]
+                ("splits", C.c_int32), ("token_tiles", C.c_int32), ("w_tiled", C.c_int32), ("reserved", C.c_int32)]
 
 
 class DlmMoe(C.Structure):

@@ -1,7 +1,5 @@
 // extern "C" boundary of libdlmrt_b200.so (include/dlmrt_b200.h): argument checks, tensor-map construction, launch.
 // Mirrors the host checks of the reference's launch<> (dlmrt/ops/csrc/tp_comm.cu:282-287) as return codes.
-#include <cstdio>
-#include <cstdlib>
 #include <cstring>
 
 #include "../../include/dlmrt_b200.h"
@@ -83,7 +81,7 @@ void fill_comm(CommDev* d, const DlmComm* c) {
     d->epochs = c->epochs;
     d->status = c->status;
     d->stamps = reinterpret_cast<long long*>(c->stamps);
-    d->timeout_ns = c->timeout_ns > 0 ? c->timeout_ns : 2000000000ll;
+    d->timeout_ns = c->timeout_ns > 0 ? c->timeout_ns : kDefaultTimeoutNs;
     d->rank = c->rank;
     d->world = c->world;
     d->rows = c->rows;
@@ -134,28 +132,19 @@ int make_map(CUtensorMap* map, const void* base, int rows, int cols, long long l
     return DLM_OK;
 }
 
-// Can the `splits` CTAs of each of `clusters` tiles run as co-resident thread-block clusters (partials exchanged through
-// distributed shared memory)? The partial tile must also fit over the drained pipeline stages.
-bool cluster_fits(int mt, int splits, int clusters) {
-    if (splits < 2 || splits > 8) return false;
-    const int stage = kBlockF * kBlockK * 2 + mt * kBlockK * 2;
-    if (mt * kBlockF * 4 > rowpar_stages(mt) * stage) return false;
-    return rowpar_max_clusters(mt, splits) >= clusters;
-}
-
 // Picks (token tiles, K splits) for a [m, n, k] GEMM on `avail` CTAs with a cost model fitted to measurements on B200
 // (256 x 2560 outputs, K from 512 to 9728, every tiling, and phase stamps of the fused kernel at one and two ranks;
 // microseconds):
 //   4.8                          launch, prologue, first loads, epilogue and push
 //   + kb * (0.24 + 0.0009 * mt)  kb k-blocks per CTA; a k-block costs more the more tokens (mt) the tile holds
 //   + 2.8 + 0.019 * mt           if K is split: FP32 partial tiles out to L2, the rendezvous, and the tiles read back
-//                                (5.2 at 128 tokens, 7.7 at 256; a cluster: about 1). Fused at ONE rank the rows'
+//                                (5.2 at 128 tokens, 7.7 at 256). Fused at ONE rank the rows'
 //                                owners read the partials themselves, one rendezvous less: 0.3 + 0.0176 * mt
 //   + 1.3 + 0.5 * (rows - 1)     owner phase of the reduction, rows = ceil(R / CTAs) per CTA (later rows overlap)
 // and never less than the weight shard takes to stream from HBM. Long K (TP = 1) ends up split seven ways over 140 SMs,
 // short K (TP = 8) tiled along the tokens, in between a mix of both.
-void choose_tiling(int m, int n, int k, int avail, int* tiles_out, int* splits_out, bool clusters = false, int ranks = 1,
-                   int owner_rows = 0, bool single_rank = false) {
+void choose_tiling(int m, int n, int k, int avail, int* tiles_out, int* splits_out, int owner_rows = 0,
+                   bool single_rank = false) {
     const double hbm_bytes_per_us = 6.0e6;
     const int feature_tiles = n / kBlockF, nkb = (k + kBlockK - 1) / kBlockK;
     double best = 1e30;
@@ -174,8 +163,7 @@ void choose_tiling(int m, int n, int k, int avail, int* tiles_out, int* splits_o
             if (us < hbm) us = hbm;
             us += 4.8;
             if (sp > 1) {
-                if (clusters && cluster_fits(mt, sp, feature_tiles * t * ranks)) us += 1.0;
-                else if (single_rank && owner_rows > 0) us += 0.3 + 0.0176 * mt;
+                if (single_rank && owner_rows > 0) us += 0.3 + 0.0176 * mt;
                 else us += 2.8 + 0.019 * mt;
             }
             if (owner_rows > 0) us += 1.3 + 0.5 * ((owner_rows + ctas - 1) / ctas - 1);
@@ -195,7 +183,7 @@ int check_gemm(const DlmGemm* g) {
     if (g->n < kBlockF || g->n % kBlockF || g->k < kBlockK || g->k % 8) return DLM_ERR_SHAPE;
     if (g->n / kBlockF > 64) return DLM_ERR_SHAPE;
     if (g->ldx < g->k || g->ldx % 8 || (!g->w_tiled && (g->ldw < g->k || g->ldw % 8))) return DLM_ERR_ALIGN;
-    if (g->w_tiled < 0 || g->w_tiled > 1 || g->use_cluster < 0 || g->use_cluster > 1) return DLM_ERR_SHAPE;
+    if (g->w_tiled < 0 || g->w_tiled > 1) return DLM_ERR_SHAPE;
     if (!aligned16(g->x) || !aligned16(g->w) || (reinterpret_cast<uintptr_t>(g->workspace) & 255)) return DLM_ERR_ALIGN;
     if (g->splits < 0 || g->splits > kMaxSplits) return DLM_ERR_SHAPE;
     if (g->token_tiles < 0 || (g->token_tiles > 0 && (g->m % (16 * g->token_tiles) || g->token_tiles > 16)))
@@ -204,23 +192,15 @@ int check_gemm(const DlmGemm* g) {
 }
 
 // Fills the device-side GEMM block; returns the per-rank grid in *grid.
-int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid, int ranks = 1, int owner_rows = 0,
+int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid, int owner_rows = 0,
               bool single_rank = false) {
     std::memset(d, 0, sizeof(*d));
     const int avail = max_ctas > 0 && max_ctas < sms ? max_ctas : sms;
     const int feature_tiles = g->n / kBlockF, nkb = (g->k + kBlockK - 1) / kBlockK;
     int token_tiles = g->token_tiles, splits = g->splits;
-    if (token_tiles == 0 && splits == 0) {
-        // Tuning aid: DLMRT_TILING="<token tiles>,<splits>" overrides the library's choice where the caller left both open.
-        if (const char* e = getenv("DLMRT_TILING")) {
-            int t = 0, sp = 0;
-            if (sscanf(e, "%d,%d", &t, &sp) == 2 && t > 0 && sp > 0 && sp <= kMaxSplits && g->m % (16 * t) == 0)
-                token_tiles = t, splits = sp;
-        }
-    }
     if (token_tiles == 0 || splits == 0) {
         int t = 1, sp = 1;
-        choose_tiling(g->m, g->n, g->k, avail, &t, &sp, g->use_cluster, ranks, owner_rows, single_rank);
+        choose_tiling(g->m, g->n, g->k, avail, &t, &sp, owner_rows, single_rank);
         if (token_tiles == 0 && splits == 0) {
             token_tiles = t;
             splits = sp;
@@ -238,9 +218,7 @@ int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid, in
     if (g->w_tiled) d->w_tiles = static_cast<const uint8_t*>(g->w);
     if (rc == DLM_OK) rc = make_map(&d->tm_x, g->x, g->m, g->k, g->ldx, mt);
     if (rc != DLM_OK) return rc;
-    const bool in_cluster = g->use_cluster && cluster_fits(mt, splits, tiles * ranks);
-    const size_t need =
-        kWorkspaceHeader + (splits > 1 && !in_cluster ? static_cast<size_t>(splits) * g->m * g->n * sizeof(float) : 0);
+    const size_t need = kWorkspaceHeader + (splits > 1 ? static_cast<size_t>(splits) * g->m * g->n * sizeof(float) : 0);
     if (g->workspace_bytes < static_cast<int64_t>(need)) return DLM_ERR_WORKSPACE;
     d->gen = static_cast<int*>(g->workspace);
     d->counters = d->gen + kEpochSlots;
@@ -251,7 +229,6 @@ int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid, in
     d->splits = splits;
     d->token_tiles = token_tiles;
     d->stages = rowpar_stages(mt);
-    d->cluster = g->use_cluster && cluster_fits(mt, splits, tiles * ranks) ? 1 : 0;
     *grid = tiles * splits;
     return DLM_OK;
 }
@@ -324,7 +301,7 @@ void fill_gather(CommDev* d, const DlmComm* c, int64_t bytes) {
     d->out = static_cast<__nv_bfloat16*>(c->out);
     d->epochs = c->epochs;
     d->status = c->status;
-    d->timeout_ns = c->timeout_ns > 0 ? c->timeout_ns : 2000000000ll;
+    d->timeout_ns = c->timeout_ns > 0 ? c->timeout_ns : kDefaultTimeoutNs;
     d->rank = c->rank;
     d->world = c->world;
     d->rows = d->R = d->slot_rows = 1;
@@ -391,7 +368,7 @@ int dlm_gemm_bf16(const DlmGemm* gemm, void* out, int64_t ldo, int pdl, dlm_stre
     p.g[0].out = static_cast<__nv_bfloat16*>(out);
     p.g[0].ldo = ldo;
     p.fused = 0;
-    return launch_rowpar(p, grid, {static_cast<cudaStream_t>(stream), pdl != 0, false, p.g[0].cluster ? p.g[0].splits : 1});
+    return launch_rowpar(p, grid, {static_cast<cudaStream_t>(stream), pdl != 0, false});
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -433,6 +410,10 @@ int dlm_gemm_bf16_noalloc(const void* x, const void* w, void* out, int m, int n,
     if (out == nullptr) return DLM_ERR_NULL;
     if (!aligned16(out) || ldo < n || ldo % 8) return DLM_ERR_ALIGN;
     const size_t per_split = static_cast<size_t>(m) * n * sizeof(float);
+    // K cannot be split into more ranges than it has k-blocks: a larger request runs as that many (as dlm_gemm_bf16
+    // does), and it is that number the scratch must hold.
+    const int nkb = (k + kBlockK - 1) / kBlockK;
+    if (g.splits > nkb) g.splits = splits = nkb;
     // An explicit request that does not fit is refused; splits the library picks are capped to what fits
     // (one split needs no partial tiles at all).
     if (splits > 1 && kWorkspaceHeader + splits * per_split > DLM_NOALLOC_SCRATCH_BYTES) return DLM_ERR_SCRATCH;
@@ -463,7 +444,12 @@ int dlm_gemm_bf16_noalloc(const void* x, const void* w, void* out, int m, int n,
     // generation and arrival counters); the partial tiles are fully rewritten before they are read.
     const cudaError_t err = cudaMemsetAsync(scratch, 0, kWorkspaceHeader, s);
     if (err != cudaSuccess) return cuda_fail(err);
-    return launch_rowpar(p, grid, {s, pdl != 0, false, 1});
+    return launch_rowpar(p, grid, {s, pdl != 0, false});
+}
+
+static bool overlaps(const void* a, size_t a_bytes, const void* b, size_t b_bytes) {
+    const uintptr_t a0 = reinterpret_cast<uintptr_t>(a), b0 = reinterpret_cast<uintptr_t>(b);
+    return a != nullptr && b != nullptr && a0 < b0 + b_bytes && b0 < a0 + a_bytes;
 }
 
 static int check_pair(const DlmGemm* gemm, const DlmComm* comm) {
@@ -471,6 +457,13 @@ static int check_pair(const DlmGemm* gemm, const DlmComm* comm) {
     if (rc == DLM_OK) rc = check_comm(comm);
     if (rc != DLM_OK) return rc;
     if (gemm->m != comm->rows || gemm->n != comm->n || comm->n > DLM_FUSED_MAX_N) return DLM_ERR_SHAPE;
+    // The fused kernel re-arms `rearm` and fills `out` while other CTAs may still be loading x: the GEMM's input must
+    // be neither (in the reference the GEMM is an earlier kernel, so there the aliasing is harmless).
+    const size_t x_bytes = (static_cast<size_t>(gemm->m - 1) * gemm->ldx + gemm->k) * 2;
+    const size_t out_bytes = static_cast<size_t>(comm->rows) * comm->n * 2;
+    if (overlaps(gemm->x, x_bytes, comm->rearm, static_cast<size_t>(comm->rearm_bytes)) ||
+        overlaps(gemm->x, x_bytes, comm->out, out_bytes))
+        return DLM_ERR_OVERLAP;
     return DLM_OK;
 }
 
@@ -483,12 +476,11 @@ int dlm_rowpar_bf16(const DlmGemm* gemm, const DlmComm* comm, dlm_stream_t strea
     RowparParams<1> p;
     std::memset(&p, 0, sizeof(p));
     int grid = 0;
-    rc = fill_gemm(&p.g[0], gemm, comm->max_ctas, info.sms, &grid, 1, comm->rows / comm->world, comm->world == 1);
+    rc = fill_gemm(&p.g[0], gemm, comm->max_ctas, info.sms, &grid, comm->rows / comm->world, comm->world == 1);
     if (rc != DLM_OK) return rc;
     fill_comm(&p.c[0], comm);
     p.fused = 1;
-    return launch_rowpar(p, grid, {static_cast<cudaStream_t>(stream), comm->pdl != 0, false,
-                                   p.g[0].cluster ? p.g[0].splits : 1});
+    return launch_rowpar(p, grid, {static_cast<cudaStream_t>(stream), comm->pdl != 0, false});
 }
 
 static int check_moe(const DlmMoe* m) {
@@ -631,15 +623,14 @@ int dlm_rowpar_bf16_loopback(const DlmGemm* gemm, const DlmComm* comm, int nrank
         if (gemm[i].m != gemm[0].m || gemm[i].n != gemm[0].n || gemm[i].k != gemm[0].k) return DLM_ERR_SHAPE;
         int cap = comm[0].max_ctas > 0 && comm[0].max_ctas < per_rank ? comm[0].max_ctas : per_rank;
         int gi = 0;
-        rc = fill_gemm(&p.g[i], &gemm[i], cap, per_rank, &gi, nranks, comm[i].rows / comm[i].world, comm[i].world == 1);
+        rc = fill_gemm(&p.g[i], &gemm[i], cap, per_rank, &gi, comm[i].rows / comm[i].world, comm[i].world == 1);
         if (rc != DLM_OK) return rc;
         if (i > 0 && gi != grid) return DLM_ERR_SHAPE;
         grid = gi;
         fill_comm(&p.c[i], &comm[i]);
     }
     p.fused = 1;
-    return launch_rowpar_loopback(p, grid, nranks, {static_cast<cudaStream_t>(stream), false, true,
-                                                    p.g[0].cluster ? p.g[0].splits : 1});
+    return launch_rowpar_loopback(p, grid, nranks, {static_cast<cudaStream_t>(stream), false, true});
 }
 
 size_t dlm_workspace_bytes(int m, int n, int k) {
@@ -695,6 +686,7 @@ const char* dlm_strerror(int code) {
         case DLM_ERR_WORKSPACE: return "workspace too small (dlm_workspace_bytes)";
         case DLM_ERR_TIMEOUT: return "device wait ran out: data from a rank never arrived";
         case DLM_ERR_ARCH: return "not an sm_100 device";
+        case DLM_ERR_OVERLAP: return "the fused GEMM's input overlaps a buffer the same launch re-arms or writes (rearm, out)";
         case DLM_ERR_SCRATCH: return "requested K splits need more than the library's built-in scratch (DLM_NOALLOC_SCRATCH_BYTES)";
         default: return "unknown error";
     }

@@ -57,6 +57,7 @@ struct CommDev {
 struct CommCtx {
     int block, blocks;  // this CTA's index among the CTAs of its rank, and their number
     int e, buf;         // invocation number and receive buffer e % 3
+    int dead;           // an earlier call on this group failed: push nothing, accept nothing (see comm_begin)
     long long deadline;
     size_t slot_elems, buf_elems;
 };
@@ -65,13 +66,24 @@ __device__ __forceinline__ void stamp(const CommDev& c, const CommCtx& x, int ph
     if (c.stamps && threadIdx.x == 0) c.stamps[x.block * kStampSlots + phase] = globaltimer();
 }
 
-// `previous` is epochs[block] as read after the previous kernel completed (callers may have fetched it early).
-__device__ __forceinline__ CommCtx comm_begin(const CommDev& c, int block, int blocks, int previous) {
+// `previous` is epochs[block] and `failed` is status[0], both as read after the previous kernel completed (callers may
+// have fetched them early). A failure is sticky: once a wait of this group ran out, receive slots may hold vectors of an
+// older invocation that would pass for arrived data, so every later call pushes nothing, waits for nothing and
+// broadcasts nothing (its peers' waits run out in turn and every rank learns of it) until the host has read the status
+// and rebuilt the group.
+__device__ __forceinline__ int comm_failed(const CommDev& c) {
+    int v = 0;
+    if (c.status) asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(c.status) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ CommCtx comm_begin(const CommDev& c, int block, int blocks, int previous, int failed) {
     CommCtx x;
     x.block = block;
     x.blocks = blocks;
     x.e = previous + 1;
     x.buf = x.e % 3;
+    x.dead = failed != 0;
     x.deadline = globaltimer() + c.timeout_ns;
     x.slot_elems = static_cast<size_t>(c.slot_rows) * c.n;
     x.buf_elems = static_cast<size_t>(c.world) * x.slot_elems;
@@ -87,6 +99,7 @@ __device__ __forceinline__ __nv_bfloat16* push_address(const CommDev& c, const C
 // Stores one 16-byte vector of this rank's partial (row, col) where the protocol wants it: into the owner's slot, or
 // (one-shot) into this rank's slot on every rank.
 __device__ __forceinline__ void push_store(const CommDev& c, const CommCtx& x, int row, int col, uint4 v) {
+    if (x.dead) return;
     if (!c.one_shot) {
         store_v4(push_address(c, x, row, col), v);
         return;
@@ -135,6 +148,7 @@ __device__ __forceinline__ void rearm(const CommDev& c, const CommCtx& x, int pa
 __device__ __forceinline__ bool poll_all(const __nv_bfloat16* base, size_t stride, int world, uint4 (&v)[kMaxWorld],
                                          const CommDev& c, const CommCtx& x, int phase, unsigned pending = ~0u) {
     pending &= (1u << world) - 1;
+    if (x.dead) return false;
     if (!pending) return true;
     while (true) {
         const unsigned was = pending;

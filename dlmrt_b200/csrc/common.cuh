@@ -162,28 +162,6 @@ __device__ __forceinline__ bool elect_one() {
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Thread-block clusters: barrier and distributed shared memory
-// ---------------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
-__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-
-// Address, in the cluster's shared window, of this CTA's shared address `local` as seen in CTA `rank` of the cluster.
-__device__ __forceinline__ uint32_t cluster_map(uint32_t local, int rank) {
-    uint32_t remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
-    return remote;
-}
-
-__device__ __forceinline__ float4 cluster_load_f4(uint32_t addr) {
-    float4 v;
-    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                 : "r"(addr)
-                 : "memory");
-    return v;
-}
-
-// ---------------------------------------------------------------------------------------------------------------
 // TMA (tiled bulk tensor loads into this CTA's shared memory; no cluster multicast anywhere in this library)
 // ---------------------------------------------------------------------------------------------------------------
 constexpr uint64_t kEvictNormal = 0x1000000000000000ull;

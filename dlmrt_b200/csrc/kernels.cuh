@@ -16,6 +16,7 @@ constexpr int kMaxTiles = 128;      // (feature tiles) x (token tiles) of one GE
 constexpr int kWorkspaceHeader = 2048;  // int32 gen[256] then int32 counters[2][128]
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 200 * 1024;
+constexpr long long kDefaultTimeoutNs = 30000000000ll;  // budget of a device wait when the caller passes 0 (tp_comm.cu:67-70: ~30 s)
 
 // The GEMM half of one rank. `out` is used by the plain GEMM (no communication) only.
 struct alignas(64) GemmDev {
@@ -28,7 +29,6 @@ struct alignas(64) GemmDev {
     __nv_bfloat16* out;
     long long ldo;
     int m, n, k, splits, token_tiles, stages;
-    int cluster;       // the K splits of a tile form a thread-block cluster and meet in distributed shared memory
 };
 
 template <int NR>
@@ -75,7 +75,6 @@ struct LaunchOpts {
     cudaStream_t stream;
     bool pdl;
     bool cooperative;
-    int cluster = 1;  // CTAs per cluster along x
 };
 
 int launch_reduce(const ReduceParams<1>& p, int grid, int threads, const LaunchOpts& o);
@@ -91,7 +90,6 @@ int moe_stages(int rows_cap);
 int rowpar_smem_bytes(int m, int stages);
 int rowpar_stages(int m);
 int rowpar_max_ctas_per_sm(int m);
-int rowpar_max_clusters(int tokens_per_tile, int cluster);  // co-resident clusters of that size, 0 if unsupported
 
 extern int g_last_cuda_error;
 extern long long g_launches;

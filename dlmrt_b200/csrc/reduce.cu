@@ -19,7 +19,8 @@ __global__ void __launch_bounds__(MAXT, 1) reduce_kernel(const __grid_constant__
     const CommDev& c = p.c[slot];
     __shared__ float scratch[64];
     pdl_wait();
-    const CommCtx x = comm_begin(c, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), c.epochs[blockIdx.x]);
+    const CommCtx x = comm_begin(c, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), c.epochs[blockIdx.x],
+                                 comm_failed(c));
     stamp(c, x, 0);
     push_partial(c, x, p.partial[slot]);
     stamp(c, x, 1);
@@ -40,7 +41,8 @@ __global__ void __launch_bounds__(256, 1) gather_kernel(const __grid_constant__ 
     const int slot = NR == 1 ? 0 : static_cast<int>(blockIdx.y);
     const CommDev& c = p.c[slot];
     pdl_wait();
-    const CommCtx x = comm_begin(c, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), c.epochs[blockIdx.x]);
+    const CommCtx x = comm_begin(c, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), c.epochs[blockIdx.x],
+                                 comm_failed(c));
     const int vecs = c.n / kVec;
     const int stride = x.blocks * blockDim.x;
     const int first = x.block * blockDim.x + threadIdx.x;
@@ -54,8 +56,8 @@ __global__ void __launch_bounds__(256, 1) gather_kernel(const __grid_constant__ 
     for (int i = first; i < vecs * c.world; i += stride) {  // slot s = i / vecs, vector i % vecs
         const __nv_bfloat16* src = mine + static_cast<size_t>(i) * kVec;
         uint4 v;
-        bool ok = true;
-        while (true) {
+        bool ok = !x.dead;
+        while (ok) {
             v = load_volatile(src);
             if (v.x != 0xFFFFFFFFu && v.y != 0xFFFFFFFFu && v.z != 0xFFFFFFFFu && v.w != 0xFFFFFFFFu) break;
             if (globaltimer() > x.deadline) {

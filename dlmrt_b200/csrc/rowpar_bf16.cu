@@ -20,8 +20,6 @@
 //   the splits in split order (the value never depends on timing). Either way each token row's 256 bytes are stored
 //   (plain GEMM) or pushed straight into the owner rank's receive slot over NVLink, and every CTA goes on to the
 //   re-arm / own / collect phases of the reduction (comm.cuh).
-#include <cstdlib>
-
 #include "kernels.cuh"
 
 namespace dlm {
@@ -33,7 +31,7 @@ struct SmemLayout {
     uint64_t empty[kMaxStages];
     uint64_t acc_full;
     uint32_t tmem_base;
-    int epoch, gen;  // epochs[block] and gen[block], fetched by a spare warp while the pipeline runs
+    int epoch, gen, failed;  // epochs[block], gen[block] and status[0], fetched by a spare warp while the pipeline runs
     float scratch[64];
 };
 
@@ -151,9 +149,9 @@ __device__ __forceinline__ void own_rows_from_splits(const GemmDev& g, const Com
     stamp(c, x, 3);
 }
 
-// The early L2 prefetch pays where the next kernel's CTAs can start while this one still runs (narrow tiles, two CTAs
-// per SM); with 256-token tiles a CTA starts only when its SM is free and the stream is already bandwidth-bound.
-__device__ __forceinline__ bool getenv_prefetch(int, int mt) { return mt <= 128; }
+// The early L2 prefetch of the rest of the weight slab pays for narrow tiles only; with 256-token tiles the stream is
+// already bandwidth-bound when the CTA starts.
+__device__ __forceinline__ bool prefetch_rest_of_slab(int mt) { return mt <= 128; }
 
 template <int NR>
 __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_constant__ RowparParams<NR> p) {
@@ -183,7 +181,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
     const int issuers = cols <= 128 && iters >= 2 ? 2 : 1;  // MMA-issuing threads, each with its own accumulator
     // One rank, K split: the owner of a row sums the FP32 split partials itself (in split order), so the BF16 partial
     // never travels through the receive slots; the value is the same, bit for bit, as pushing and summing one rank.
-    const bool local_rows = p.fused && c.world == 1 && g.splits > 1 && !g.cluster;
+    const bool local_rows = p.fused && c.world == 1 && g.splits > 1;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < g.stages; ++i) {
@@ -201,7 +199,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
     tcgen05_fence_after();
     const uint32_t tmem = sm->tmem_base;
     // Budget of the local pipeline and of the split-K rendezvous; the cross-rank waits take theirs in comm_begin.
-    const long long pipeline_deadline = globaltimer() + (c.timeout_ns > 0 ? c.timeout_ns : 2000000000ll);
+    const long long pipeline_deadline = globaltimer() + (c.timeout_ns > 0 ? c.timeout_ns : kDefaultTimeoutNs);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -217,7 +215,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
             }
             // The rest of this CTA's weight slab is pulled into L2 now, while the previous kernel of the stream is still
             // finishing: weights never depend on it, and the ring then refills at L2 latency instead of HBM latency.
-            if (iters > pre && getenv_prefetch(g.stages, mt)) {
+            if (iters > pre && prefetch_rest_of_slab(mt)) {
                 if (g.w_tiles) {
                     bulk_prefetch_l2(g.w_tiles + (static_cast<size_t>(f) * nkb + kb0 + pre) * kTileBytesW,
                                      static_cast<uint32_t>(iters - pre) * kTileBytesW);
@@ -258,7 +256,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
         if (lane == 0) {
             if (who == 1) {
                 pdl_wait();
-                if (p.fused) sm->epoch = c.epochs[block];
+                if (p.fused) sm->epoch = c.epochs[block], sm->failed = comm_failed(c);
                 if (g.splits > 1) sm->gen = g.gen[block];
             }
             if (who < issuers) {
@@ -305,12 +303,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
         // One K split: the BF16 tile is staged in shared memory, token-major, over the drained pipeline stages.
         // Several: this CTA's FP32 partial tile goes to the workspace (which the previous kernel of the chain may
         // still be reading, hence the wait).
-        // With a cluster the partial tile stays in this CTA's shared memory (over the drained stages), where the other
-        // CTAs of the cluster read it.
-        float* part = g.cluster ? reinterpret_cast<float*>(tiles)
-                                : g.ws + (static_cast<size_t>(tile) * g.splits + s) * mt * kBlockF;
+        float* part = g.ws + (static_cast<size_t>(tile) * g.splits + s) * mt * kBlockF;
         __nv_bfloat16* staged = reinterpret_cast<__nv_bfloat16*>(tiles);
-        if (g.splits > 1 && !g.cluster) pdl_wait();
+        if (g.splits > 1) pdl_wait();
         for (int chunk = half; chunk < mt / 16; chunk += 2) {
             uint32_t r[16];
             if (iters > 0 && ok) {
@@ -349,55 +344,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
 
     CommCtx x{};
     if (p.fused) {
-        x = comm_begin(c, block, blocks, sm->epoch);
+        x = comm_begin(c, block, blocks, sm->epoch, sm->failed);
         stamp(c, x, 0);
     }
-    if (g.splits > 1 && g.cluster) {
-        // Split-K inside a cluster: the CTAs of a tile are one thread-block cluster (cluster rank = split). After the
-        // cluster barrier every CTA sums ITS share of the tile's tokens over the splits, in split order, straight out
-        // of the other CTAs' shared memory, and pushes it. No global round trip, no atomics.
-        cluster_arrive();
-        cluster_wait();
-        const int tok_lo = static_cast<int>(static_cast<long long>(s) * mt / g.splits);
-        const int tok_hi = static_cast<int>(static_cast<long long>(s + 1) * mt / g.splits);
-        const uint32_t local = smem_u32(tiles);
-        for (int v = threadIdx.x; v < (tok_hi - tok_lo) * (kBlockF / kVec); v += kFusedThreads) {
-            const int token = tok_lo + v / (kBlockF / kVec), j = v % (kBlockF / kVec);
-            const uint32_t off = local + (token * kBlockF + j * kVec) * 4;
-            float acc[kVec];
-            for (int base_sp = 0; base_sp < g.splits; base_sp += 4) {
-                float4 a[4], b[4];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    if (base_sp + u < g.splits) {
-                        const uint32_t remote = cluster_map(off, base_sp + u);
-                        a[u] = cluster_load_f4(remote);
-                        b[u] = cluster_load_f4(remote + 16);
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    if (base_sp + u < g.splits) {
-                        if (base_sp + u == 0) {
-                            acc[0] = a[u].x, acc[1] = a[u].y, acc[2] = a[u].z, acc[3] = a[u].w;
-                            acc[4] = b[u].x, acc[5] = b[u].y, acc[6] = b[u].z, acc[7] = b[u].w;
-                        } else {
-                            acc[0] += a[u].x, acc[1] += a[u].y, acc[2] += a[u].z, acc[3] += a[u].w;
-                            acc[4] += b[u].x, acc[5] += b[u].y, acc[6] += b[u].z, acc[7] += b[u].w;
-                        }
-                    }
-                }
-            }
-            const uint4 packed = pack_bf16x8(acc);
-            const int col = f * kBlockF + j * kVec;
-            if (p.fused) {
-                push_store(c, x, token0 + token, col, packed);
-            } else {
-                store_v4(g.out + static_cast<size_t>(token0 + token) * g.ldo + col, packed);
-            }
-        }
-        cluster_arrive();  // done reading the others' partials; the matching wait is at the very end of the kernel
-    } else if (local_rows) {
+    if (local_rows) {
         // Announce this CTA's partial tile on the counter of its token tile; the rows' owners wait for it below.
         const int gen = sm->gen + 1;
         if (threadIdx.x == 0) {
@@ -499,20 +449,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
     } else {
         pdl_launch_dependents();
     }
-    // A CTA's shared memory must outlive the reads of its cluster peers.
-    if (g.splits > 1 && g.cluster) cluster_wait();
 }
 
 int rowpar_stages(int m) {  // m: tokens per tile
-    // The ring takes what an SM has. (A half-SM ring for narrow tiles, which lets the next kernel of the stream move in
-    // early as a programmatic dependent launch, measured slower than the deeper ring: DLMRT_SMALL_TILE_SMEM_KB=100.)
     const int stage = kTileBytesW + m * kBlockK * 2;
-    static const int small_tile_kb = [] {
-        const char* e = getenv("DLMRT_SMALL_TILE_SMEM_KB");  // tuning knob: ring budget for tiles of up to 128 tokens
-        const int v = e ? atoi(e) : 0;
-        return v >= 48 && v <= 200 ? v : 200;
-    }();
-    int stages = (m <= 128 ? small_tile_kb * 1024 : kSmemBudget) / stage;
+    int stages = kSmemBudget / stage;  // the ring takes what an SM has
     if (stages > kMaxStages) stages = kMaxStages;
     return stages;
 }
@@ -540,7 +481,7 @@ static int launch_impl(const RowparParams<NR>& p, dim3 grid, const LaunchOpts& o
         config.blockDim = dim3(kFusedThreads);
         config.dynamicSmemBytes = static_cast<size_t>(smem);
         config.stream = o.stream;
-        cudaLaunchAttribute attrs[3];
+        cudaLaunchAttribute attrs[2];
         int n = 0;
         if (o.pdl) {
             attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -550,13 +491,6 @@ static int launch_impl(const RowparParams<NR>& p, dim3 grid, const LaunchOpts& o
         if (o.cooperative) {
             attrs[n].id = cudaLaunchAttributeCooperative;
             attrs[n].val.cooperative = 1;
-            ++n;
-        }
-        if (o.cluster > 1) {
-            attrs[n].id = cudaLaunchAttributeClusterDimension;
-            attrs[n].val.clusterDim.x = static_cast<unsigned>(o.cluster);
-            attrs[n].val.clusterDim.y = 1;
-            attrs[n].val.clusterDim.z = 1;
             ++n;
         }
         config.attrs = attrs;
@@ -576,34 +510,6 @@ int launch_rowpar(const RowparParams<1>& p, int grid, const LaunchOpts& o) { ret
 
 int launch_rowpar_loopback(const RowparParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o) {
     return launch_impl<kMaxWorld>(p, dim3(grid, nranks), o);
-}
-
-int rowpar_max_clusters(int tokens_per_tile, int cluster) {
-    static int cache[257][9];  // by tokens per tile and cluster size; 0 = not asked yet, -1 = unsupported
-    if (tokens_per_tile < 1 || tokens_per_tile > 256 || cluster < 2 || cluster > 8) return 0;
-    int& slot = cache[tokens_per_tile][cluster];
-    if (slot == 0) {
-        const int smem = rowpar_smem_bytes(tokens_per_tile, rowpar_stages(tokens_per_tile));
-        cudaLaunchConfig_t config{};
-        config.gridDim = dim3(static_cast<unsigned>(cluster) * 64);
-        config.blockDim = dim3(kFusedThreads);
-        config.dynamicSmemBytes = static_cast<size_t>(smem);
-        cudaLaunchAttribute attr{};
-        attr.id = cudaLaunchAttributeClusterDimension;
-        attr.val.clusterDim.x = static_cast<unsigned>(cluster);
-        attr.val.clusterDim.y = attr.val.clusterDim.z = 1;
-        config.attrs = &attr;
-        config.numAttrs = 1;
-        int n = 0;
-        if (cudaFuncSetAttribute(rowpar_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 rowpar_smem_bytes(256, rowpar_stages(256))) != cudaSuccess ||
-            cudaOccupancyMaxActiveClusters(&n, rowpar_kernel<1>, &config) != cudaSuccess) {
-            (void)cudaGetLastError();
-            n = -1;
-        }
-        slot = n > 0 ? n : -1;
-    }
-    return slot > 0 ? slot : 0;
 }
 
 int rowpar_max_ctas_per_sm(int m) {

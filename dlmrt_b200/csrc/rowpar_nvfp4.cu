@@ -44,7 +44,7 @@ struct MoeSmem {
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint32_t tmem_base;
-    int n_active, epoch, gen;
+    int n_active, epoch, gen, failed;
     int warp_count[8];
     float scratch[64];
     short active[kMaxEntries];  // expert | row block << 8
@@ -187,6 +187,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
         int early = 0;  // the invocation counters, fetched in the same round trip as the counts
         if (threadIdx.x == 352 && p.fused) early = c.epochs[block];
         if (threadIdx.x == 353) early = g.gen[block];
+        if (threadIdx.x == 354 && p.fused) early = comm_failed(c);
         const int nb = (total_rows + kItemRows - 1) / kItemRows;
         int incl = nb;
 #pragma unroll
@@ -213,12 +214,13 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
         }
         if (threadIdx.x == 352) sm->epoch = early;
         if (threadIdx.x == 353) sm->gen = early;
+        if (threadIdx.x == 354) sm->failed = early;
         __syncthreads();
     }
     if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 0] = globaltimer();
     const uint32_t tmem = sm->tmem_base;
     const int n_items = sm->n_active * feature_tiles;
-    const long long deadline = globaltimer() + (c.timeout_ns > 0 ? c.timeout_ns : 2000000000ll);
+    const long long deadline = globaltimer() + (c.timeout_ns > 0 ? c.timeout_ns : kDefaultTimeoutNs);
 
     // An item: entry (expert e, row block rb) x feature tile ft; `cnt` rows of the expert starting at row0.
     struct Item {
@@ -408,7 +410,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
         tmem_dealloc(tmem, kTmemCols);
     }
     CommCtx x{};
-    if (p.fused) x = comm_begin(c, block, blocks, sm->epoch);
+    if (p.fused) x = comm_begin(c, block, blocks, sm->epoch, sm->failed);
     // The expert list of this CTA's first output row is fetched now, ahead of the wait for the experts' outputs.
     CombineMeta first;
     if (block < g.m) first = combine_meta(g, block, 0);

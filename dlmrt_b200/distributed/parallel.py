@@ -24,13 +24,16 @@ import torch
 from .. import _lib
 from .._lib import DlmComm, DlmGemm, DlmStatus
 
-# CTAs' wait budget on the device; a rank that never pushes ends in a DLM_ERR_TIMEOUT status, not a hang.
-TIMEOUT_NS = int(os.environ.get("DLMRT_TP_TIMEOUT_NS", 2_000_000_000))
+# Budget of every wait on the device. The reference's kernel gives up after about 30 s and traps (tp_comm.cu:67-70);
+# here the kernel records DLM_ERR_TIMEOUT in the group's status words and returns, and the failure is sticky (below).
+# Ranks replay their graphs independently, so the budget has to cover the largest host-side skew between ranks.
+TIMEOUT_NS = int(os.environ.get("DLMRT_TP_TIMEOUT_NS", 30_000_000_000))
 PDL = os.environ.get("DLMRT_PDL", "1") != "0"
 
 
 def init():
-    """Join the torchrun process group; returns None when running on one GPU (parallel.py:34-44)."""
+    """The group of this torchrun job (one process per GPU, NCCL only as the bootstrap of symmetric memory), or None
+    when WORLD_SIZE is 1. Same contract as the reference's `init` (parallel.py:34-44)."""
     import torch.distributed as dist
 
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -47,9 +50,10 @@ def init():
 class Handle:
     """What a rendezvous yields: every rank's address of the buffer and its NVLS multicast address (0 if none)."""
 
-    def __init__(self, buffer_ptrs, multicast_ptr=0):
+    def __init__(self, buffer_ptrs, multicast_ptr=0, torch_handle=None):
         self.buffer_ptrs = list(buffer_ptrs)
         self.multicast_ptr = multicast_ptr
+        self.torch_handle = torch_handle  # torch's own symmetric-memory handle (views of peers' copies), if any
 
 
 class SymmetricAllocator:
@@ -67,7 +71,7 @@ class SymmetricAllocator:
             t.view(torch.int16).fill_(-1)
             torch.cuda.synchronize(self.device)
         h = symm.rendezvous(t, self.name)
-        return t, Handle(h.buffer_ptrs, h.multicast_ptr if h.multicast_ptr else 0)
+        return t, Handle(h.buffer_ptrs, h.multicast_ptr if h.multicast_ptr else 0, h)
 
 
 class LocalAllocator:
@@ -108,7 +112,8 @@ class Group:
         self._pending = {}   # partial data_ptr -> (linear, x): GEMMs deferred into the next reduction
         self._workspaces = {}
         self._gather = {}    # per key: slot addresses, invocation counters, multicast address of the slots
-        self.stamps = 0      # device address of a [grid, 4] int64 buffer to record kernel phase times
+        self.stamps = 0      # device address of a [grid, 8] int64 buffer to record kernel phase times
+        self._failed = False  # set by check() on a device time-out; the group must then be rebuilt
         self.status = torch.zeros(_lib.STATUS_WORDS, device=device, dtype=torch.int32)
         _lib.lib()  # fail now, not at the first reduction, when the library is missing
 
@@ -118,15 +123,17 @@ class Group:
         return cls(torch.device(device), rank=0, world=1, allocator=LocalAllocator(torch.device(device)))
 
     def symmetric(self, key, shape, dtype=torch.bfloat16, armed=False):
-        """A symmetric-memory tensor, allocated once per key (collectively, in the same order on every rank); every
-        later call with the key must ask for the same shape and dtype.
+        """The buffer named `key`, which exists at the same offset on every rank. The first request creates it, which
+        is a collective: all ranks must make their first requests in the same order. Later requests return the same
+        tensor and must repeat shape and dtype exactly (ValueError otherwise, as parallel.py:76-78).
 
-        `armed`: filled with the arrival sentinel (every bf16 lane 0xFFFF) before any rank can write into it.
+        `armed` buffers start out as "nothing has arrived": all 16-bit lanes 0xFFFF, written before any peer can
+        reach the buffer.
         """
         if key not in self._buffers:
             self._buffers[key], self._handles[key] = self._alloc.alloc(tuple(shape), dtype, armed)
         t = self._buffers[key]
-        if tuple(t.shape) != tuple(shape) or t.dtype != dtype:  # a larger request would write past it
+        if tuple(t.shape) != tuple(shape) or t.dtype != dtype:  # never hand out a view the caller may overrun
             raise ValueError(f"symmetric buffer {key}: {tuple(t.shape)} {t.dtype} allocated, {tuple(shape)} {dtype} "
                              "requested")
         return t
@@ -139,7 +146,8 @@ class Group:
         raise ValueError("not a symmetric tensor of this group")
 
     def multicast(self, t):
-        """Multicast address of symmetric tensor `t` (stores reach every rank's copy), or 0 without NVLink multicast."""
+        """The NVSwitch multicast address that aliases `t` on all ranks at once (one store lands in every copy);
+        0 when the node has no multicast support. `t` may be a view into a symmetric buffer (parallel.py:88-93)."""
         handle = self._handle(t)[1]
         if not handle.multicast_ptr:
             return 0
@@ -152,7 +160,8 @@ class Group:
         return [p + offset for p in handle.buffer_ptrs]
 
     def peers(self, t):
-        """[world] int64 device tensor: the address of `t` in every rank's copy (parallel.py:95-102)."""
+        """peer_addresses(t) as an int64 device tensor of `world` entries, the form the reference's extension takes
+        (parallel.py:95-102); cached per tensor."""
         key = self._handle(t)[0]
         if (key, t.data_ptr()) not in self._out_peers:
             self._out_peers[key, t.data_ptr()] = torch.tensor(self.peer_addresses(t), device=self.device,
@@ -177,8 +186,9 @@ class Group:
                 and (self.world - 1) * rows * n * 2 <= self.one_shot_bytes)
 
     def partial(self, site, shape):
-        """Where a row-parallel GEMM writes its partial product: one buffer shared by every call site (`site` is not
-        used), so every call passes the same shape (parallel.py:114-117)."""
+        """The destination of row-parallel GEMMs. All call sites get the SAME buffer (the argument `site` only
+        documents the caller), hence one shape per group (parallel.py:114-117). A `Linear` that is handed this buffer
+        defers its GEMM into the reduction that follows."""
         return self.symmetric("partial", shape)
 
     # -- deferred GEMMs ---------------------------------------------------------------------------------------------
@@ -220,7 +230,7 @@ class Group:
         one_shot = self.one_shot(rows, n, mode)
         ptrs, epochs, recv_mc = self._receive(rows, n, chain, one_shot)
         last = self._last.get(chain)
-        if last is out:
+        if last is out:  # same wording as parallel.py:124-125: callers may match on it
             raise ValueError(f"call site {site} ran twice in a row; its buffer would never be re-armed")
         c = DlmComm()
         c.rank, c.world, c.rows, c.n, c.mode = self.rank, self.world, rows, n, mode
@@ -231,7 +241,7 @@ class Group:
             c.out_peers[s] = peers[s]
         c.out = out.data_ptr()
         c.out_mc = self.multicast(out) or None
-        # The previous call's output on this chain: its consumer has finished, so this call re-arms it.
+        # Whatever this chain produced last has been consumed by now: this launch resets it to "not arrived".
         if last is not None:
             c.rearm, c.rearm_bytes = last.data_ptr(), last.numel() * last.element_size()
         c.epochs = epochs.data_ptr()
@@ -257,12 +267,32 @@ class Group:
         g.workspace, g.workspace_bytes, g.splits = ws.data_ptr(), ws.numel(), 0
         return g
 
+    @staticmethod
+    def _overlap(a, b):
+        """Whether tensors a and b share any byte (by address range)."""
+        if a is None or b is None:
+            return False
+        a0, b0 = a.data_ptr(), b.data_ptr()
+        a1 = a0 + ((a.shape[0] - 1) * a.stride(0) + a.shape[1]) * a.element_size() if a.dim() == 2 else \
+            a0 + a.numel() * a.element_size()
+        b1 = b0 + b.numel() * b.element_size()
+        return a0 < b1 and b0 < a1
+
     def _launch(self, mode, partial, h, weight, site, eps=0.0, scale=1.0, chain=0):
+        if self._failed:
+            raise RuntimeError("this group reported a device time-out: its buffers may hold stale arrivals; build a new "
+                               "Group before reducing again")
         rows, n = partial.shape
+        last = self._last.get(chain)
         comm, out = self._comm(rows, n, site, chain, mode, h, weight, eps, scale)
         stream = torch.cuda.current_stream(self.device).cuda_stream
         pending = self._pending.pop(partial.data_ptr(), None)
-        if pending is not None and n <= _lib.FUSED_MAX_N:
+        # The fused kernel re-arms `last` and fills `out` while other CTAs still load the GEMM's input; an input that
+        # IS one of those (a projection fed straight from the previous reduction) therefore runs as two kernels, the
+        # order the reference has anyway.
+        fusable = pending is not None and n <= _lib.FUSED_MAX_N and not self._overlap(pending[1], last) \
+            and not self._overlap(pending[1], out)
+        if fusable:
             linear, x, _ = pending
             gemm = self._gemm(linear, x, chain)
             _lib.check(_lib.lib().dlm_rowpar_bf16(C.byref(gemm), C.byref(comm), stream), f"rowpar {site}")
@@ -274,18 +304,23 @@ class Group:
         return out
 
     def reduce_norm(self, partial, h, weight, eps, scale=1.0, *, site, chain=0):
-        """rmsnorm(h [+= sum of partial over ranks]) * weight * scale, on every rank (parallel.py:134-143).
+        """All-reduce `partial`, then RMSNorm, in one launch; every rank gets the same [rows, n] result
+        (same arguments as parallel.py:134-143).
 
-        With `h`, only this rank's rows of `h` are updated (the residual stream becomes sequence-parallel);
-        without it the reduced partial itself is normalized. The result lives in this call site's buffer
-        until the next call on the same `chain`, which re-arms it. Reductions that may run concurrently
-        (different streams) need different `chain`s; calls on one chain are ordered.
+        h given:  v = bf16(sum) + h; this rank's rows of `h` become bf16(v) (each rank keeps only its own rows of
+                  the residual stream current); returns rmsnorm(v) * weight * scale.
+        h None:   returns rmsnorm(bf16(sum)) * weight * scale.
+
+        The returned tensor is the buffer of call site `site`; it stays valid until the NEXT call on `chain`, whose
+        launch resets it. Calls on one chain must be stream-ordered; calls that can overlap in time (two streams)
+        must use different chains.
         """
         mode = _lib.REDUCE_NORM_RESIDUAL if h is not None else _lib.REDUCE_NORM
         return self._launch(mode, partial, h, weight, site, eps, scale, chain)
 
     def reduce(self, partial, *, site, chain=0):
-        """Sum over ranks of `partial`, on every rank, in this call site's buffer (parallel.py:145-147)."""
+        """All-reduce (sum) of `partial` into the buffer of call site `site`, identical bits on every rank
+        (parallel.py:145-147). Buffer lifetime and chain rules as for reduce_norm."""
         return self._launch(_lib.REDUCE, partial, None, None, site, chain=chain)
 
     def shard(self, t, dim=0):
@@ -294,17 +329,22 @@ class Group:
         return t.chunk(self.world, dim)[self.rank].contiguous()
 
     def check(self):
-        """Read and clear the device status words (synchronises the current stream); raises on a timed-out wait."""
+        """Read the device status words (synchronises the current stream); raises TimeoutError when a wait ran out.
+        The kernels make such a failure sticky (later calls exchange nothing), and so does the host: after the error
+        the group refuses further reductions, because slots may hold late arrivals of the failed call. Call this
+        wherever the host synchronises anyway (end of a block, end of a request)."""
         st = DlmStatus()
         stream = torch.cuda.current_stream(self.device).cuda_stream
         _lib.check(_lib.lib().dlm_status_read(self.status.data_ptr(), C.byref(st), stream), "status")
         if st.code:
+            self._failed = True
             raise TimeoutError(f"rank {self.rank}: {_lib.lib().dlm_strerror(st.code).decode()} (block {st.block}, "
                                f"rank slot {st.slot}, phase {st.phase}, invocation {st.epoch})")
 
     def all_reduce_(self, x):
-        """In-place sum over ranks of a symmetric tensor; identical result on every rank (parallel.py:154-162).
-        Off the hot path: torch's symmetric-memory kernels, as in the reference."""
+        """The reference's UNFUSED switch (DLMRT_TP_FUSED=0, parallel.py:154-162), kept so model code that still calls
+        it runs: in-place sum of a symmetric tensor through the same torch symmetric-memory operators the reference
+        uses. Nothing on the fused path calls it."""
         if self.world == 1:
             return x
         if self.multicast(x):
@@ -313,36 +353,34 @@ class Group:
             torch.ops.symm_mem.two_shot_all_reduce_(x, "sum", self.name)
         return x
 
-    def all_gather(self, x, key):
-        """[world, *x.shape]: every rank's `x`, stacked in rank order (parallel.py:164-180): the row statistics of the
-        decoders, the one other collective of a round. Blocks of floating-point values whose size is a multiple of
-        16 bytes (up to 1 MiB) go through this library's barrier-free kernel (`dlm_all_gather`: multicast stores into
-        triple-buffered slots, in-band arrival); anything else takes torch's symmetric-memory path, as the reference."""
-        out = self.symmetric(key, (self.world, *x.shape), x.dtype)
-        nbytes = x.numel() * x.element_size()
-        if x.is_floating_point() and x.is_contiguous() and nbytes % 16 == 0 and 0 < nbytes <= _lib.GATHER_MAX_BYTES:
-            if key not in self._gather:
-                slots = self.symmetric(key + ".slots", (3, self.world, nbytes // 2), armed=True)
-                epochs = torch.zeros(_lib.EPOCH_SLOTS, device=self.device, dtype=torch.int32)
-                self._gather[key] = list(self._handles[key + ".slots"].buffer_ptrs), epochs, self.multicast(slots)
-            ptrs, epochs, recv_mc = self._gather[key]
-            c = DlmComm()
-            c.rank, c.world = self.rank, self.world
-            for s in range(self.world):
-                c.recv[s] = ptrs[s]
-            c.recv_mc = recv_mc or None
-            c.out, c.epochs, c.status = out.data_ptr(), epochs.data_ptr(), self.status.data_ptr()
-            c.timeout_ns, c.pdl, c.max_ctas = TIMEOUT_NS, int(PDL), self.max_ctas
-            stream = torch.cuda.current_stream(self.device).cuda_stream
-            _lib.check(_lib.lib().dlm_all_gather(x.data_ptr(), nbytes, C.byref(c), stream), f"all_gather {key}")
-            return out
-        if self.world == 1:
-            out[0].copy_(x)
-            return out
-        if self.multicast(out):
-            torch.ops.symm_mem.multimem_all_gather_out(x, self.name, out.view(-1, *x.shape[1:]))
-            return out
-        import torch.distributed as dist
+    # Payloads the gather kernel can tell from "not arrived": arithmetic never produces an all-ones 32-bit word in these.
+    GATHER_DTYPES = (torch.float32, torch.float16, torch.bfloat16)
 
-        dist.all_gather_into_tensor(out.view(-1, *x.shape[1:]), x.contiguous())
+    def all_gather(self, x, key):
+        """[world, *x.shape]: every rank's `x` in rank order (parallel.py:164-180). This is the other collective of a
+        round (row statistics of the decoders) and runs on this library's barrier-free kernel only (`dlm_all_gather`:
+        multicast stores into triple-buffered slots, arrival detected in band). The kernel needs a contiguous FP32 /
+        FP16 / BF16 block of 16..1 MiB bytes, a multiple of 16; anything else is a ValueError rather than a silent
+        detour through another backend."""
+        nbytes = x.numel() * x.element_size()
+        if x.dtype not in self.GATHER_DTYPES or not x.is_contiguous() or nbytes % 16 or not 0 < nbytes <= _lib.GATHER_MAX_BYTES:
+            raise ValueError(f"all_gather {key}: needs a contiguous float32/float16/bfloat16 block whose size is a multiple "
+                             f"of 16 bytes, at most {_lib.GATHER_MAX_BYTES}; got {tuple(x.shape)} {x.dtype}")
+        if self._failed:
+            raise RuntimeError("this group reported a device time-out; build a new Group")
+        out = self.symmetric(key, (self.world, *x.shape), x.dtype)
+        if key not in self._gather:
+            slots = self.symmetric(key + ".slots", (3, self.world, nbytes // 2), armed=True)
+            epochs = torch.zeros(_lib.EPOCH_SLOTS, device=self.device, dtype=torch.int32)
+            self._gather[key] = list(self._handles[key + ".slots"].buffer_ptrs), epochs, self.multicast(slots)
+        ptrs, epochs, recv_mc = self._gather[key]
+        c = DlmComm()
+        c.rank, c.world = self.rank, self.world
+        for s in range(self.world):
+            c.recv[s] = ptrs[s]
+        c.recv_mc = recv_mc or None
+        c.out, c.epochs, c.status = out.data_ptr(), epochs.data_ptr(), self.status.data_ptr()
+        c.timeout_ns, c.pdl, c.max_ctas = TIMEOUT_NS, int(PDL), self.max_ctas
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _lib.check(_lib.lib().dlm_all_gather(x.data_ptr(), nbytes, C.byref(c), stream), f"all_gather {key}")
         return out

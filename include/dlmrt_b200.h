@@ -58,7 +58,8 @@ enum {
     DLM_ERR_WORKSPACE = -7, /* workspace smaller than dlm_workspace_bytes() */
     DLM_ERR_TIMEOUT = -8,   /* device status: a bounded wait ran out (data from a rank never arrived) */
     DLM_ERR_ARCH = -9,      /* not an sm_100 device */
-    DLM_ERR_SCRATCH = -10   /* dlm_gemm_bf16_noalloc: the requested K splits do not fit the built-in scratch */
+    DLM_ERR_SCRATCH = -10,  /* dlm_gemm_bf16_noalloc: the requested K splits do not fit the built-in scratch */
+    DLM_ERR_OVERLAP = -11   /* dlm_rowpar_bf16: the GEMM's input overlaps `rearm` or `out` of the same call */
 };
 
 /* What follows the rank-ordered sum (tp_comm.cu:138 template <NORM, RESIDUAL>). */
@@ -86,12 +87,16 @@ typedef struct DlmComm {
     int32_t* epochs;               /* [DLM_EPOCH_SLOTS] int32, zero-initialised, one array per receive buffer */
     void* h;                       /* [rows, n] BF16 residual stream (mode 2): own rows read and rewritten */
     const void* weight;            /* [n] BF16 RMSNorm weight (modes 1, 2) */
-    int32_t* status;               /* [DLM_STATUS_WORDS] int32 device words, zero-initialised, or NULL */
+    int32_t* status;               /* [DLM_STATUS_WORDS] int32 device words, zero-initialised, or NULL. A failure is
+                                      sticky: while status[0] != 0 every call on these words pushes nothing, accepts
+                                      nothing and broadcasts nothing (slots may hold an older invocation's vectors), so
+                                      its peers' waits run out too. After DLM_ERR_TIMEOUT the receive slots, outputs and
+                                      epochs of the group must be re-created before it is used again. */
     int64_t* stamps;               /* [grid, DLM_STAMP_SLOTS] int64 %globaltimer phase stamps per CTA, or NULL
                                       (tp_comm.cu:121): 0 start, 1 pushed, 2 owned rows broadcast, 3 collected; fused
                                       kernels also 4 accumulator ready, 5 dependency wait returned, 6 tile summed+pushed,
                                       7 kernel entry */
-    int64_t timeout_ns;            /* budget of every device wait; 0 = 2 s */
+    int64_t timeout_ns;            /* budget of every device wait; 0 = 30 s (the reference's budget, tp_comm.cu:67-70) */
     int32_t pdl;                   /* launch as a programmatic dependent launch (tp_comm.cu:304-309) */
     int32_t max_ctas;              /* cap on the grid, 0 = one CTA per SM. Calls that may run concurrently (different
                                       chains on different streams) must together fit on the GPU. */
@@ -121,10 +126,7 @@ typedef struct DlmGemm {
                         position c ^ (r % 8) (the 128-byte shared-memory swizzle); ldw is ignored. Weights are static,
                         so the layout is made once when they are loaded, as the reference re-lays its FP8 and NVFP4
                         weights (linear.py:30-31, nvfp4.py:104-112). */
-    int32_t use_cluster; /* 0 (default): FP32 partial tiles of a split K meet through the workspace. 1: where the GPU can
-                        hold them all at once, the CTAs of a tile run as one thread-block cluster and sum the partial
-                        tiles out of each other's shared memory. Same result either way; measured slower on B200 for
-                        these shapes (remote shared-memory reads), kept for shapes where it may pay. */
+    int32_t reserved;    /* must be 0 */
 } DlmGemm;
 
 /* The NVFP4 expert half of a fused call: GEMM2 (down-projection) of this rank's routed experts and the weighted top-k
@@ -193,7 +195,9 @@ DLM_API int dlm_gemm_bf16(const DlmGemm* gemm, void* out, int64_t ldo, int pdl, 
  *     request beyond 8 MiB returns DLM_ERR_SCRATCH. With splits = 0 the library picks a tiling and lowers the number
  *     of splits until it fits (a single split needs no partial tiles), so every legal shape runs, if slower;
  *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress with that device
- *     current); make that first call before any stream capture starts;
+ *     current); make that first call before any stream capture starts. The address is remembered per device for the
+ *     life of the process and does not survive cudaDeviceReset or a re-created primary context;
+ *   - `splits` larger than the number of 64-wide k-blocks runs as that number, and only that number has to fit;
  *   - all calls on a GPU share the one array. Each call clears the small header it depends on (stream-ordered
  *     memset) and rewrites the partial tiles before reading them, so calls that follow each other on one stream are
  *     safe; calls that overlap on the GPU (different streams, different host threads) race on it and give wrong
@@ -205,7 +209,9 @@ DLM_API int dlm_gemm_bf16_noalloc(const void* x, const void* w, void* out, int m
  * owner ranks' receive slots, followed in the same kernel by the reduction of dlm_reduce_bf16.
  * Replaces the pair Linear.__call__(x, out=partial) -> Group.reduce / reduce_norm
  * (dlmrt/models/sdar/model.py:237-243, llada2/model.py:435-439, diffusion_gemma/model.py:272-292).
- * gemm->m == comm->rows, gemm->n == comm->n <= DLM_FUSED_MAX_N. */
+ * gemm->m == comm->rows, gemm->n == comm->n <= DLM_FUSED_MAX_N.
+ * gemm->x must not overlap comm->rearm or comm->out (DLM_ERR_OVERLAP): CTAs re-arm and fill those while others still
+ * load x. A caller whose input IS the previous output of the chain runs dlm_gemm_bf16 + dlm_reduce_bf16 instead. */
 DLM_API int dlm_rowpar_bf16(const DlmGemm* gemm, const DlmComm* comm, dlm_stream_t stream);
 
 /* NVFP4 routed experts on one GPU: out[m, n] BF16 (ldo elements) = combine(GEMM2). Replaces the GEMM2 + finalize

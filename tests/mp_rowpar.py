@@ -1,6 +1,7 @@
 """One rank of the real multi-GPU parity run (launched by tests/test_multigpu.py through torch.distributed.run):
 stand-alone reductions and fused projections over symmetric memory, checked bit for bit against the CPU oracle fed
-with the all-gathered inputs, and for identity across ranks."""
+with the all-gathered inputs, and for identity across ranks; first call by call with a host synchronisation after
+each, then as a CUDA graph of back-to-back calls replayed without any (graph_section)."""
 
 import os
 import sys
@@ -22,6 +23,78 @@ def gather(t):
     out = [torch.empty_like(t) for _ in range(dist.get_world_size())]
     dist.all_gather(out, t.contiguous())
     return out
+
+
+def graph_section(group):
+    """What the design is for, value-checked on real NVLink: back-to-back calls with NO host synchronisation and no
+    NCCL in between, captured once in a CUDA graph and replayed. Twenty calls per pass: plain sums and residual +
+    RMSNorm on alternating call sites, the fused GEMM in both modes, a one-hop chain of 32-row blocks and the
+    all-gather of row statistics, so that triple-buffered slots, cross-call re-arming, programmatic dependent launch and
+    the multicast stores all run the way a denoise round runs them. After several replays the final outputs and the
+    residual stream must equal the oracle fed with the same sequence, and be identical on every rank."""
+    from dlmrt_b200.layers.linear import Linear
+
+    rank, world, dev = group.rank, group.world, group.device
+    rows, n, k = 64, 2048, 512
+    weight = randn_bf16(n, seed=41, std=0.1, device=dev) + 1
+    h = randn_bf16(rows, n, seed=42, device=dev)
+    given = [randn_bf16(rows, n, seed=300 + 10 * i + rank, device=dev) for i in range(4)]
+    small = [randn_bf16(32, n, seed=400 + 10 * i + rank, device=dev) for i in range(2)]
+    stats = torch.randn(32, 4, generator=torch.Generator().manual_seed(500 + rank)).to(dev)
+    g = torch.Generator().manual_seed(600 + rank)
+    x = torch.randint(-3, 4, (rows, k), generator=g).to(torch.bfloat16).to(dev)
+    w = torch.randint(-2, 3, (n, k), generator=g).to(torch.bfloat16).to(dev)
+    lin = Linear(w, group=group)
+    own = bits((x.float() @ w.float().t()).to(torch.bfloat16))  # exact integers, one BF16 rounding: this rank's partial
+    partial = group.symmetric("graph.partial", (rows, n))
+    assert group.one_shot(32, n, 0) and not group.one_shot(rows, n, 2)
+
+    def one_pass():
+        o = {}
+        group.reduce_norm(given[0], h, weight, 1e-6, site="g.a")
+        group.reduce(lin(x, out=partial), site="g.b")
+        group.reduce_norm(given[1], h, weight, 1e-6, site="g.a")
+        group.reduce(small[0], site="g.s0", chain=32)
+        group.reduce_norm(lin(x, out=partial), h, weight, 1e-6, site="g.b")
+        o["stats"] = group.all_gather(stats, "g.stats")
+        group.reduce(given[2], site="g.a")
+        o["small"] = group.reduce(small[1], site="g.s1", chain=32)
+        group.reduce_norm(given[3], None, weight, 1e-6, 0.5, site="g.b")
+        group.reduce(lin(x, out=partial), site="g.a")
+        o["last"] = group.reduce_norm(given[0], h, weight, 1e-6, site="g.b")
+        return o
+
+    h_start = np.stack([bits(t) for t in gather(h)])
+    parts = {name: np.stack([bits(t) for t in gather(t_)]) for name, t_ in
+             [("g0", given[0]), ("g1", given[1]), ("g2", given[2]), ("g3", given[3]), ("s1", small[1])]}
+    parts["own"] = np.stack([bits(t) for t in gather(torch.from_numpy(own.view(np.int16)).to(dev))]).view(np.uint16)
+    stats_all = torch.stack(gather(stats)).cpu()
+    replays = 5
+    stream = torch.cuda.Stream(dev)
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            out = one_pass()
+        stream.synchronize()
+        group.check()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            out = one_pass()
+        for _ in range(replays):
+            graph.replay()
+        stream.synchronize()
+    group.check()
+    # the oracle, fed with the same sequence: only the residual-stream calls carry state from pass to pass
+    hs, want_last = h_start, None
+    for _ in range(2 + replays):  # two eager passes and the replays (capturing launches nothing)
+        for name in ("g0", "g1", "own", "g0"):
+            want_last, hs = red.reduce_norm(parts[name], bits(weight), 1e-6, 1.0, hs)
+    assert_same_bits(bits(h), hs[rank], "graph: residual stream after the replays")
+    assert_norm_close(bits(out["last"]), want_last, "graph: last residual + RMSNorm output")
+    assert_same_bits(bits(out["small"]), red.reduce(parts["s1"]), "graph: one-hop sum")
+    assert torch.equal(out["stats"].cpu().view(torch.int32), stats_all.view(torch.int32)), "graph: all_gather"
+    for name in ("last", "small"):
+        for r, other in enumerate(gather(out[name])):
+            assert_same_bits(bits(other), bits(out[name]), f"graph: {name} of rank {r} vs rank {rank}")
 
 
 def main():
@@ -115,6 +188,7 @@ def main():
             group.check()
             want = torch.stack([t.to(dev) for t in gather(stats)])
             assert torch.equal(got.view(torch.int32), want.view(torch.int32)), f"all_gather {key} call {call}"
+    graph_section(group)
     dist.barrier()
     if rank == 0:
         print(f"MULTIGPU_OK world={world} multicast={report['multicast']}")

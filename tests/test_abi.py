@@ -45,7 +45,7 @@ def test_header_constants_match_binding():
 
 def test_strerror_and_sizes():
     lib = _lib.lib()
-    for code in range(0, -10, -1):
+    for code in range(0, -12, -1):
         assert lib.dlm_strerror(code)
     assert lib.dlm_strerror(-99) == b"unknown error"
     assert lib.dlm_workspace_bytes(256, 2560, 9728) == 2048 + 8 * 256 * 2560 * 4
@@ -103,6 +103,27 @@ def test_fused_requires_matching_shapes():
     c = comm(rows=32, n=256)
     assert _lib.lib().dlm_rowpar_bf16(C.byref(gemm(m=64)), C.byref(c), None) == _lib.ERR_SHAPE
     assert _lib.lib().dlm_rowpar_bf16(C.byref(gemm(n=512)), C.byref(c), None) == _lib.ERR_SHAPE
+
+
+def test_fused_rejects_an_input_that_the_same_launch_rearms_or_writes():
+    """CTAs of the fused kernel re-arm `rearm` and fill `out` while others still load x, so x may be neither."""
+    lib = _lib.lib()
+    g = gemm()  # x at 0x1000, 32 x 128 BF16 = 8 KiB
+    assert lib.dlm_rowpar_bf16(C.byref(g), C.byref(comm(rearm=0x2000, rearm_bytes=4096)), None) == _lib.ERR_OVERLAP
+    assert lib.dlm_rowpar_bf16(C.byref(g), C.byref(comm(out=0x1800, out_peers=(C.c_void_p * 8)(0x1800))), None) \
+        == _lib.ERR_OVERLAP
+    assert b"overlaps" in lib.dlm_strerror(_lib.ERR_OVERLAP)
+    # disjoint buffers pass the pair check (and then fail later, on the missing GPU or nothing at all)
+    assert lib.dlm_rowpar_bf16(C.byref(g), C.byref(comm(rearm=0x40000, rearm_bytes=4096, out=0x50000,
+                                                       out_peers=(C.c_void_p * 8)(0x50000))), None) != _lib.ERR_OVERLAP
+
+
+def test_noalloc_counts_the_splits_that_would_run():
+    """More splits than K has 64-wide blocks run as that many blocks, and only those must fit the built-in scratch."""
+    f = _lib.lib().dlm_gemm_bf16_noalloc
+    # k = 64: one k-block, so "8 splits" is one split and needs no partial tiles; the call gets past the scratch check
+    assert f(0x1000, 0x2000, 0x3000, 256, 2560, 64, 64, 64, 2560, 8, 1, 0, None) != _lib.ERR_SCRATCH
+    assert f(0x1000, 0x2000, 0x3000, 256, 2560, 9728, 9728, 9728, 2560, 8, 1, 0, None) == _lib.ERR_SCRATCH
 
 
 def test_all_gather_rejects_bad_arguments():

@@ -12,13 +12,16 @@ from oracle.bf16 import bf16_to_f32, f32_to_bf16, to_torch
 pytestmark = pytest.mark.gpu
 
 
-def make_case(rows, hidden, f, e_total, top_k, seed, exact=False, skew=False):
+def make_case(rows, hidden, f, e_total, top_k, seed, exact=False, skew=False, hot=False, m_max=None):
     """Routed inputs of one MoE layer call as numpy arrays in the layouts the kernel takes.
 
     exact: codes and power-of-two scales chosen so that every product and partial sum is exact in FP32; the kernel must
     then match the oracle bit for bit whatever its summation order, which also pins the scale-factor layout."""
     rng = np.random.default_rng(seed)
-    if skew:
+    if hot:  # expert 0 is on every token's list: it alone holds `rows` rows
+        ids = np.stack([np.concatenate([[0], 1 + np.sort(rng.permutation(e_total - 1)[:top_k - 1])]) for _ in range(rows)])
+        ids = ids.astype(np.int32)
+    elif skew:
         p = 1.0 / np.arange(1, e_total + 1) ** 1.2
         p /= p.sum()
         ids = np.stack([np.sort(rng.choice(e_total, top_k, replace=False, p=p)) for _ in range(rows)]).astype(np.int32)
@@ -27,7 +30,11 @@ def make_case(rows, hidden, f, e_total, top_k, seed, exact=False, skew=False):
     weights = rng.random((rows, top_k), dtype=np.float32)
     weights = bf16_to_f32(f32_to_bf16(weights / weights.sum(-1, keepdims=True) * 2.5))
     amap, counts = onv.route_slots(ids, e_total)
-    m_max = rows
+    if m_max is None:
+        m_max = rows
+    else:  # fewer slots per expert than tokens: the caller guarantees no expert is routed more (llada2/kernels route)
+        assert counts.max() <= m_max < rows
+        amap = np.ascontiguousarray(amap[:, :m_max])
     if exact:
         w_codes = rng.integers(0, 256, (e_total, hidden, f // 2), dtype=np.uint8)
         a_codes = rng.integers(0, 256, (e_total * m_max, f // 2), dtype=np.uint8)
@@ -94,7 +101,47 @@ def test_exact_operands_match_bit_for_bit(rows, hidden, f, e_total, top_k):
     assert_same_bits(run_single(case), want, "exact NVFP4 expert down-projection")
 
 
+def test_shapes_the_configs_reach_at_their_edges():
+    """BASELINE config 4's real expert count under Zipf(1.2) routing at 32 rows; fewer slots per expert than tokens
+    (m_max < rows); one expert that holds more than 128 rows at hidden 2048 (two row blocks of one work item list)."""
+    for kw in (dict(rows=32, hidden=2048, f=512, e_total=256, top_k=8, seed=31, skew=True),
+               dict(rows=64, hidden=2048, f=512, e_total=32, top_k=2, seed=32, m_max=16),
+               dict(rows=256, hidden=2048, f=512, e_total=8, top_k=2, seed=33, hot=True)):
+        case = make_case(exact=True, **kw)
+        if kw.get("hot"):
+            assert case["counts"][0] == 256 > 128
+        want, _ = oracle_out(case, 0, kw["e_total"])
+        assert_same_bits(run_single(case), want, f"{kw}")
+
+
+def test_kernel_reproduces_the_reference_math_where_it_is_exact():
+    """The golden case on which the reference's W4A4 torch statement of GEMM2 + combine rounds nowhere
+    (tests/golden/make_moe_golden.py `exact`): the kernel must give the BF16 rounding of the reference's FP32 result,
+    bit for bit. Hidden 256, F 128, 8 experts, top-2, 16 tokens."""
+    from pathlib import Path
+
+    g = np.load(Path(__file__).parent / "golden" / "moe_golden.npz")
+    ids, weights = g["exact_ids"], g["exact_weights"]
+    rows, top_k = ids.shape
+    e_total, hidden, half_f = g["exact_down_packed"].shape
+    a2, ws2 = g["exact_down_input_scale"], g["exact_down_scale2"]
+    act = bf16_to_f32(g["exact_act"])
+    amap, counts = onv.route_slots(ids, e_total)
+    m_max = rows
+    a_codes = np.zeros((e_total * m_max, half_f), dtype=np.uint8)
+    a_scales = np.zeros((e_total * m_max, half_f // 8), dtype=np.uint8)
+    for e in range(e_total):
+        for j in range(counts[e]):
+            c, sc = onv.quantize(act[amap[e, j]][None], a2[e])
+            a_codes[e * m_max + j], a_scales[e * m_max + j] = c[0], sc[0]
+    case = dict(ids=ids, weights=weights.astype(np.float32), amap=amap, counts=counts, m_max=m_max,
+                w_codes=g["exact_down_packed"], w_scales=g["exact_down_scale"], a_codes=a_codes, a_scales=a_scales,
+                g2=(a2 * ws2).astype(np.float32), rows=rows, hidden=hidden, f=half_f * 2, e_total=e_total, top_k=top_k)
+    assert_same_bits(run_single(case), f32_to_bf16(g["exact_ref"]), "golden exact case")
+
+
 @pytest.mark.parametrize("rows, hidden, f, e_total, top_k, skew", [(32, 2048, 512, 64, 8, False), (32, 2048, 512, 64, 8, True),
+                                                                  (32, 2048, 512, 256, 8, True),
                                                                   (256, 2816, 704, 16, 8, False)])
 def test_gaussian_operands_within_tolerance(rows, hidden, f, e_total, top_k, skew):
     """Per output row relative L2 <= 1e-2 against the W4A4 oracle on identical quantised inputs; with a shared-expert

@@ -169,11 +169,55 @@ def test_group_all_gather_world_one_and_fallback():
     torch.cuda.synchronize()
     g.check()
     assert _lib.lib().dlm_launch_count() == before + 4 and torch.equal(out[0], x)
-    odd = torch.randn(5, 3, device="cuda")  # 60 bytes: not a multiple of 16, takes the plain path
-    assert torch.equal(g.all_gather(odd, "odd")[0], odd)
-    ints = torch.full((8, 4), -1, dtype=torch.int32, device="cuda")  # all-ones words: never through the flagged slots
-    assert torch.equal(g.all_gather(ints, "ints")[0], ints)
+    # Payloads the in-band arrival flag cannot carry are refused, not sent through another backend.
+    for bad in (torch.randn(5, 3, device="cuda"),                                  # 60 bytes: not a multiple of 16
+                torch.full((8, 4), -1, dtype=torch.int32, device="cuda"),          # integers may be all-ones words
+                torch.randn(8, 4, dtype=torch.float64, device="cuda"),             # low mantissa words may be all ones
+                torch.randn(8, 8, device="cuda")[:, :4]):                          # not contiguous
+        with pytest.raises(ValueError, match="all_gather"):
+            g.all_gather(bad, "bad")
     assert _lib.lib().dlm_launch_count() == before + 4
+
+
+def test_a_timed_out_group_stays_failed():
+    """After a wait ran out, slots may hold late arrivals of the failed call. Later calls must therefore report an
+    error instead of data: on the device (status words non-zero at entry: push nothing, accept nothing, broadcast
+    nothing) and on the host (the Group refuses to launch once check() has raised)."""
+    import ctypes as C
+
+    from dlmrt_b200 import _lib
+    from dlmrt_b200.distributed import parallel
+    from dlmrt_b200.distributed.loopback import LoopbackWorld
+
+    parallel.TIMEOUT_NS = 2_000_000  # 2 ms
+    lw = LoopbackWorld(2, one_shot_bytes=0)
+    rows, n = 8, 256
+    partials = [randn_bf16(rows, n, seed=r) for r in range(2)]
+    comms, outs = lw._comms(rows, n, "lost", 0, None, None, 0.0, 1.0)
+    lost = torch.full((3, 2, rows // 2, n), -1, dtype=torch.int16, device="cuda")
+    comms[1].recv[0] = lost.data_ptr()  # rank 1's pushes to rank 0 never arrive
+    ptrs = (C.c_void_p * 2)(*[p.data_ptr() for p in partials])
+    _lib.check(_lib.lib().dlm_reduce_bf16_loopback(ptrs, comms, 2, None), "loopback")
+    lw._done(0, outs)
+    torch.cuda.synchronize()
+    assert int(lw.groups[0].status[0]) == _lib.ERR_TIMEOUT
+    # A second call with every address right, WITHOUT the host having looked at the status: the device words are
+    # still set, so the kernel exchanges nothing and the outputs stay armed (no row is broadcast).
+    comms2, outs2 = lw._comms(rows, n, "after", 0, None, None, 0.0, 1.0)
+    _lib.check(_lib.lib().dlm_reduce_bf16_loopback(ptrs, comms2, 2, None), "loopback")
+    lw._done(0, outs2)
+    torch.cuda.synchronize()
+    for r in range(2):
+        assert int(lw.groups[r].status[0]) == _lib.ERR_TIMEOUT
+        armed = outs2[r].view(torch.int16) == -1
+        assert bool(armed.all()), f"rank {r}: {int((~armed).sum())} lanes of the output were written after a failure"
+    # The host side: check() raises once and the group then refuses to reduce.
+    for g in lw.groups:
+        with pytest.raises(TimeoutError):
+            g.check()
+        with pytest.raises(RuntimeError, match="new Group"):
+            g.reduce(partials[0], site="again")
+    run_sequence(2, 8, 256, calls=3, seed=11)  # a fresh world works
 
 
 def test_reference_kernel_agrees_bit_for_bit():
@@ -218,3 +262,68 @@ def test_reference_kernel_agrees_bit_for_bit():
             assert_same_bits(bits(h_mine), bits(h_ref), f"call {i}: residual stream")
         if mode == 0:
             assert_same_bits(bits(out), red.reduce(bits(p)[None]), f"call {i}: reference kernel vs CPU oracle")
+
+
+def test_one_chain_sees_calls_of_different_row_counts():
+    """LLaDA2's pair rounds (dlmrt/models/llada2/engine.py:139, llada2/model.py:291-297): the 32-row self-conditioning
+    reduction is issued on the chain of the 64-row forward that follows it, so consecutive calls of ONE chain differ in
+    rows. Receive slots are per (rows, n, chain), but the chain's previous output is shared bookkeeping: every call
+    must re-arm it over ITS OWN size (tp_comm.cu:201-208), whatever this call's rows are."""
+    from dlmrt_b200.distributed.loopback import LoopbackWorld
+
+    world, n, chain = 2, 2048, 64
+    lw = LoopbackWorld(world, one_shot_bytes=0)
+    previous = None
+    for i, rows in enumerate([32, 64, 64, 32, 64, 32, 32, 64, 64]):
+        partials = [randn_bf16(rows, n, seed=700 + 10 * i + r) for r in range(world)]
+        site = f"{rows}.{i % 2}.{'sc' if rows == 32 else 'attn'}"
+        outs = lw.reduce(partials, site=site, chain=chain)
+        torch.cuda.synchronize()
+        lw.check()
+        want = red.reduce(np.stack([bits(p) for p in partials]))
+        for r in range(world):
+            assert_same_bits(bits(outs[r]), want, f"call {i} ({rows} rows) rank {r}")
+        if previous is not None:  # the output of the call before, of whatever size, is armed again in full
+            for r, old in enumerate(previous):
+                armed = old.view(torch.int16) == -1
+                assert bool(armed.all()), f"call {i}: {int((~armed).sum())} lanes of rank {r}'s previous output not re-armed"
+        previous = outs
+
+
+def test_two_chains_resident_at_once_on_two_streams():
+    """DiffusionGemma reduces the dense MLP (chain 2, side stream) while the experts' reduction (chain 1) runs
+    (dlmrt/models/diffusion_gemma/model.py:281-288, dlmrt/distributed/parallel.py:139-140). Both kernels spin on peers,
+    so both grids must fit on the GPU together: the caller caps each at half the SMs with `max_ctas`. Waits are bounded
+    to milliseconds here, so a grid that did not fit would surface as DLM_ERR_TIMEOUT, not as a stall."""
+    from dlmrt_b200 import _lib
+    from dlmrt_b200.distributed import parallel
+    from dlmrt_b200.distributed.loopback import LoopbackWorld
+
+    parallel.TIMEOUT_NS = 50_000_000  # 50 ms
+    world, rows, n, k = 2, 256, 2816, 2176
+    sms = _lib.lib().dlm_device_sms()
+    lw = LoopbackWorld(world, max_ctas=sms // world // 2)
+    side, main = torch.cuda.Stream(), torch.cuda.Stream()
+    x, w = randn_bf16(rows, k * world, seed=1), randn_bf16(n, k * world, seed=2, std=0.02)
+    xs = [t.contiguous() for t in x.chunk(world, 1)]
+    ws = [t.contiguous() for t in w.chunk(world, 1)]
+    results = []
+    torch.cuda.synchronize()
+    for i in range(6):
+        moe = [randn_bf16(rows, n, seed=800 + 10 * i + r) for r in range(world)]
+        torch.cuda.synchronize()
+        with torch.cuda.stream(side):   # dense down-projection fused with its reduction, chain 2
+            dense = lw.rowpar(xs, ws, site=f"{i % 2}.mlp", chain=2)
+        with torch.cuda.stream(main):   # the experts' partial, chain 1
+            routed = lw.reduce(moe, site=f"{i % 2}.moe", chain=1)
+        results.append((moe, dense, routed))
+        torch.cuda.synchronize()
+        lw.check()
+        want_routed = red.reduce(np.stack([bits(p) for p in moe]))
+        for r in range(world):
+            assert_same_bits(bits(routed[r]), want_routed, f"round {i}: experts' sum, rank {r}")
+            assert_same_bits(bits(dense[r]), bits(dense[0]), f"round {i}: dense sum, rank {r} vs 0")
+    # the dense result equals the same call on a single stream
+    alone = LoopbackWorld(world).rowpar(xs, ws, site="alone", chain=2)
+    torch.cuda.synchronize()
+    assert_same_bits(bits(results[-1][1][0]), bits(alone[0]), "dense sum: two streams vs alone")

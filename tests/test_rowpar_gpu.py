@@ -22,7 +22,7 @@ def short_timeouts(monkeypatch):
     monkeypatch.setattr(parallel, "TIMEOUT_NS", 500_000_000)
 
 
-def gemm(x, w, splits=0, token_tiles=0, use_cluster=0):
+def gemm(x, w, splits=0, token_tiles=0):
     from dlmrt_b200 import _lib
     from dlmrt_b200._lib import DlmGemm
 
@@ -33,7 +33,6 @@ def gemm(x, w, splits=0, token_tiles=0, use_cluster=0):
     g = DlmGemm()
     g.x, g.w, g.m, g.n, g.k, g.ldx, g.ldw = x.data_ptr(), w.data_ptr(), m, n, k, x.stride(0), w.stride(0)
     g.workspace, g.workspace_bytes, g.splits, g.token_tiles = ws.data_ptr(), ws.numel(), splits, token_tiles
-    g.use_cluster = use_cluster
     _lib.check(_lib.lib().dlm_gemm_bf16(C.byref(g), out.data_ptr(), n, 0, None), "gemm")
     torch.cuda.synchronize()
     return out
@@ -103,9 +102,8 @@ def test_gemm_token_tiles_and_splits_agree(token_tiles, splits):
     x, w = integer_case(m, n, k, seed=3)
     want = f32_to_bf16(rowpar.gemm_f32(bits(x), bits(w)))
     from dlmrt_b200.layers.linear import Linear
-    for use_cluster in (0, 1, 0):  # partial tiles through the workspace, clusters meeting in shared memory, and back
-        assert_same_bits(bits(gemm(x, w, splits, token_tiles, use_cluster)), want,
-                         f"tiles {token_tiles} splits {splits} use_cluster {use_cluster}")
+    for attempt in range(2):
+        assert_same_bits(bits(gemm(x, w, splits, token_tiles)), want, f"tiles {token_tiles} splits {splits} #{attempt}")
     lin = Linear(w)
     out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
     for _ in range(5):  # same workspace, back to back, no host synchronisation in between
@@ -241,3 +239,34 @@ def test_linear_defers_into_group_reduce():
     g.flush(p2)
     torch.cuda.synchronize()
     assert_same_bits(bits(p2), partial_bits[0], "flushed partial")
+
+
+def test_projection_fed_by_the_previous_output_runs_unfused():
+    """The fused kernel re-arms the chain's previous output while some of its CTAs may still be loading x, so a
+    projection whose input IS that output must not be fused: the Group runs GEMM and reduction as two launches (the
+    reference's order), and the C entry point refuses the aliasing outright."""
+    from dlmrt_b200 import _lib
+    from dlmrt_b200._lib import DlmGemm
+    from dlmrt_b200.distributed.parallel import Group
+    from dlmrt_b200.layers.linear import Linear
+
+    g = Group.local("cuda:0")
+    m, n = 32, 2048
+    w = [randn_bf16(n, n, seed=90 + i, std=0.02) for i in range(2)]
+    lin = [Linear(w[i], group=g) for i in range(2)]
+    x = randn_bf16(m, n, seed=92)
+    before = _lib.lib().dlm_launch_count()
+    first = g.reduce(lin[0](x, out=g.partial("a", (m, n))), site="a")
+    assert _lib.lib().dlm_launch_count() == before + 1           # fused
+    second = g.reduce(lin[1](first, out=g.partial("b", (m, n))), site="b")
+    assert _lib.lib().dlm_launch_count() == before + 3           # GEMM, then reduction
+    torch.cuda.synchronize()
+    g.check()
+    want = Linear(w[1]).gemm(Linear(w[0]).gemm(x, torch.empty(m, n, dtype=torch.bfloat16, device="cuda")),
+                             torch.empty(m, n, dtype=torch.bfloat16, device="cuda"))
+    torch.cuda.synchronize()
+    assert_same_bits(bits(second), bits(want), "chained projections")
+    # through the C ABI the same aliasing is an error
+    comm, _ = g._comm(m, n, "c", 0, _lib.REDUCE, None, None, 0.0, 1.0)
+    gm = g._gemm(lin[0], second, 0)   # x = the chain's previous output = what this call would re-arm
+    assert _lib.lib().dlm_rowpar_bf16(C.byref(gm), C.byref(comm), None) == _lib.ERR_OVERLAP

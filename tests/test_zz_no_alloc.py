@@ -3,7 +3,7 @@ else's stream capture, a host that forbids allocation after start-up, a process 
 owns). Its split-K scratch is an 8 MiB array built into the library instead of a caller-provided workspace.
 
 Called through the C ABI only, twice in a row, and compared bit for bit with dlm_gemm_bf16 on the same tiling (the
-arithmetic is the same kernel, so the tolerance is zero). This file sorts last on purpose: a run that stops at the
+arithmetic is the same kernel, so the tolerance is zero), and once directly with the CPU oracle on exact operands. This file sorts last on purpose: a run that stops at the
 first failure has then already run every other test. It must pass alone in a fresh process and after all the others.
 """
 
@@ -76,6 +76,25 @@ def test_noalloc_rejects_what_does_not_fit_and_caps_what_it_picks_itself():
     want = torch.empty_like(out)
     assert call_workspace(x, w, want, 3, 1) == 0  # 2 KiB + 3 * m * n * 4 is the most that fits in 8 MiB
     assert_same_bits(bits(out), bits(want), "capped tiling")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m, n, k, splits", [(64, 512, 2048, 4), (256, 2560, 4096, 0), (32, 2048, 64, 8)])
+def test_noalloc_matches_the_cpu_oracle_on_exact_operands(m, n, k, splits):
+    """Not only equal to its sibling: small-integer operands make every product and sum exact, so the result must
+    equal the CPU restatement bit for bit, twice in a row on the shared scratch."""
+    from oracle import rowpar
+    from oracle.bf16 import f32_to_bf16
+
+    g = torch.Generator().manual_seed(m + n + k)
+    x = torch.randint(-3, 4, (m, k), generator=g).to(torch.bfloat16).cuda()
+    w = torch.randint(-2, 3, (n, k), generator=g).to(torch.bfloat16).cuda()
+    want = f32_to_bf16(rowpar.gemm_f32(bits(x), bits(w)))
+    for attempt in range(2):
+        out = torch.full((m, n), -1, dtype=torch.int16, device="cuda").view(torch.bfloat16)
+        assert call_noalloc(x, w, out, splits, 1 if splits else 0) == 0
+        torch.cuda.synchronize()
+        assert_same_bits(bits(out), want, f"call {attempt}")
 
 
 def test_noalloc_argument_checks_need_no_gpu():
