@@ -412,7 +412,69 @@ def run_dense(args, rig, link_gbs):
     }
     if ref_gpu is not None:
         line["reference_gpu_path"] = ref_gpu
+    if args.timeline and not only_reduce:
+        line["timeline"] = timeline(rig, step, group)
     return line
+
+
+STAMP_NAMES = {7: "kernel entry", 5: "dependency released", 4: "accumulator ready", 0: "mainloop drained, comm begins",
+               6: "tile summed and pushed", 2: "owned rows broadcast", 3: "collected"}
+
+
+def timeline(rig, step, group, layers=(3, 4)):
+    """Phase stamps (%globaltimer, written by thread 0 of every CTA when the caller passes a stamp buffer) of the two
+    fused launches of a few layers inside a graph replay: per phase the median over CTAs, in microseconds after the
+    launch's first CTA entered; `next_entry` is when the first CTA of the following launch entered. Plain run, no
+    profiler."""
+    import numpy as np
+
+    torch = rig.torch
+    sms = rig.lib.dlm_device_sms()
+    bufs, order = {}, []
+    original = group._comm
+
+    def comm(rows, n, site, *a, **kw):
+        c, out = original(rows, n, site, *a, **kw)
+        for layer in layers:
+            for k, name in enumerate((f"{layer}.post", f"{layer + 1}.input")):
+                if site == name:
+                    key = (layer, "o_proj" if k == 0 else "down_proj")
+                    if key not in bufs:
+                        bufs[key] = torch.zeros(sms * 8, dtype=torch.int64, device=rig.device)
+                        order.append(key)
+                    c.stamps = bufs[key].data_ptr()
+        return c, out
+
+    group._comm = comm
+    try:
+        with torch.cuda.stream(rig.stream):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=rig.stream):
+                step()
+    finally:
+        group._comm = original
+    rig.barrier()
+    with torch.cuda.stream(rig.stream):
+        for _ in range(5):
+            graph.replay()
+    rig.barrier()
+    group.check()
+    report, entries = {}, {}
+    for key in order:
+        s = bufs[key].cpu().numpy().reshape(sms, 8)
+        s = s[s[:, 7] > 0]
+        t0 = int(s[:, 7].min())
+        entries[key] = t0
+        phases = {"ctas": int(len(s))}
+        for slot, name in STAMP_NAMES.items():
+            v = s[:, slot]
+            v = v[v > 0] - t0
+            if len(v):
+                phases[name] = {"median": round(float(np.median(v)) / 1e3, 2), "max": round(float(v.max()) / 1e3, 2)}
+        report[f"layer {key[0]} {key[1]}"] = phases
+    for i, key in enumerate(order[:-1]):
+        report[f"layer {key[0]} {key[1]}"]["next_entry"] = round((entries[order[i + 1]] - entries[key]) / 1e3, 2)
+    return report
 
 
 def reference_gpu_path(rig, lin_o, lin_d, norms, x_o, x_d, h, args):
@@ -804,6 +866,7 @@ def main():
     ap.add_argument("--routing", default="uniform", choices=["uniform", "zipf"])
     ap.add_argument("--shard-of", type=int, default=1, help="profiling aid: run the K shard of a TP=<n> rank on the GPUs "
                     "given (the GEMM of a higher TP degree without its peers)")
+    ap.add_argument("--timeline", action="store_true", help="c2: also record the kernels' phase stamps of two layers")
     ap.add_argument("--only", action="store_true", help="c2 / k1 / k3: leave out the parity, moe and round blocks "
                     "(profiler captures)")
     args = ap.parse_args()
