@@ -42,6 +42,16 @@ class DlmMoe(C.Structure):
                 ("e_total", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64)]
 
 
+class DlmMoeFront(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("xq", C.c_void_p), ("xs", C.c_void_p), ("a1_inv", C.c_void_p), ("packed", C.c_void_p),
+                ("w13_codes", C.c_void_p), ("w13_scales", C.c_void_p), ("g1", C.c_void_p), ("a2_inv", C.c_void_p),
+                ("ids", C.c_void_p), ("weights", C.c_void_p), ("counts", C.c_void_p), ("amap", C.c_void_p),
+                ("slot_codes", C.c_void_p), ("slot_scales", C.c_void_p), ("act_codes", C.c_void_p),
+                ("act_scales", C.c_void_p), ("m", C.c_int32), ("hidden", C.c_int32), ("f", C.c_int32),
+                ("top_k", C.c_int32), ("m_max", C.c_int32), ("lo", C.c_int32), ("e_local", C.c_int32),
+                ("e_total", C.c_int32), ("activation", C.c_int32), ("reserved", C.c_int32)]
+
+
 class DlmStatus(C.Structure):
     _fields_ = [("code", C.c_int32), ("block", C.c_int32), ("slot", C.c_int32), ("phase", C.c_int32),
                 ("epoch", C.c_int32)]
@@ -84,6 +94,9 @@ SIGNATURES = {
     "dlm_rowpar_nvfp4_moe": (C.c_int, [C.POINTER(DlmMoe), C.POINTER(DlmComm), C.c_void_p]),
     "dlm_rowpar_nvfp4_moe_loopback": (C.c_int, [C.POINTER(DlmMoe), C.POINTER(DlmComm), C.c_int, C.c_void_p]),
     "dlm_moe_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
+    "dlm_moe_front_nvfp4": (C.c_int, [C.POINTER(DlmMoeFront), C.c_int, C.c_void_p]),
+    "dlm_route_packed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "dlm_abi_check_front": (C.c_int, [C.c_size_t]),
     "dlm_abi_check_moe": (C.c_int, [C.c_size_t]),
     "dlm_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "dlm_choose_tiling": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
@@ -112,7 +125,8 @@ def lib():
             fn = getattr(handle, name)
             fn.restype, fn.argtypes = res, args
         if handle.dlm_abi_check(C.sizeof(DlmComm), C.sizeof(DlmGemm), C.sizeof(DlmStatus)) != OK or \
-                handle.dlm_abi_check_moe(C.sizeof(DlmMoe)) != OK:
+                handle.dlm_abi_check_moe(C.sizeof(DlmMoe)) != OK or \
+                handle.dlm_abi_check_front(C.sizeof(DlmMoeFront)) != OK:
             raise ImportError(f"{LIB_PATH}: struct layout differs from this binding; rebuild the library")
         _lib = handle
     return _lib

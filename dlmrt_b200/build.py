@@ -14,7 +14,7 @@ from pathlib import Path
 PACKAGE = Path(__file__).resolve().parent
 CSRC = PACKAGE / "csrc"
 LIB = PACKAGE / "libdlmrt_b200.so"
-SOURCES = ["api.cu", "reduce.cu", "rowpar_bf16.cu", "rowpar_nvfp4.cu", "device_loop.cu"]
+SOURCES = ["api.cu", "reduce.cu", "rowpar_bf16.cu", "rowpar_nvfp4.cu", "moe_front.cu", "device_loop.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 

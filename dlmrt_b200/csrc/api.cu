@@ -577,6 +577,80 @@ int dlm_rowpar_nvfp4_moe(const DlmMoe* moe, const DlmComm* comm, dlm_stream_t st
     return launch_moe(p, grid, {static_cast<cudaStream_t>(stream), comm->pdl != 0, false});
 }
 
+static int check_front(const DlmMoeFront* a) {
+    if (a == nullptr) return DLM_ERR_NULL;
+    if ((a->x == nullptr && (a->xq == nullptr || a->xs == nullptr)) || (a->x != nullptr && a->a1_inv == nullptr))
+        return DLM_ERR_NULL;
+    if (!a->packed || !a->w13_codes || !a->w13_scales || !a->g1 || !a->a2_inv || !a->ids || !a->weights || !a->counts ||
+        !a->amap || !a->slot_codes || !a->slot_scales || !a->act_codes || !a->act_scales)
+        return DLM_ERR_NULL;
+    if (a->m < 1 || a->m > DLM_MAX_M || a->hidden < 256 || a->hidden % 256 || a->hidden > DLM_MAX_N) return DLM_ERR_SHAPE;
+    if (a->f < 64 || a->f % 64 || a->f > 4096 || a->top_k < 1 || a->top_k > 16) return DLM_ERR_SHAPE;
+    if (a->m_max < 1 || a->m_max > 256 || a->e_local < 1 || a->e_local > 256 || a->activation < 0 || a->activation > 1)
+        return DLM_ERR_SHAPE;
+    if (a->lo < 0 || a->lo + a->e_local > a->e_total) return DLM_ERR_SHAPE;
+    if (!aligned16(a->x) || !aligned16(a->xq) || !aligned16(a->xs) || !aligned16(a->w13_codes) ||
+        !aligned16(a->w13_scales) || !aligned16(a->slot_codes) || !aligned16(a->slot_scales) ||
+        !aligned16(a->act_codes) || (reinterpret_cast<uintptr_t>(a->act_scales) & 3))
+        return DLM_ERR_ALIGN;
+    return DLM_OK;
+}
+
+int dlm_moe_front_nvfp4(const DlmMoeFront* a, int pdl, dlm_stream_t stream) {
+    int rc = check_front(a);
+    if (rc != DLM_OK) return rc;
+    DeviceInfo info;
+    rc = device_info(&info);
+    if (rc != DLM_OK) return rc;
+    PrepareDev prep;
+    std::memset(&prep, 0, sizeof(prep));
+    prep.x = static_cast<const __nv_bfloat16*>(a->x);
+    prep.xq = static_cast<const uint8_t*>(a->xq), prep.xs = static_cast<const uint8_t*>(a->xs);
+    prep.a1_inv = a->a1_inv, prep.packed = a->packed;
+    prep.ids = a->ids, prep.weights = a->weights, prep.counts = a->counts, prep.amap = a->amap;
+    prep.slot_codes = static_cast<uint8_t*>(a->slot_codes), prep.slot_scales = static_cast<uint8_t*>(a->slot_scales);
+    prep.rows = a->m, prep.hidden = a->hidden, prep.top_k = a->top_k, prep.e_total = a->e_total;
+    prep.lo = a->lo, prep.e_local = a->e_local, prep.m_max = a->m_max;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    rc = launch_moe_prepare(prep, {s, pdl != 0, false});
+    if (rc != DLM_OK) return rc;
+    // GEMM1 on the expert pipeline: the "output features" are the 2F interleaved gate / up rows, K is the hidden size.
+    MoeParams<1> p;
+    std::memset(&p, 0, sizeof(p));
+    MoeDev* d = &p.g[0];
+    rc = make_map_u8(&d->tm_w, a->w13_codes, static_cast<long long>(a->e_local) * 2 * a->f, a->hidden / 2, kBlockF);
+    if (rc == DLM_OK)
+        rc = make_map_u8(&d->tm_a, a->slot_codes, static_cast<long long>(a->e_local) * a->m_max, a->hidden / 2, 8);
+    if (rc != DLM_OK) return rc;
+    d->a_scales = static_cast<const uint8_t*>(a->slot_scales);
+    d->w_scales = static_cast<const uint8_t*>(a->w13_scales);
+    d->amap = a->amap, d->counts = a->counts, d->g2 = a->g1, d->a2_inv = a->a2_inv;
+    d->aq_out = static_cast<uint8_t*>(a->act_codes), d->as_out = static_cast<uint8_t*>(a->act_scales);
+    d->m = a->m, d->n = 2 * a->f, d->f = a->hidden, d->top_k = a->top_k, d->m_max = a->m_max;
+    d->lo = a->lo, d->e_local = a->e_local, d->e_total = a->e_total;
+    d->f_out = a->f, d->act_kind = a->activation;
+    d->rows_cap = (a->m_max + 15) / 16 * 16;
+    if (d->rows_cap > 128) d->rows_cap = 128;
+    d->stages = moe_stages(d->rows_cap);
+    p.fused = 0;
+    return launch_moe_gate_up(p, info.sms, {s, true, false});  // always a dependent launch of the kernel above
+}
+
+int dlm_route_packed(const void* logits, const void* scale, int32_t* packed, int rows, int e, int top_k, int pdl,
+                     dlm_stream_t stream) {
+    if (logits == nullptr || scale == nullptr || packed == nullptr) return DLM_ERR_NULL;
+    if (rows < 1 || e < 1 || e > 256 || top_k < 1 || top_k > 16 || top_k > e) return DLM_ERR_SHAPE;
+    DeviceInfo info;
+    const int rc = device_info(&info);
+    if (rc != DLM_OK) return rc;
+    RouteDev r;
+    r.logits = static_cast<const __nv_bfloat16*>(logits), r.scale = static_cast<const __nv_bfloat16*>(scale);
+    r.packed = packed, r.rows = rows, r.e = e, r.top_k = top_k;
+    return launch_route_packed(r, {static_cast<cudaStream_t>(stream), pdl != 0, false});
+}
+
+int dlm_abi_check_front(size_t sizeof_front) { return sizeof_front == sizeof(DlmMoeFront) ? DLM_OK : DLM_ERR_SHAPE; }
+
 int dlm_rowpar_nvfp4_moe_loopback(const DlmMoe* moe, const DlmComm* comm, int nranks, dlm_stream_t stream) {
     if (moe == nullptr || comm == nullptr) return DLM_ERR_NULL;
     if (nranks < 1 || nranks > DLM_MAX_WORLD) return DLM_ERR_WORLD;

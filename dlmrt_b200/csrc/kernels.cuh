@@ -62,6 +62,35 @@ struct alignas(64) MoeDev {
     __nv_bfloat16* out;       // plain (unfused) output [m, n]
     long long ldo;
     int m, n, f, top_k, m_max, lo, e_local, e_total, stages, rows_cap;
+    // GEMM1 (gate / up) only: n = 2F interleaved weight rows, f = hidden, g2 = the GEMM1 alpha g1
+    const float* a2_inv;      // [e_local] 1 / (GEMM2 input scale): global scale of the activation's NVFP4 rounding
+    uint8_t* aq_out;          // [e_local * m_max, f_out / 2] activation codes written into the expert-major slots
+    uint8_t* as_out;          // [e_local * m_max, f_out / 16] their E4M3 scales (linear)
+    int f_out, act_kind;      // F; 0 = SwiGLU, 1 = GeGLU (tanh GELU)
+};
+
+// Routing bookkeeping + input quantisation in front of the experts' GEMM1 (one CTA per token).
+struct PrepareDev {
+    const __nv_bfloat16* x;    // [rows, hidden] BF16, or null when the input comes quantised
+    const uint8_t* xq;         // [rows, hidden / 2] codes and
+    const uint8_t* xs;         // [rows, hidden / 16] E4M3 scales of a pre-quantised input (x null)
+    const float* a1_inv;       // device scalar: global scale of the input's NVFP4 rounding (x given)
+    const int* packed;         // [rows, top_k] expert << 16 | BF16 weight bits
+    int* ids;                  // out [rows, top_k]
+    float* weights;            // out [rows, top_k]
+    int* counts;               // out [e_total]
+    int* amap;                 // out [e_total, m_max]
+    uint8_t* slot_codes;       // out [e_local * m_max, hidden / 2]
+    uint8_t* slot_scales;      // out [e_local * m_max, hidden / 16]
+    int rows, hidden, top_k, e_total, lo, e_local, m_max;
+};
+
+// Softmax top-k routing of one token per CTA (dlmrt/ops/triton/moe.py:14-47, PACK variant).
+struct RouteDev {
+    const __nv_bfloat16* logits;  // [rows, e] BF16
+    const __nv_bfloat16* scale;   // [e] per-expert scale
+    int* packed;                  // out [rows, top_k]
+    int rows, e, top_k;
 };
 
 template <int NR>
@@ -85,6 +114,9 @@ int launch_rowpar(const RowparParams<1>& p, int grid, const LaunchOpts& o);
 int launch_rowpar_loopback(const RowparParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o);
 int launch_moe(const MoeParams<1>& p, int grid, const LaunchOpts& o);
 int launch_moe_loopback(const MoeParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o);
+int launch_moe_gate_up(const MoeParams<1>& p, int grid, const LaunchOpts& o);
+int launch_moe_prepare(const PrepareDev& p, const LaunchOpts& o);
+int launch_route_packed(const RouteDev& p, const LaunchOpts& o);
 int moe_stage_bytes(int rows_cap);
 int moe_stages(int rows_cap);
 int rowpar_smem_bytes(int m, int stages);

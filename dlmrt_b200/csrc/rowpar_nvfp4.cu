@@ -20,6 +20,14 @@
 //   warps 4-11  per item: tcgen05.ld, times g2, BF16, scatter rows to Y[pair] through the expert's slot map
 // When all CTAs are through their items (arrival counter), rows of the output are combined from Y in FP32 and pushed
 // into the owner ranks' receive slots, and the reduction phases of comm.cuh follow.
+//
+// The same pipeline, instantiated with GATE_UP, is GEMM1 of the experts (the step in front of the down-projection,
+// dlmrt/ops/triton/nvfp4_moe.py:69-104 `_gate_up`): W13 [2F x hidden] streams instead of W2, its rows interleaved
+// (row 2i = gate feature i, row 2i + 1 = up feature i) so that a gate value and its up value sit in neighbouring lanes
+// of the accumulator; the expert's rows are the NVFP4-quantised tokens routed to it. The epilogue scales by g1, applies
+// SwiGLU or GeGLU in FP32, re-quantises to NVFP4 against 1 / a2 (per 16 features: E4M3 scale, E2M1 codes, the
+// approximate-reciprocal recipe of nvfp4_moe.py:36-47) and writes codes and scales straight into the expert-major
+// slots the down-projection reads. It ends there: no combine, no reduction.
 #include "kernels.cuh"
 
 namespace dlm {
@@ -143,7 +151,39 @@ __device__ __forceinline__ void combine_and_finish(const MoeDev& g, const CommDe
     }
 }
 
-template <int NR>
+// ---- NVFP4 re-quantisation of the activation (nvfp4_moe.py:20-47) --------------------------------------------------
+__device__ __forceinline__ float rcp_approx(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
+// FP32 -> FP8 E4M3 bits (round to nearest even, saturating) and back.
+__device__ __forceinline__ uint32_t f32_to_e4m3(float x) {
+    uint16_t pair;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pair) : "f"(0.f), "f"(x));
+    return pair & 0xFFu;
+}
+__device__ __forceinline__ float e4m3_to_f32(uint32_t bits) {
+    uint32_t h2;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(static_cast<uint16_t>(bits)));
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(h2 & 0xFFFFu)));
+}
+
+// One byte of two E2M1 codes (nearest, ties to the even code, saturating at 6): `lo` in the low nibble.
+__device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
+    uint32_t out;
+    asm("{\n.reg .b8 t;\ncvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\ncvt.u32.u8 %0, t;\n}" : "=r"(out) : "f"(hi), "f"(lo));
+    return out;
+}
+
+__device__ __forceinline__ float gated_activation(float gate, float up, int kind) {
+    if (kind == 0) return gate * (1.f / (1.f + __expf(-gate))) * up;  // SwiGLU: g * sigmoid(g) * u
+    const float inner = 0.7978845608028654f * (gate + 0.044715f * gate * gate * gate);
+    return 0.5f * gate * (1.f + tanhf(inner)) * up;                  // GeGLU with the tanh GELU
+}
+
+template <int NR, bool GATE_UP>
 __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_constant__ MoeParams<NR> p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const int slot = NR == 1 ? 0 : static_cast<int>(blockIdx.y);
@@ -185,9 +225,11 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
         const int e = threadIdx.x;
         const int total_rows = e < g.e_local ? min(g.counts[g.lo + e], g.m_max) : 0;
         int early = 0;  // the invocation counters, fetched in the same round trip as the counts
-        if (threadIdx.x == 352 && p.fused) early = c.epochs[block];
-        if (threadIdx.x == 353) early = g.gen[block];
-        if (threadIdx.x == 354 && p.fused) early = comm_failed(c);
+        if (!GATE_UP) {
+            if (threadIdx.x == 352 && p.fused) early = c.epochs[block];
+            if (threadIdx.x == 353) early = g.gen[block];
+            if (threadIdx.x == 354 && p.fused) early = comm_failed(c);
+        }
         const int nb = (total_rows + kItemRows - 1) / kItemRows;
         int incl = nb;
 #pragma unroll
@@ -358,22 +400,28 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
         }
         __syncwarp();
     } else if (warp >= 4) {
-        // Epilogue: lane = output feature of the tile, registers = the expert's rows. Scatter through the slot map.
+        // Epilogue: lane = output feature of the tile, registers = the expert's rows.
         const int quarter = warp & 3, half = (warp - 4) >> 2;
         int item = 0;
         for (int i = block; i < n_items; i += blocks, ++item) {
             const Item t = item_of(i);
             const int n_mma = max(16, (t.cnt + 15) & ~15);
             const int buf = item & 1;
-            // Issued before the wait so that their latency overlaps the item's MMAs: the expert's scale and, for each
-            // of this warp's 16-row chunks (at most four), the destination row of lane % 16's accumulator column.
+            // Issued before the wait so that their latency overlaps the item's MMAs: the expert's scale(s) and, for the
+            // down-projection, for each of this warp's 16-row chunks (at most four) the destination row of lane % 16's
+            // accumulator column.
             const float g2 = g.g2[t.e];
-            const int* slots = g.amap + static_cast<size_t>(g.lo + t.e) * g.m_max + t.row0;
-            int dest[4];
+            float a2i = 0.f;
+            int dest[4] = {-1, -1, -1, -1};
+            if (GATE_UP) {
+                a2i = g.a2_inv[t.e];
+            } else {
+                const int* slots = g.amap + static_cast<size_t>(g.lo + t.e) * g.m_max + t.row0;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const int row = (half + 2 * q) * 16 + (lane & 15);
-                dest[q] = row < t.cnt ? slots[row] : -1;
+                for (int q = 0; q < 4; ++q) {
+                    const int row = (half + 2 * q) * 16 + (lane & 15);
+                    dest[q] = row < t.cnt ? slots[row] : -1;
+                }
             }
             const bool ok = mbar_wait(&sm->acc_full[buf], (item >> 1) & 1, deadline);
             if (!ok) report(c.status, kErrTimeout, 0, kPhasePipeline, 2);
@@ -386,11 +434,38 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
                     uint32_t r[16];
                     tmem_load_16(tmem + kTmemAcc + buf * kItemRows + (static_cast<uint32_t>(quarter * 32) << 16) + chunk * 16, r);
                     tmem_load_wait();
+                    if (GATE_UP) {
+                        // Tile row 2i holds gate feature i, row 2i + 1 its up feature: neighbouring lanes. The warp's 32
+                        // lanes are one block of 16 activation features (ft * 64 + quarter * 16 ..) of 16 token rows.
+                        const size_t slot0 = static_cast<size_t>(t.e) * g.m_max + t.row0;
+                        const int half_f = g.f_out / 2, groups = g.f_out / 16;
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int pair = __shfl_sync(0xffffffff, dest[q], j);
-                        if (pair >= 0)
-                            g.y[static_cast<size_t>(pair) * g.n + col] = __float2bfloat16_rn(__uint_as_float(r[j]) * g2);
+                        for (int j = 0; j < 16; ++j) {
+                            const float mine = __uint_as_float(r[j]) * g2;
+                            const float other = __shfl_xor_sync(0xffffffff, mine, 1);
+                            const float act = gated_activation(lane & 1 ? other : mine, lane & 1 ? mine : other, g.act_kind);
+                            float amax = fabsf(act);
+#pragma unroll
+                            for (int o = 2; o < 32; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffff, amax, o));
+                            const uint32_t sf = f32_to_e4m3(a2i * (amax * rcp_approx(6.f)));
+                            const float scale = amax != 0.f ? rcp_approx(e4m3_to_f32(sf) * rcp_approx(a2i)) : 0.f;
+                            const float y = act * scale;
+                            const float y_next = __shfl_down_sync(0xffffffff, y, 2);  // the next feature's value
+                            const int row = chunk * 16 + j;
+                            if (row < t.cnt) {
+                                if ((lane & 3) == 0)
+                                    g.aq_out[(slot0 + row) * half_f + t.ft * 32 + quarter * 8 + (lane >> 2)] =
+                                        static_cast<uint8_t>(e2m1x2(y, y_next));
+                                if (lane == 0) g.as_out[(slot0 + row) * groups + t.ft * 4 + quarter] = static_cast<uint8_t>(sf);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int pair = __shfl_sync(0xffffffff, dest[q], j);
+                            if (pair >= 0)
+                                g.y[static_cast<size_t>(pair) * g.n + col] = __float2bfloat16_rn(__uint_as_float(r[j]) * g2);
+                        }
                     }
                 }
             }
@@ -408,6 +483,10 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
     if (warp == 2) {
         tcgen05_fence_after();
         tmem_dealloc(tmem, kTmemCols);
+    }
+    if (GATE_UP) {  // the activation slots are written; the down-projection launch that follows does the rest
+        pdl_launch_dependents();
+        return;
     }
     CommCtx x{};
     if (p.fused) x = comm_begin(c, block, blocks, sm->epoch, sm->failed);
@@ -476,7 +555,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
     }
 }
 
-template <int NR>
+template <int NR, bool GATE_UP>
 static int launch_impl(const MoeParams<NR>& p, dim3 grid, const LaunchOpts& o) {
     const int smem = p.g[0].stages * moe_stage_bytes(p.g[0].rows_cap) + static_cast<int>(sizeof(MoeSmem)) + 1024;
     static bool raised[64] = {};
@@ -484,7 +563,7 @@ static int launch_impl(const MoeParams<NR>& p, dim3 grid, const LaunchOpts& o) {
     int dev = 0;
     (void)cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !raised[dev]) {
-        err = cudaFuncSetAttribute(moe_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        err = cudaFuncSetAttribute(moe_kernel<NR, GATE_UP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    kSmemBudget + static_cast<int>(sizeof(MoeSmem)) + 1024);
         raised[dev] = err == cudaSuccess;
     }
@@ -508,7 +587,7 @@ static int launch_impl(const MoeParams<NR>& p, dim3 grid, const LaunchOpts& o) {
         }
         config.attrs = attrs;
         config.numAttrs = n;
-        err = cudaLaunchKernelEx(&config, moe_kernel<NR>, p);
+        err = cudaLaunchKernelEx(&config, moe_kernel<NR, GATE_UP>, p);
     }
     if (err != cudaSuccess) {
         g_last_cuda_error = static_cast<int>(err);
@@ -519,10 +598,12 @@ static int launch_impl(const MoeParams<NR>& p, dim3 grid, const LaunchOpts& o) {
     return 0;
 }
 
-int launch_moe(const MoeParams<1>& p, int grid, const LaunchOpts& o) { return launch_impl<1>(p, dim3(grid), o); }
+int launch_moe(const MoeParams<1>& p, int grid, const LaunchOpts& o) { return launch_impl<1, false>(p, dim3(grid), o); }
+
+int launch_moe_gate_up(const MoeParams<1>& p, int grid, const LaunchOpts& o) { return launch_impl<1, true>(p, dim3(grid), o); }
 
 int launch_moe_loopback(const MoeParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o) {
-    return launch_impl<kMaxWorld>(p, dim3(grid, nranks), o);
+    return launch_impl<kMaxWorld, false>(p, dim3(grid, nranks), o);
 }
 
 }  // namespace dlm

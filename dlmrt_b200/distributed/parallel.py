@@ -203,15 +203,29 @@ class Group:
 
     def defer(self, linear, x, out):
         """Record `out = x @ linear.weight^T` instead of running it; the next reduce* of `out` runs it fused."""
-        self._pending[out.data_ptr()] = (linear, x, out)
+        self._pending[out.data_ptr()] = ("linear", linear, x, out)
         return out
 
+    def defer_experts(self, out, down):
+        """Record the NVFP4 expert down-projection + combine into `out` (keyword arguments of
+        dlmrt_b200.quantization.nvfp4.moe_down) instead of running it; the next reduce* of `out` runs it fused."""
+        self._pending[out.data_ptr()] = ("experts", down, None, out)
+        return out
+
+    def _run_alone(self, pending):
+        kind, what, x, out = pending
+        if kind == "linear":
+            what.gemm(x, out)
+        else:
+            from ..quantization import nvfp4
+
+            nvfp4.moe_down(out=out, **what)
+
     def flush(self, partial):
-        """Run a deferred GEMM on its own, for callers that read the partial before reducing it."""
+        """Run a deferred producer on its own, for callers that read the partial before reducing it."""
         pending = self._pending.pop(partial.data_ptr(), None)
         if pending is not None:
-            linear, x, out = pending
-            linear.gemm(x, out)
+            self._run_alone(pending)
         return partial
 
     def workspace(self, chain, nbytes):
@@ -290,15 +304,21 @@ class Group:
         # The fused kernel re-arms `last` and fills `out` while other CTAs still load the GEMM's input; an input that
         # IS one of those (a projection fed straight from the previous reduction) therefore runs as two kernels, the
         # order the reference has anyway.
-        fusable = pending is not None and n <= _lib.FUSED_MAX_N and not self._overlap(pending[1], last) \
-            and not self._overlap(pending[1], out)
-        if fusable:
-            linear, x, _ = pending
-            gemm = self._gemm(linear, x, chain)
+        fusable = pending is not None and n <= _lib.FUSED_MAX_N and not self._overlap(pending[2], last) \
+            and not self._overlap(pending[2], out)
+        if fusable and pending[0] == "linear":
+            gemm = self._gemm(pending[1], pending[2], chain)
             _lib.check(_lib.lib().dlm_rowpar_bf16(C.byref(gemm), C.byref(comm), stream), f"rowpar {site}")
+        elif fusable:  # the experts' down-projection + combine (+ shared) in front of the same reduction
+            from ..quantization import nvfp4
+
+            down = dict(pending[1])
+            shared = down.pop("shared", None)
+            m = nvfp4.descriptor(shared=shared, **down)
+            _lib.check(_lib.lib().dlm_rowpar_nvfp4_moe(C.byref(m), C.byref(comm), stream), f"experts {site}")
         else:
             if pending is not None:
-                pending[0].gemm(pending[1], pending[2])
+                self._run_alone(pending)
             _lib.check(_lib.lib().dlm_reduce_bf16(partial.data_ptr(), C.byref(comm), stream), f"reduce {site}")
         self._last[chain] = out
         return out

@@ -1,11 +1,14 @@
-"""NVFP4 routed experts on the row-parallel hot path: formats, expert layout and the expert down-projection entry.
+"""NVFP4 routed experts on the row-parallel hot path: formats, expert layout and the MoE entry points.
 
 Mirror of the parts of the reference's `dlmrt/quantization/nvfp4.py` that sit on the path: the format (:1-12,23), the
-packed top-k (`pack`, :275-277), an expert layout for this library's kernel (`b200_experts`, the counterpart of
-`trtllm_experts` :89-121 / `triton_experts` :159-181) and the call that replaces the GEMM2 + finalize half of
-`trtllm_moe` (:280-306), optionally fused with the reduction over ranks. GEMM1 (gate/up + activation + requantisation)
-is the step before this path and is not part of it: the entry point takes GEMM2's input already quantised, in the
-expert-major slot layout of `dlmrt/ops/triton/nvfp4_moe.py:11-12` (what its `_gate_up` kernel writes).
+packed top-k (`pack`, :275-277), an expert layout for this library's kernels (`b200_experts`, the counterpart of
+`trtllm_experts` :89-121 / `triton_experts` :159-181) and `trtllm_moe` (:280-306) with the reference's signature: the
+whole routed-expert call (input quantisation, GEMM1 + activation + re-quantisation, GEMM2, weighted combine), which the
+reference hands to FlashInfer's TRT-LLM-gen kernels on a B200. `Experts` mirrors DiffusionGemma's `TrtllmExperts`
+(dlmrt/models/diffusion_gemma/experts.py:47-114). When the output is a tensor-parallel group's symmetric partial, the
+down-projection half is deferred into the `Group.reduce*` that follows, one fused launch. `moe_down` is that half
+alone, for callers that hold GEMM2's input already quantised in the expert-major slot layout of
+`dlmrt/ops/triton/nvfp4_moe.py:11-12`.
 
 Nothing numeric runs in Python here: tensors are only laid out and handed to libdlmrt_b200.so.
 """
@@ -15,7 +18,7 @@ import ctypes as C
 import torch
 
 from .. import _lib
-from .._lib import DlmMoe
+from .._lib import DlmMoe, DlmMoeFront
 
 E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
 
@@ -46,19 +49,45 @@ def interleave_scales(scales):
     return s.contiguous().reshape(*lead, n // 128, groups // 4, 512)
 
 
-def b200_experts(parts, layer, lo, count, device):
-    """Layer `layer`'s experts [lo, lo + count) for this library: down-projection codes as exported, their block
-    scales in atoms, and per expert the GEMM2 alpha (input scale x weight scale) and the GEMM2 input quantisation
-    scale. `parts[(layer, expert, proj, field)]` are the checkpoint's tensors, as in the reference's loaders."""
-    def get(e, field):
-        return parts[(layer, e, "down", field)].to(device)
+def interleave_gate_up(gate, up):
+    """[..., F, X] gate and up rows -> [..., 2F, X] with row 2i = gate row i, row 2i + 1 = up row i: the order GEMM1's
+    kernel wants, so that a gate value and its up value land in neighbouring lanes of the accumulator."""
+    return torch.stack((gate, up), dim=-2).flatten(-3, -2).contiguous()
 
-    w2 = torch.stack([get(e, "weight") for e in range(lo, lo + count)]).contiguous()
-    s2 = torch.stack([get(e, "weight_scale").view(torch.uint8) for e in range(lo, lo + count)])
-    a2 = torch.stack([get(e, "input_scale").float().reshape(()) for e in range(lo, lo + count)])
-    ws2 = torch.stack([get(e, "weight_scale_2").float().reshape(()) for e in range(lo, lo + count)])
-    return {"backend": "b200", "lo": lo, "w2": w2, "s2": interleave_scales(s2), "g2": (a2 * ws2).contiguous(),
-            "a2_inv": (1 / a2).contiguous()}
+
+def b200_experts(parts, layer, lo, count, device, group=None):
+    """Layer `layer`'s experts [lo, lo + count) for this library (counterpart of `trtllm_experts`, nvfp4.py:89-121):
+    codes as exported (GEMM1 rows interleaved gate / up), block scales in 128 x 4 atoms, and per expert the GEMM
+    alphas (input scale x weight scale) and the reciprocal input scales. Gate and up must share their per-tensor
+    scale and all experts one GEMM1 input scale, as the reference requires (nvfp4.py:75-86,103-104).
+    `parts[(layer, expert, proj, field)]` are the checkpoint's tensors, as in the reference's loaders. `group`: the
+    tensor-parallel group whose reductions the down-projection may be fused into."""
+    def get(e, proj, field):
+        return parts[(layer, e, proj, field)].to(device)
+
+    def scalars(proj, field):
+        return torch.stack([get(e, proj, field).float().reshape(()) for e in range(lo, lo + count)])
+
+    experts = range(lo, lo + count)
+    w2 = torch.stack([get(e, "down", "weight") for e in experts]).contiguous()
+    s2 = torch.stack([get(e, "down", "weight_scale").view(torch.uint8) for e in experts])
+    a2, ws2 = scalars("down", "input_scale"), scalars("down", "weight_scale_2")
+    out = {"backend": "b200", "lo": lo, "w2": w2, "s2": interleave_scales(s2), "g2": (a2 * ws2).contiguous(),
+           "a2_inv": (1 / a2).contiguous(), "group": group}
+    if (layer, lo, "gate", "weight") in parts:
+        for e in experts:
+            if not torch.equal(get(e, "gate", "weight_scale_2"), get(e, "up", "weight_scale_2")):
+                raise ValueError(f"layer {layer} expert {e}: gate and up have different per-tensor scales")
+        a1 = scalars("gate", "input_scale")
+        if not torch.equal(a1, scalars("up", "input_scale")) or not bool((a1 == a1[0]).all()):
+            raise ValueError(f"layer {layer}: the experts' GEMM1 input scales differ")
+        w13 = interleave_gate_up(torch.stack([get(e, "gate", "weight") for e in experts]),
+                                 torch.stack([get(e, "up", "weight") for e in experts]))
+        s13 = interleave_gate_up(torch.stack([get(e, "gate", "weight_scale").view(torch.uint8) for e in experts]),
+                                 torch.stack([get(e, "up", "weight_scale").view(torch.uint8) for e in experts]))
+        out.update(w13=w13, s13=interleave_scales(s13), g1=(a1 * scalars("gate", "weight_scale_2")).contiguous(),
+                   a1_inv=(1 / a1[:1]).contiguous())
+    return out
 
 
 class Buffers:
@@ -115,3 +144,122 @@ def moe_down(act_codes, act_scales, amap, counts, experts, ids, weights, buffers
     _lib.check(_lib.lib().dlm_rowpar_nvfp4_moe(C.byref(m), C.byref(comm), stream), f"moe_down {site}")
     group._last[chain] = reduced
     return reduced
+
+
+ACTIVATIONS = {"swiglu": 0, "geglu": 1}
+
+
+class FrontBuffers:
+    """Scratch of one routed-expert call for up to `rows` tokens on `count` local experts: what the front half writes
+    for the down-projection (ids, weights, slot map, quantised rows and activations in expert-major slots) and the
+    down-projection's own workspace. Every expert has room for all rows, as in the reference's layouts."""
+
+    def __init__(self, rows, hidden, intermediate, count, num_experts, top_k, device):
+        u8 = dict(device=device, dtype=torch.uint8)
+        i32 = dict(device=device, dtype=torch.int32)
+        self.rows = rows
+        self.ids = torch.zeros(rows, top_k, **i32)
+        self.weights = torch.zeros(rows, top_k, device=device, dtype=torch.float32)
+        self.counts = torch.zeros(num_experts, **i32)
+        self.amap = torch.zeros(num_experts, rows, **i32)
+        self.slot_codes = torch.zeros(count * rows, hidden // 2, **u8)
+        self.slot_scales = torch.zeros(count * rows, hidden // 16, **u8)
+        self.act_codes = torch.zeros(count * rows, intermediate // 2, **u8)
+        self.act_scales = torch.zeros(count * rows, intermediate // 16, **u8)
+        self.down = Buffers(rows, hidden, top_k, device)
+
+
+def trtllm_moe(x, packed, experts, out, num_experts, lo, intermediate, quantized=None, activation="geglu", shared=None):
+    """out = sum over each row's experts in [lo, lo + count) of weight * expert(x) [+ shared], all NVFP4: same
+    arguments and meaning as the reference's `trtllm_moe` (dlmrt/quantization/nvfp4.py:280-306), on this library's
+    kernels. `packed` [rows, k] int32: see `pack`. `quantized`: x already quantised, (codes [rows, hidden / 2] uint8,
+    scales [rows, hidden / 16] uint8), with x None. `experts`: see `b200_experts`.
+
+    `shared` (not in the reference's signature): a BF16 [rows, hidden] addend folded into the combine, in place of the
+    `torch.add(routed, shared, out=...)` that follows the call in dlmrt/models/llada2/model.py:360-362.
+
+    Three launches: per-token bookkeeping + input quantisation, GEMM1 + activation + re-quantisation, and the
+    down-projection + combine. When `out` is a symmetric partial of `experts["group"]`, the third is not run here but
+    deferred into the `Group.reduce*` of `out` that follows (one fused launch with the reduction over ranks)."""
+    if quantized is None:
+        rows, hidden = x.shape
+        if x.dtype != torch.bfloat16 or not x.is_contiguous():
+            raise ValueError("x must be a contiguous BF16 [rows, hidden] tensor")
+        device = x.device
+    else:
+        xq, xs = quantized
+        rows, hidden = xq.shape[0], xq.shape[1] * 2
+        device = xq.device
+    count, top_k = experts["w2"].shape[0], packed.shape[1]
+    if experts["lo"] != lo or "w13" not in experts:
+        raise ValueError("experts were laid out for another rank, or without their gate / up weights (b200_experts)")
+    if experts["w13"].shape[1] != 2 * intermediate or experts["w13"].shape[2] * 2 != hidden:
+        raise ValueError(f"experts are {tuple(experts['w13'].shape)}; the call says hidden {hidden}, intermediate {intermediate}")
+    cache = experts.setdefault("_buffers", {})
+    if rows not in cache:  # first call with this row count: before any graph capture, as the reference tunes
+        cache[rows] = FrontBuffers(rows, hidden, intermediate, count, num_experts, top_k, device)
+    b = cache[rows]
+    f = DlmMoeFront()
+    if quantized is None:
+        f.x, f.a1_inv = x.data_ptr(), experts["a1_inv"].data_ptr()
+    else:
+        f.xq, f.xs = xq.data_ptr(), xs.data_ptr()
+    f.packed = packed.data_ptr()
+    f.w13_codes, f.w13_scales = experts["w13"].data_ptr(), experts["s13"].data_ptr()
+    f.g1, f.a2_inv = experts["g1"].data_ptr(), experts["a2_inv"].data_ptr()
+    f.ids, f.weights, f.counts, f.amap = b.ids.data_ptr(), b.weights.data_ptr(), b.counts.data_ptr(), b.amap.data_ptr()
+    f.slot_codes, f.slot_scales = b.slot_codes.data_ptr(), b.slot_scales.data_ptr()
+    f.act_codes, f.act_scales = b.act_codes.data_ptr(), b.act_scales.data_ptr()
+    f.m, f.hidden, f.f, f.top_k, f.m_max = rows, hidden, intermediate, top_k, rows
+    f.lo, f.e_local, f.e_total, f.activation = lo, count, num_experts, ACTIVATIONS[activation]
+    if packed.dtype != torch.int32 or not packed.is_contiguous():
+        raise ValueError("packed must be a contiguous int32 [rows, top_k] tensor")
+    stream = torch.cuda.current_stream(device).cuda_stream
+    _lib.check(_lib.lib().dlm_moe_front_nvfp4(C.byref(f), 1, stream), "trtllm_moe: front half")
+    down = dict(act_codes=b.act_codes, act_scales=b.act_scales, amap=b.amap, counts=b.counts, experts=experts, ids=b.ids,
+                weights=b.weights, buffers=b.down, num_experts=num_experts, shared=shared)
+    group = experts.get("group")
+    if group is not None and group.is_partial(out):
+        return group.defer_experts(out, down)
+    return moe_down(out=out, **down)
+
+
+def route_packed(logits, per_expert_scale, packed, top_k):
+    """The router's top-k for this path, packed (dlmrt/ops/triton/moe.py:70-73): logits [rows, experts] BF16,
+    per_expert_scale [experts] BF16 -> packed [rows, top_k] int32 = expert << 16 | BF16 weight bits."""
+    rows, e = logits.shape
+    if logits.dtype != torch.bfloat16 or per_expert_scale.dtype != torch.bfloat16 or packed.dtype != torch.int32:
+        raise ValueError("route_packed takes BF16 logits and scales and an int32 output")
+    stream = torch.cuda.current_stream(logits.device).cuda_stream
+    _lib.check(_lib.lib().dlm_route_packed(logits.contiguous().data_ptr(), per_expert_scale.data_ptr(), packed.data_ptr(),
+                                           rows, e, top_k, 1, stream), "route_packed")
+    return packed
+
+
+class Experts:
+    """DiffusionGemma's NVFP4 routed experts on this library (mirror of `TrtllmExperts`,
+    dlmrt/models/diffusion_gemma/experts.py:47-114): takes a layer's router logits and writes this rank's part of the
+    MoE output. `config` needs `top_k_experts`, `hidden_size`, `num_experts`, `moe_intermediate_size`. `sample` and
+    `extra_rows` are accepted for signature compatibility (there are no tactics to tune here)."""
+
+    def __init__(self, config, lo, rows, device, sample=None, extra_rows=()):
+        c = self.config = config
+        self.lo = lo
+        most = max([rows, *extra_rows])
+        self.packed = torch.zeros(most, c.top_k_experts, dtype=torch.int32, device=device)
+        # The expert input as the post-attention kernel writes it: NVFP4 codes and E4M3 scales (see `quantized`).
+        self.codes = torch.zeros(most, c.hidden_size // 2, dtype=torch.uint8, device=device)
+        self.scales = torch.zeros(most, c.hidden_size // 16, dtype=torch.uint8, device=device)
+
+    def quantized(self, layer):
+        """(global scale, codes, scales): where the kernel in front writes this layer's quantised expert input, read by
+        __call__ with x None."""
+        return layer["fp4"]["a1_inv"], self.codes, self.scales
+
+    def __call__(self, x, logits, layer, out):
+        """`x` None: the input is already in `codes` / `scales` (see `quantized`)."""
+        c, n = self.config, logits.shape[0]
+        packed = self.packed[:n]
+        route_packed(logits, layer["expert_scale"], packed, c.top_k_experts)
+        return trtllm_moe(x, packed, layer["fp4"], out, c.num_experts, self.lo, c.moe_intermediate_size,
+                          quantized=None if x is not None else (self.codes[:n], self.scales[:n]))

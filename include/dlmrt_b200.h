@@ -155,6 +155,41 @@ typedef struct DlmMoe {
     int64_t workspace_bytes;
 } DlmMoe;
 
+/* What runs in front of the expert down-projection inside the reference's one FlashInfer call
+ * (dlmrt/quantization/nvfp4.py:280-306; arithmetic as stated in dlmrt/ops/triton/nvfp4_moe.py:36-104): the packed top-k
+ * is unpacked and every expert's rows are numbered in token order, the input rows are quantised to NVFP4 against the
+ * GEMM1 input scale (or taken pre-quantised, dlmrt/models/diffusion_gemma/experts.py:64-67) and copied into
+ * expert-major slots, and GEMM1 (gate and up, FP4 tensor cores) + SwiGLU / GeGLU in FP32 + NVFP4 re-quantisation against
+ * 1 / a2 writes GEMM2's input straight into the slots DlmMoe.act_codes / act_scales name. Everything the
+ * down-projection needs (ids, weights, counts, amap, activation slots) is produced here on the device.
+ * Weight layout, made once when the experts are loaded: W13 rows interleaved, row 2i = gate feature i, row 2i + 1 = up
+ * feature i ([e_local, 2F, hidden / 2] codes), block scales of those rows in the same 128-row x 4-scale atoms as
+ * DlmMoe.w_scales ([e_local, 2F / 128, hidden / 64, 512]). */
+typedef struct DlmMoeFront {
+    const void* x;            /* [m, hidden] BF16 expert input, or NULL: then xq / xs hold it already quantised */
+    const void* xq;           /* [m, hidden / 2] uint8 codes (x NULL) */
+    const void* xs;           /* [m, hidden / 16] E4M3 scales, linear (x NULL) */
+    const float* a1_inv;      /* device scalar: 1 / (GEMM1 input scale), the global scale of the input's rounding */
+    const int32_t* packed;    /* [m, top_k] expert << 16 | BF16 routing-weight bits, ascending experts per token */
+    const void* w13_codes;    /* [e_local, 2F, hidden / 2] uint8, rows interleaved gate / up */
+    const void* w13_scales;   /* [e_local, 2F / 128, hidden / 64, 512] E4M3 atoms */
+    const float* g1;          /* [e_local] GEMM1 alpha = input scale x weight scale */
+    const float* a2_inv;      /* [e_local] 1 / (GEMM2 input scale) */
+    int32_t* ids;             /* out [m, top_k] */
+    float* weights;           /* out [m, top_k] */
+    int32_t* counts;          /* out [e_total] */
+    int32_t* amap;            /* out [e_total, m_max] */
+    void* slot_codes;         /* scratch [e_local * m_max, hidden / 2]: the quantised input rows, expert-major */
+    void* slot_scales;        /* scratch [e_local * m_max, hidden / 16] */
+    void* act_codes;          /* out [e_local * m_max, f / 2]: GEMM2's input */
+    void* act_scales;         /* out [e_local * m_max, f / 16] */
+    int32_t m, hidden, f, top_k; /* m <= 256; hidden % 256 == 0, <= 8192; f % 64 == 0; top_k <= 16 */
+    int32_t m_max;            /* rows reserved per expert (<= 256); rows beyond it are dropped */
+    int32_t lo, e_local, e_total;
+    int32_t activation;       /* 0 SwiGLU (g * sigmoid(g) * u), 1 GeGLU (tanh GELU) */
+    int32_t reserved;
+} DlmMoeFront;
+
 /* Device status read back by dlm_status_read(). */
 typedef struct DlmStatus {
     int32_t code;   /* DLM_OK or DLM_ERR_TIMEOUT */
@@ -225,6 +260,18 @@ DLM_API int dlm_moe_nvfp4(const DlmMoe* moe, void* out, int64_t ldo, int pdl, dl
 DLM_API int dlm_rowpar_nvfp4_moe(const DlmMoe* moe, const DlmComm* comm, dlm_stream_t stream);
 DLM_API int dlm_rowpar_nvfp4_moe_loopback(const DlmMoe* moe, const DlmComm* comm, int nranks, dlm_stream_t stream);
 DLM_API size_t dlm_moe_workspace_bytes(int m, int n, int top_k);
+
+/* Two launches: the per-token bookkeeping + quantisation, then GEMM1 + activation + re-quantisation (see DlmMoeFront).
+ * With dlm_moe_nvfp4 / dlm_rowpar_nvfp4_moe behind it this replaces the whole of nvfp4.trtllm_moe
+ * (dlmrt/quantization/nvfp4.py:280-306). */
+DLM_API int dlm_moe_front_nvfp4(const DlmMoeFront* front, int pdl, dlm_stream_t stream);
+
+/* The router's top-k as the reference packs it for this path (dlmrt/ops/triton/moe.py:70-73 `route_packed`): FP32
+ * softmax of `logits` [rows, e] BF16, the top_k largest (ties to the lower expert), renormalised, times `scale` [e]
+ * BF16, in ascending expert order, packed[rows, top_k] = expert << 16 | BF16 weight bits. e <= 256, top_k <= 16. */
+DLM_API int dlm_route_packed(const void* logits, const void* scale, int32_t* packed, int rows, int e, int top_k, int pdl,
+                             dlm_stream_t stream);
+DLM_API int dlm_abi_check_front(size_t sizeof_front);
 
 /* Single-GPU loopback of `nranks` ranks of dlm_rowpar_bf16 in one launch (see dlm_reduce_bf16_loopback). */
 DLM_API int dlm_rowpar_bf16_loopback(const DlmGemm* gemm, const DlmComm* comm, int nranks, dlm_stream_t stream);
