@@ -54,8 +54,9 @@ int check_comm(const DlmComm* c) {
             if (!aligned16(c->out_peers[s])) return DLM_ERR_ALIGN;
         }
     }
-    // One-shot: a plain sum only (the residual stream of modes 1 and 2 is kept per owner), and only between ranks.
-    if (c->one_shot != 0 && (c->one_shot != 1 || c->mode != DLM_REDUCE)) return DLM_ERR_SHAPE;
+    // One-shot: every rank sums (and, in modes 1 and 2, normalises) all rows itself; with mode 2 the residual stream
+    // is then REPLICATED: each rank updates all rows of its own copy of h.
+    if (c->one_shot != 0 && c->one_shot != 1) return DLM_ERR_SHAPE;
     if (!aligned16(c->recv_mc)) return DLM_ERR_ALIGN;
     if (c->mode != DLM_REDUCE && c->weight == nullptr) return DLM_ERR_NULL;
     if (c->mode == DLM_REDUCE_NORM_RESIDUAL && c->h == nullptr) return DLM_ERR_NULL;

@@ -66,12 +66,13 @@ class LoopbackWorld:
             return _lib.REDUCE
         return _lib.REDUCE_NORM_RESIDUAL if hs is not None else _lib.REDUCE_NORM
 
-    def _comms(self, rows, n, site, chain, hs, weight, eps, scale):
+    def _comms(self, rows, n, site, chain, hs, weight, eps, scale, replicated=False):
         comms = (DlmComm * self.world)()
         outs = []
         mode = self._mode(hs, weight)
         for r, g in enumerate(self.groups):
-            c, out = g._comm(rows, n, site, chain, mode, hs[r] if hs is not None else None, weight, eps, scale)
+            c, out = g._comm(rows, n, site, chain, mode, hs[r] if hs is not None else None, weight, eps, scale,
+                             replicated and hs is not None)
             c.pdl = 0
             comms[r] = c
             outs.append(out)
@@ -81,21 +82,22 @@ class LoopbackWorld:
         for g, out in zip(self.groups, outs):
             g._last[chain] = out
 
-    def reduce(self, partials, *, site, chain=0, hs=None, weight=None, eps=0.0, scale=1.0):
+    def reduce(self, partials, *, site, chain=0, hs=None, weight=None, eps=0.0, scale=1.0, replicated=False):
         """All ranks of Group.reduce / reduce_norm in one launch; partials[r] is rank r's [rows, n] partial.
         Returns every rank's output buffer."""
         rows, n = partials[0].shape
-        comms, outs = self._comms(rows, n, site, chain, hs, weight, eps, scale)
+        comms, outs = self._comms(rows, n, site, chain, hs, weight, eps, scale, replicated)
         ptrs = (C.c_void_p * self.world)(*[p.data_ptr() for p in partials])
         stream = torch.cuda.current_stream(self.device).cuda_stream
         _lib.check(_lib.lib().dlm_reduce_bf16_loopback(ptrs, comms, self.world, stream), f"loopback reduce {site}")
         self._done(chain, outs)
         return outs
 
-    def rowpar(self, xs, ws, *, site, chain=0, hs=None, weight=None, eps=0.0, scale=1.0, splits=0, token_tiles=0):
+    def rowpar(self, xs, ws, *, site, chain=0, hs=None, weight=None, eps=0.0, scale=1.0, splits=0, token_tiles=0,
+               replicated=False):
         """All ranks of the fused projection + reduction in one launch: xs[r] [m, k_r], ws[r] [n, k_r]."""
         m, n = xs[0].shape[0], ws[0].shape[0]
-        comms, outs = self._comms(m, n, site, chain, hs, weight, eps, scale)
+        comms, outs = self._comms(m, n, site, chain, hs, weight, eps, scale, replicated)
         gemms = (DlmGemm * self.world)()
         for r, g in enumerate(self.groups):
             x, w = xs[r], ws[r]
@@ -137,10 +139,10 @@ class LoopbackWorld:
         _lib.check(_lib.lib().dlm_all_gather_loopback(ptrs, nbytes, comms, self.world, stream), f"loopback all_gather {key}")
         return outs
 
-    def moe(self, descriptors, *, site, chain=0, hs=None, weight=None, eps=0.0, scale=1.0):
+    def moe(self, descriptors, *, site, chain=0, hs=None, weight=None, eps=0.0, scale=1.0, replicated=False):
         """All ranks of the fused NVFP4 expert down-projection + reduction in one launch; descriptors[r] is rank r's
         DlmMoe (dlmrt_b200.quantization.nvfp4.descriptor)."""
-        comms, outs = self._comms(descriptors[0].m, descriptors[0].n, site, chain, hs, weight, eps, scale)
+        comms, outs = self._comms(descriptors[0].m, descriptors[0].n, site, chain, hs, weight, eps, scale, replicated)
         moes = (DlmMoe * self.world)(*descriptors)
         stream = torch.cuda.current_stream(self.device).cuda_stream
         _lib.check(_lib.lib().dlm_rowpar_nvfp4_moe_loopback(moes, comms, self.world, stream), f"loopback moe {site}")

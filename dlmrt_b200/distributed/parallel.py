@@ -181,7 +181,8 @@ class Group:
     def one_shot(self, rows, n, mode):
         """Whether a reduction runs as one NVLink hop (every rank receives every partial whole and sums all rows
         itself) instead of reduce-scatter + all-gather: plain sums whose incoming partials stay under
-        `one_shot_bytes` per rank (32-row blocks); residual modes keep their residual stream per owner and never do."""
+        `one_shot_bytes` per rank (32-row blocks). The residual modes keep their residual stream per owner and take
+        two hops, unless the caller says the stream is replicated (reduce_norm(..., replicated=True))."""
         return (self.world > 1 and mode == _lib.REDUCE
                 and (self.world - 1) * rows * n * 2 <= self.one_shot_bytes)
 
@@ -238,10 +239,11 @@ class Group:
         return ws
 
     # -- launches ---------------------------------------------------------------------------------------------------
-    def _comm(self, rows, n, site, chain, mode, h, weight, eps, scale):
+    def _comm(self, rows, n, site, chain, mode, h, weight, eps, scale, replicated=False):
         """The DlmComm of one call and its output buffer (the bookkeeping of parallel.py:119-132)."""
         out = self.symmetric(f"out:{site}", (rows, n), armed=True)
-        one_shot = self.one_shot(rows, n, mode)
+        # A replicated residual stream needs every row on every rank: always one hop, whatever the size.
+        one_shot = self.one_shot(rows, n, mode) or (replicated and self.world > 1)
         ptrs, epochs, recv_mc = self._receive(rows, n, chain, one_shot)
         last = self._last.get(chain)
         if last is out:  # same wording as parallel.py:124-125: callers may match on it
@@ -292,13 +294,13 @@ class Group:
         b1 = b0 + b.numel() * b.element_size()
         return a0 < b1 and b0 < a1
 
-    def _launch(self, mode, partial, h, weight, site, eps=0.0, scale=1.0, chain=0):
+    def _launch(self, mode, partial, h, weight, site, eps=0.0, scale=1.0, chain=0, replicated=False):
         if self._failed:
             raise RuntimeError("this group reported a device time-out: its buffers may hold stale arrivals; build a new "
                                "Group before reducing again")
         rows, n = partial.shape
         last = self._last.get(chain)
-        comm, out = self._comm(rows, n, site, chain, mode, h, weight, eps, scale)
+        comm, out = self._comm(rows, n, site, chain, mode, h, weight, eps, scale, replicated)
         stream = torch.cuda.current_stream(self.device).cuda_stream
         pending = self._pending.pop(partial.data_ptr(), None)
         # The fused kernel re-arms `last` and fills `out` while other CTAs still load the GEMM's input; an input that
@@ -323,20 +325,24 @@ class Group:
         self._last[chain] = out
         return out
 
-    def reduce_norm(self, partial, h, weight, eps, scale=1.0, *, site, chain=0):
+    def reduce_norm(self, partial, h, weight, eps, scale=1.0, *, site, chain=0, replicated=False):
         """All-reduce `partial`, then RMSNorm, in one launch; every rank gets the same [rows, n] result
-        (same arguments as parallel.py:134-143).
+        (same arguments as parallel.py:134-143, plus `replicated`).
 
         h given:  v = bf16(sum) + h; this rank's rows of `h` become bf16(v) (each rank keeps only its own rows of
                   the residual stream current); returns rmsnorm(v) * weight * scale.
         h None:   returns rmsnorm(bf16(sum)) * weight * scale.
+        replicated (with h): every rank holds the WHOLE residual stream and all its rows are updated on every rank:
+                  the pair `reduce` -> `rmsnorm(h, weight, delta=reduced)` of LLaDA2's layers
+                  (dlmrt/models/llada2/model.py:435-439, dlmrt/ops/triton/core.py:29-56) as one launch. Every rank then
+                  receives every partial whole and sums all rows itself (one NVLink hop).
 
         The returned tensor is the buffer of call site `site`; it stays valid until the NEXT call on `chain`, whose
         launch resets it. Calls on one chain must be stream-ordered; calls that can overlap in time (two streams)
         must use different chains.
         """
         mode = _lib.REDUCE_NORM_RESIDUAL if h is not None else _lib.REDUCE_NORM
-        return self._launch(mode, partial, h, weight, site, eps, scale, chain)
+        return self._launch(mode, partial, h, weight, site, eps, scale, chain, replicated and h is not None)
 
     def reduce(self, partial, *, site, chain=0):
         """All-reduce (sum) of `partial` into the buffer of call site `site`, identical bits on every rank

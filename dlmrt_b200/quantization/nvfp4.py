@@ -123,7 +123,7 @@ def descriptor(act_codes, act_scales, amap, counts, experts, ids, weights, buffe
 
 
 def moe_down(act_codes, act_scales, amap, counts, experts, ids, weights, buffers, out, num_experts, shared=None,
-             group=None, site=None, chain=0, h=None, norm_weight=None, eps=0.0, scale=1.0):
+             group=None, site=None, chain=0, h=None, norm_weight=None, eps=0.0, scale=1.0, replicated=False):
     """out = sum over each token's experts in this rank's [lo, lo + count) of weight * expert_down(activation)
     [+ shared], BF16; with `group`, the sum over ranks of that, in the call site's buffer (one fused launch).
 
@@ -133,14 +133,15 @@ def moe_down(act_codes, act_scales, amap, counts, experts, ids, weights, buffers
 
     With `group` and `norm_weight` the owner rows are also normalised before the all-gather, and with `h` added to the
     residual stream first, exactly as `Group.reduce_norm` does: the row kernel that follows the reduction in the
-    reference (`rmsnorm(h, weight, delta=reduced)`, dlmrt/ops/triton/core.py:29-56) folded into the same launch."""
+    reference (`rmsnorm(h, weight, delta=reduced)`, dlmrt/ops/triton/core.py:29-56) folded into the same launch.
+    `replicated`: every rank holds and updates the whole residual stream (LLaDA2), see `Group.reduce_norm`."""
     m = descriptor(act_codes, act_scales, amap, counts, experts, ids, weights, buffers, num_experts, shared)
     stream = torch.cuda.current_stream(act_codes.device).cuda_stream
     if group is None:
         _lib.check(_lib.lib().dlm_moe_nvfp4(C.byref(m), out.data_ptr(), out.stride(0), 1, stream), "moe_down")
         return out
     mode = _lib.REDUCE if norm_weight is None else _lib.REDUCE_NORM_RESIDUAL if h is not None else _lib.REDUCE_NORM
-    comm, reduced = group._comm(m.m, m.n, site, chain, mode, h, norm_weight, eps, scale)
+    comm, reduced = group._comm(m.m, m.n, site, chain, mode, h, norm_weight, eps, scale, replicated and h is not None)
     _lib.check(_lib.lib().dlm_rowpar_nvfp4_moe(C.byref(m), C.byref(comm), stream), f"moe_down {site}")
     group._last[chain] = reduced
     return reduced

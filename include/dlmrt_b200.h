@@ -100,10 +100,15 @@ typedef struct DlmComm {
     int32_t pdl;                   /* launch as a programmatic dependent launch (tp_comm.cu:304-309) */
     int32_t max_ctas;              /* cap on the grid, 0 = one CTA per SM. Calls that may run concurrently (different
                                       chains on different streams) must together fit on the GPU. */
-    int32_t one_shot;              /* 1 (mode DLM_REDUCE only): every rank stores its whole partial into every rank's
-                                      slots and sums all rows itself, in rank order, into its own `out`: one NVLink hop,
-                                      no broadcast; meant for small partials (32-row blocks). `recv` buffers are then
-                                      [3][world][rows][n]. Same bits as the two-hop protocol. Ignored when world == 1. */
+    int32_t one_shot;              /* 1: every rank stores its whole partial into every rank's slots and sums all rows
+                                      itself, in rank order, into its own `out`: one NVLink hop, no broadcast; meant
+                                      for small partials (32-row blocks). `recv` buffers are then [3][world][rows][n].
+                                      Same bits as the two-hop protocol. In mode DLM_REDUCE_NORM_RESIDUAL the residual
+                                      stream is then REPLICATED: every rank holds all rows of `h` and updates all of
+                                      them, which is how LLaDA2 keeps it (`rmsnorm(h, w, delta=reduced)`,
+                                      dlmrt/ops/triton/core.py:29-56, dlmrt/models/llada2/model.py:435-439); with
+                                      one_shot 0 only the owner's rows of `h` are read and written. With world == 1
+                                      the two are the same thing. */
     int32_t reserved;
     void* recv_mc;                 /* one_shot: NVLS multicast address of the receive buffer, or NULL (one store per rank) */
 } DlmComm;

@@ -327,3 +327,39 @@ def test_two_chains_resident_at_once_on_two_streams():
     alone = LoopbackWorld(world).rowpar(xs, ws, site="alone", chain=2)
     torch.cuda.synchronize()
     assert_same_bits(bits(results[-1][1][0]), bits(alone[0]), "dense sum: two streams vs alone")
+
+
+@pytest.mark.parametrize("world, rows", [(1, 32), (2, 32), (8, 32), (4, 64), (2, 256)])
+def test_replicated_residual_stream(world, rows):
+    """LLaDA2 keeps the whole residual stream on every rank and follows each plain sum with
+    `rmsnorm(h, weight, delta=reduced)` (dlmrt/models/llada2/model.py:435-439, dlmrt/ops/triton/core.py:29-56). Folded
+    into the reduction (`replicated=True`): every rank receives every partial, sums all rows itself and updates ALL
+    rows of its own copy of h. Stand-alone and behind the fused projection; h stays identical on every rank."""
+    from dlmrt_b200.distributed.loopback import LoopbackWorld
+
+    n, k = 2048, 512
+    lw = LoopbackWorld(world)
+    weight = randn_bf16(n, seed=5, std=0.1) + 1
+    h0 = randn_bf16(rows, n, seed=6)
+    hs = [h0.clone() for _ in range(world)]
+    h_want = bits(h0)
+    for i in range(4):
+        if i % 2 == 0:
+            partials = [randn_bf16(rows, n, seed=900 + 10 * i + r) for r in range(world)]
+            p_bits = np.stack([bits(p) for p in partials])
+            outs = lw.reduce(partials, site=f"rep{i % 2}", chain=rows, hs=hs, weight=weight, eps=1e-6, replicated=True)
+        else:
+            g = torch.Generator().manual_seed(i)
+            xs = [torch.randint(-3, 4, (rows, k), generator=g).to(torch.bfloat16).cuda() for _ in range(world)]
+            ws = [torch.randint(-2, 3, (n, k), generator=g).to(torch.bfloat16).cuda() for _ in range(world)]
+            p_bits = np.stack([bits((x.float() @ w.float().t()).to(torch.bfloat16)) for x, w in zip(xs, ws)])
+            outs = lw.rowpar(xs, ws, site=f"rep{i % 2}", chain=rows, hs=hs, weight=weight, eps=1e-6, replicated=True)
+        torch.cuda.synchronize()
+        lw.check()
+        summed = red.reduce(p_bits)
+        want, h_after = red.reduce_norm(summed[None], bits(weight), 1e-6, 1.0, h_want[None])
+        h_want = h_after[0]
+        for r in range(world):
+            assert_same_bits(bits(hs[r]), h_want, f"call {i}: residual stream of rank {r}")
+            assert_norm_close(bits(outs[r]), want, f"call {i}: rank {r}")
+            assert_same_bits(bits(outs[r]), bits(outs[0]), f"call {i}: rank {r} vs rank 0")
