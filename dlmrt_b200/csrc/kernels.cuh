@@ -8,6 +8,9 @@
 namespace dlm {
 
 constexpr int kFusedThreads = 384;  // 12 warps: TMA producer, MMA issuer, TMEM allocator, spare, 8 epilogue warps
+constexpr int kGemmRegs = 80;       // registers per thread of the GEMM kernel and of the tail kernel: 12 warps of the one
+constexpr int kTailRegs = 96;
+constexpr int kMoeRegs = 96;        // the expert GEMM kernel; its tail kernel compiles to 80 or fewer       // and 11 of the other (hidden <= 2816) must fit an SM's 64 K registers together
 constexpr int kBlockF = 128;        // weight rows (output features) per tile: the MMA's M
 constexpr int kBlockK = 64;         // BF16 per k-block: one 128-byte swizzled row
 constexpr int kUmmaK = 16;          // K of one tcgen05.mma kind::f16
@@ -110,9 +113,9 @@ int launch_reduce(const ReduceParams<1>& p, int grid, int threads, const LaunchO
 int launch_reduce_loopback(const ReduceParams<kMaxWorld>& p, int grid, int nranks, int threads, const LaunchOpts& o);
 int launch_gather(const ReduceParams<1>& p, int grid, const LaunchOpts& o);
 int launch_gather_loopback(const ReduceParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o);
-int launch_rowpar(const RowparParams<1>& p, int grid, const LaunchOpts& o);
-int launch_rowpar_loopback(const RowparParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o);
-int launch_moe(const MoeParams<1>& p, int grid, const LaunchOpts& o);
+int launch_rowpar(const RowparParams<1>& p, int grid, int tail_grid, const LaunchOpts& o);
+int launch_rowpar_loopback(const RowparParams<kMaxWorld>& p, int grid, int tail_grid, int nranks, const LaunchOpts& o);
+int launch_moe(const MoeParams<1>& p, int grid, int tail_grid, const LaunchOpts& o);
 int launch_moe_loopback(const MoeParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o);
 int launch_moe_gate_up(const MoeParams<1>& p, int grid, const LaunchOpts& o);
 int launch_moe_prepare(const PrepareDev& p, const LaunchOpts& o);

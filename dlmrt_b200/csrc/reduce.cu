@@ -18,6 +18,9 @@ __global__ void __launch_bounds__(MAXT, 1) reduce_kernel(const __grid_constant__
     const int slot = NR == 1 ? 0 : static_cast<int>(blockIdx.y);
     const CommDev& c = p.c[slot];
     __shared__ float scratch[64];
+    // The next kernel of the stream may start its prologue now (it waits for this one to complete before it reads
+    // anything this one writes); this kernel's blocks are small enough to share an SM with it.
+    pdl_launch_dependents();
     pdl_wait();
     const CommCtx x = comm_begin(c, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), c.epochs[blockIdx.x],
                                  comm_failed(c));
@@ -27,7 +30,6 @@ __global__ void __launch_bounds__(MAXT, 1) reduce_kernel(const __grid_constant__
     rearm_early(c, x);
     own_and_collect<(MAXT <= 512)>(c, x, scratch);  // re-arms late shares between its own and collect phases
     comm_end(c, x);
-    pdl_launch_dependents();
 }
 
 // All-gather of a small block of bytes (row statistics and the like) in the same barrier-free style: every rank stores
