@@ -712,7 +712,8 @@ def run_moe(args, rig, link_gbs, workload, routing, steps):
     layer_experts = []
     for _ in range(layers):
         s2 = torch.randint(0x28, 0x48, (e_local, hidden, f // 16), **u8)  # E4M3 scales between 0.25 and 4
-        layer_experts.append({"lo": lo, "w2": torch.randint(0, 256, (e_local, hidden, f // 2), **u8),
+        layer_experts.append({"lo": lo, "w2": nvfp4.tile_codes(torch.randint(0, 256, (e_local, hidden, f // 2), **u8)),
+                              "tiled": True, "n": hidden, "f": f,
                               "s2": nvfp4.interleave_scales(s2), "g2": torch.full((e_local,), 1e-4, device=device)})
     act_codes = torch.randint(0, 256, (e_local * rows, f // 2), **u8)
     act_scales = torch.randint(0x28, 0x48, (e_local * rows, f // 16), **u8)

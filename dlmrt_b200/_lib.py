@@ -39,7 +39,8 @@ class DlmMoe(C.Structure):
                 ("w_codes", C.c_void_p), ("w_scales", C.c_void_p), ("g2", C.c_void_p), ("ids", C.c_void_p),
                 ("weights", C.c_void_p), ("shared", C.c_void_p), ("m", C.c_int32), ("n", C.c_int32), ("f", C.c_int32),
                 ("top_k", C.c_int32), ("m_max", C.c_int32), ("lo", C.c_int32), ("e_local", C.c_int32),
-                ("e_total", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64)]
+                ("e_total", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
+                ("w_tiled", C.c_int32), ("reserved", C.c_int32)]
 
 
 class DlmMoeFront(C.Structure):
@@ -49,7 +50,7 @@ class DlmMoeFront(C.Structure):
                 ("slot_codes", C.c_void_p), ("slot_scales", C.c_void_p), ("act_codes", C.c_void_p),
                 ("act_scales", C.c_void_p), ("m", C.c_int32), ("hidden", C.c_int32), ("f", C.c_int32),
                 ("top_k", C.c_int32), ("m_max", C.c_int32), ("lo", C.c_int32), ("e_local", C.c_int32),
-                ("e_total", C.c_int32), ("activation", C.c_int32), ("reserved", C.c_int32)]
+                ("e_total", C.c_int32), ("activation", C.c_int32), ("w13_tiled", C.c_int32)]
 
 
 class DlmStatus(C.Structure):

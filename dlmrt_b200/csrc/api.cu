@@ -494,7 +494,7 @@ static int check_moe(const DlmMoe* m) {
     if (m->m < 1 || m->m > DLM_MAX_M || m->n < kBlockF || m->n % 256 || m->n > DLM_FUSED_MAX_N) return DLM_ERR_SHAPE;
     if (m->f < 64 || m->f % 64 || m->f > 4096 || m->top_k < 1 || m->top_k > 16) return DLM_ERR_SHAPE;
     if (m->m_max < 1 || m->m_max > 256 || m->e_local < 1 || m->e_local > 256) return DLM_ERR_SHAPE;
-    if (m->lo < 0 || m->lo + m->e_local > m->e_total) return DLM_ERR_SHAPE;
+    if (m->lo < 0 || m->lo + m->e_local > m->e_total || m->w_tiled < 0 || m->w_tiled > 1) return DLM_ERR_SHAPE;
     if (!aligned16(m->act_codes) || !aligned16(m->w_codes) || !aligned16(m->w_scales) || !aligned16(m->shared) ||
         (reinterpret_cast<uintptr_t>(m->act_scales) & 3) || (reinterpret_cast<uintptr_t>(m->workspace) & 255))
         return DLM_ERR_ALIGN;
@@ -521,7 +521,9 @@ static int make_map_u8(CUtensorMap* map, const void* base, long long rows, int r
 
 static int fill_moe(MoeDev* d, const DlmMoe* m) {
     std::memset(d, 0, sizeof(*d));
-    int rc = make_map_u8(&d->tm_w, m->w_codes, static_cast<long long>(m->e_local) * m->n, m->f / 2, kBlockF);
+    int rc = DLM_OK;
+    if (m->w_tiled) d->w_tiles = static_cast<const uint8_t*>(m->w_codes);
+    else rc = make_map_u8(&d->tm_w, m->w_codes, static_cast<long long>(m->e_local) * m->n, m->f / 2, kBlockF);
     if (rc == DLM_OK) rc = make_map_u8(&d->tm_a, m->act_codes, static_cast<long long>(m->e_local) * m->m_max, m->f / 2, 8);
     if (rc != DLM_OK) return rc;
     d->a_scales = static_cast<const uint8_t*>(m->act_scales);
@@ -591,7 +593,7 @@ static int check_front(const DlmMoeFront* a) {
     if (a->f < 64 || a->f % 64 || a->f > 4096 || a->top_k < 1 || a->top_k > 16) return DLM_ERR_SHAPE;
     if (a->m_max < 1 || a->m_max > 256 || a->e_local < 1 || a->e_local > 256 || a->activation < 0 || a->activation > 1)
         return DLM_ERR_SHAPE;
-    if (a->lo < 0 || a->lo + a->e_local > a->e_total) return DLM_ERR_SHAPE;
+    if (a->lo < 0 || a->lo + a->e_local > a->e_total || a->w13_tiled < 0 || a->w13_tiled > 1) return DLM_ERR_SHAPE;
     if (!aligned16(a->x) || !aligned16(a->xq) || !aligned16(a->xs) || !aligned16(a->w13_codes) ||
         !aligned16(a->w13_scales) || !aligned16(a->slot_codes) || !aligned16(a->slot_scales) ||
         !aligned16(a->act_codes) || (reinterpret_cast<uintptr_t>(a->act_scales) & 3))
@@ -621,7 +623,8 @@ int dlm_moe_front_nvfp4(const DlmMoeFront* a, int pdl, dlm_stream_t stream) {
     MoeParams<1> p;
     std::memset(&p, 0, sizeof(p));
     MoeDev* d = &p.g[0];
-    rc = make_map_u8(&d->tm_w, a->w13_codes, static_cast<long long>(a->e_local) * 2 * a->f, a->hidden / 2, kBlockF);
+    if (a->w13_tiled) d->w_tiles = static_cast<const uint8_t*>(a->w13_codes);
+    else rc = make_map_u8(&d->tm_w, a->w13_codes, static_cast<long long>(a->e_local) * 2 * a->f, a->hidden / 2, kBlockF);
     if (rc == DLM_OK)
         rc = make_map_u8(&d->tm_a, a->slot_codes, static_cast<long long>(a->e_local) * a->m_max, a->hidden / 2, 8);
     if (rc != DLM_OK) return rc;

@@ -111,6 +111,19 @@ int launch_gather_loopback(const ReduceParams<kMaxWorld>& p, int grid, int nrank
 
 template <int NR>
 static int launch_impl(const ReduceParams<NR>& p, dim3 grid, int threads, const LaunchOpts& o) {
+    // The same shared-memory / L1 split as the GEMM kernels of this library, so that this kernel's small blocks can
+    // share an SM with the GEMM launch that follows (an SM runs kernels of one split at a time).
+    static bool carved[64] = {};
+    int dev = 0;
+    (void)cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !carved[dev]) {
+        const bool a = cudaFuncSetAttribute(reduce_kernel<NR, 512>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                            cudaSharedmemCarveoutMaxShared) == cudaSuccess;
+        const bool b = cudaFuncSetAttribute(reduce_kernel<NR, 1024>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                            cudaSharedmemCarveoutMaxShared) == cudaSuccess;
+        carved[dev] = a && b;
+        (void)cudaGetLastError();
+    }
     cudaLaunchConfig_t config{};
     config.gridDim = grid;
     config.blockDim = dim3(static_cast<unsigned>(threads));

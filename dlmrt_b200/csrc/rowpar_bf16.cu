@@ -285,12 +285,16 @@ __global__ void __maxnreg__(kGemmRegs) rowpar_kernel(const __grid_constant__ Row
             tcgen05_fence_after();
         }
         if (c.stamps && threadIdx.x == 128) c.stamps[block * kStampSlots + 4] = globaltimer();
-        // One K split: the BF16 tile is staged in shared memory, token-major, over the drained pipeline stages.
-        // Several: this CTA's FP32 partial tile goes to the workspace (which the previous kernel of the chain may
-        // still be reading, hence the wait).
+        // One K split: the tile leaves in chunks of 16 tokens. The four warps that hold a chunk's 128 features round it to
+        // BF16 into shared memory (token-major, over the drained pipeline stages), meet on a barrier of their own and
+        // store or push its 16 rows while the other four warps are already loading the next chunk from tensor memory.
+        // Several: this CTA's FP32 partial tile goes to the workspace.
+        // Either way the destination may still be in use by the kernels in front of this one, hence the wait.
         float* part = g.ws + (static_cast<size_t>(tile) * g.splits + s) * mt * kBlockF;
         __nv_bfloat16* staged = reinterpret_cast<__nv_bfloat16*>(tiles);
-        if (g.splits > 1) pdl_wait();
+        pdl_wait();
+        CommCtx xe{};
+        if (p.fused && g.splits == 1) xe = comm_begin(c, block, blocks, c.epochs[block], comm_failed(c));
         for (int chunk = half; chunk < mt / 16; chunk += 2) {
             uint32_t r[16];
             if (iters > 0 && ok) {
@@ -316,6 +320,16 @@ __global__ void __maxnreg__(kGemmRegs) rowpar_kernel(const __grid_constant__ Row
 #pragma unroll
                 for (int j = 0; j < 16; ++j)
                     staged[(chunk * 16 + j) * kBlockF + feature] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+                const uint4* rows = reinterpret_cast<const uint4*>(staged + chunk * 16 * kBlockF);
+                for (int v = quarter * 32 + lane; v < 16 * (kBlockF / kVec); v += 128) {
+                    const int token = token0 + chunk * 16 + v / (kBlockF / kVec), col = f * kBlockF + v % (kBlockF / kVec) * kVec;
+                    if (p.fused) {
+                        push_store(c, xe, token, col, rows[v]);
+                    } else {
+                        store_v4(g.out + static_cast<size_t>(token) * g.ldo + col, rows[v]);
+                    }
+                }
             }
         }
         tcgen05_fence_before();
@@ -328,7 +342,7 @@ __global__ void __maxnreg__(kGemmRegs) rowpar_kernel(const __grid_constant__ Row
     }
 
     CommCtx x{};
-    if (p.fused) x = comm_begin(c, block, blocks, sm->epoch, sm->failed);
+    if (p.fused && g.splits > 1) x = comm_begin(c, block, blocks, sm->epoch, sm->failed);
     if (local_rows) {
         // The partial tile is in the workspace; the tail kernel reads it once this launch has completed.
     } else if (g.splits > 1) {
@@ -393,18 +407,6 @@ __global__ void __maxnreg__(kGemmRegs) rowpar_kernel(const __grid_constant__ Row
                 store_v4(g.out + static_cast<size_t>(token0 + token) * g.ldo + col, packed);
             }
         }
-    } else {
-        const uint4* staged = reinterpret_cast<const uint4*>(tiles);
-        for (int v = threadIdx.x; v < mt * (kBlockF / kVec); v += kFusedThreads) {
-            const int token = v / (kBlockF / kVec), j = v % (kBlockF / kVec);
-            const uint4 packed = staged[v];
-            const int col = f * kBlockF + j * kVec;
-            if (p.fused) {
-                push_store(c, x, token0 + token, col, packed);
-            } else {
-                store_v4(g.out + static_cast<size_t>(token0 + token) * g.ldo + col, packed);
-            }
-        }
     }
     if (p.fused) {
         if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 6] = globaltimer();
@@ -439,7 +441,7 @@ __global__ void __maxnreg__(kTailRegs) rowpar_tail_kernel(const __grid_constant_
         rearm(c, x, x.block, x.blocks);
     } else {
         rearm_early(c, x);
-        own_and_collect<false>(c, x, scratch);  // re-arms late shares between its own and collect phases
+        own_and_collect<true>(c, x, scratch);  // re-arms late shares between its own and collect phases
     }
     comm_end(c, x);
 }
@@ -457,6 +459,17 @@ int rowpar_smem_bytes(int m, int stages) {
 
 template <int NR>
 static int launch_tail(const RowparParams<NR>& p, dim3 grid, const LaunchOpts& o) {
+    // An SM runs kernels of one shared-memory / L1 split at a time. The GEMM kernels need the largest split, so the tail
+    // kernel asks for the same one although it uses next to no shared memory; otherwise it could not share an SM
+    // with them.
+    static bool carved[64] = {};
+    int dev = 0;
+    (void)cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !carved[dev]) {
+        carved[dev] = cudaFuncSetAttribute(rowpar_tail_kernel<NR>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                           cudaSharedmemCarveoutMaxShared) == cudaSuccess;
+        (void)cudaGetLastError();
+    }
     cudaLaunchConfig_t config{};
     config.gridDim = grid;
     config.blockDim = dim3(static_cast<unsigned>((p.c[0].n / kVec + 31) / 32 * 32));

@@ -284,7 +284,11 @@ __global__ void __maxnreg__(kMoeRegs) moe_kernel(const __grid_constant__ MoePara
                     }
                     uint8_t* stage = tiles + st * stage_bytes;
                     mbar_expect_tx(&sm->full[st], static_cast<uint32_t>(kCodeTileW + boxes * kBoxRows * 128));
-                    tma_load_2d(stage, &g.tm_w, &sm->full[st], kb * 128, t.e * g.n + t.ft * kBlockF, kEvictFirst);
+                    if (g.w_tiles)  // one contiguous 16 KB run of HBM, already in the swizzled shared-memory order
+                        bulk_load(stage, g.w_tiles + (static_cast<size_t>(t.e * feature_tiles + t.ft) * nkb + kb) * kCodeTileW,
+                                  kCodeTileW, &sm->full[st], kEvictFirst);
+                    else
+                        tma_load_2d(stage, &g.tm_w, &sm->full[st], kb * 128, t.e * g.n + t.ft * kBlockF, kEvictFirst);
                     for (int b = 0; b < boxes; ++b)
                         tma_load_2d(stage + off_a + b * kBoxRows * 128, &g.tm_a, &sm->full[st], kb * 128,
                                     t.e * g.m_max + t.row0 + b * kBoxRows, kEvictLast);
@@ -527,7 +531,7 @@ __global__ void __maxnreg__(kTailRegs) moe_tail_kernel(const __grid_constant__ M
             rearm(c, x, x.block, x.blocks);
         } else {
             rearm_early(c, x);
-            own_and_collect<false>(c, x, scratch);  // re-arms late shares between its own and collect phases
+            own_and_collect<true>(c, x, scratch);  // re-arms late shares between its own and collect phases
         }
         comm_end(c, x);
     }
@@ -535,6 +539,14 @@ __global__ void __maxnreg__(kTailRegs) moe_tail_kernel(const __grid_constant__ M
 
 template <int NR>
 static int launch_tail(const MoeParams<NR>& p, dim3 grid, const LaunchOpts& o) {
+    static bool carved[64] = {};  // the same shared-memory / L1 split as the GEMM kernels, so that they can share an SM
+    int dev = 0;
+    (void)cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !carved[dev]) {
+        carved[dev] = cudaFuncSetAttribute(moe_tail_kernel<NR>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                           cudaSharedmemCarveoutMaxShared) == cudaSuccess;
+        (void)cudaGetLastError();
+    }
     cudaLaunchConfig_t config{};
     config.gridDim = grid;
     config.blockDim = dim3(static_cast<unsigned>((p.g[0].n / kVec + 31) / 32 * 32));

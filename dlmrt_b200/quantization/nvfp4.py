@@ -49,6 +49,26 @@ def interleave_scales(scales):
     return s.contiguous().reshape(*lead, n // 128, groups // 4, 512)
 
 
+def tile_codes(codes):
+    """[..., n, k / 2] uint8 codes -> the streaming layout of the expert kernels: [..., n / 128, ceil(k / 256)] tiles of
+    128 rows x 128 bytes, each 16 KB tile contiguous and already in the 128-byte-swizzled order it has in shared memory
+    (16-byte chunk c of tile row r at chunk position c ^ (r % 8)); a last tile that k does not fill is zero-padded. One
+    bulk copy then brings a tile in, and an expert's slab is a contiguous run of HBM. Done once when the experts load."""
+    *lead, n, row_bytes = codes.shape
+    if n % 128 or row_bytes % 16:
+        raise ValueError(f"codes {tuple(codes.shape)}: rows must be a multiple of 128 and row bytes of 16")
+    if row_bytes % 128:
+        codes = torch.nn.functional.pad(codes, (0, 128 - row_bytes % 128))
+        row_bytes = codes.shape[-1]
+    d = len(lead)
+    t = codes.reshape(*lead, n // 128, 128, row_bytes // 128, 8, 16)
+    t = t.permute(*range(d), d, d + 2, d + 1, d + 3, d + 4)          # (.., tile row, tile col, r, chunk, 16 bytes)
+    r = torch.arange(128, device=codes.device).view(128, 1)
+    c = torch.arange(8, device=codes.device).view(1, 8)
+    src = (c ^ (r % 8)).view(*([1] * (d + 2)), 128, 8, 1).expand(*t.shape)   # position p holds chunk p ^ (r % 8)
+    return torch.gather(t, d + 3, src).contiguous()
+
+
 def interleave_gate_up(gate, up):
     """[..., F, X] gate and up rows -> [..., 2F, X] with row 2i = gate row i, row 2i + 1 = up row i: the order GEMM1's
     kernel wants, so that a gate value and its up value land in neighbouring lanes of the accumulator."""
@@ -72,8 +92,8 @@ def b200_experts(parts, layer, lo, count, device, group=None):
     w2 = torch.stack([get(e, "down", "weight") for e in experts]).contiguous()
     s2 = torch.stack([get(e, "down", "weight_scale").view(torch.uint8) for e in experts])
     a2, ws2 = scalars("down", "input_scale"), scalars("down", "weight_scale_2")
-    out = {"backend": "b200", "lo": lo, "w2": w2, "s2": interleave_scales(s2), "g2": (a2 * ws2).contiguous(),
-           "a2_inv": (1 / a2).contiguous(), "group": group}
+    out = {"backend": "b200", "lo": lo, "w2": tile_codes(w2), "s2": interleave_scales(s2), "g2": (a2 * ws2).contiguous(),
+           "a2_inv": (1 / a2).contiguous(), "group": group, "tiled": True, "n": w2.shape[1], "f": w2.shape[2] * 2}
     if (layer, lo, "gate", "weight") in parts:
         for e in experts:
             if not torch.equal(get(e, "gate", "weight_scale_2"), get(e, "up", "weight_scale_2")):
@@ -85,8 +105,8 @@ def b200_experts(parts, layer, lo, count, device, group=None):
                                  torch.stack([get(e, "up", "weight") for e in experts]))
         s13 = interleave_gate_up(torch.stack([get(e, "gate", "weight_scale").view(torch.uint8) for e in experts]),
                                  torch.stack([get(e, "up", "weight_scale").view(torch.uint8) for e in experts]))
-        out.update(w13=w13, s13=interleave_scales(s13), g1=(a1 * scalars("gate", "weight_scale_2")).contiguous(),
-                   a1_inv=(1 / a1[:1]).contiguous())
+        out.update(w13=tile_codes(w13), s13=interleave_scales(s13), hidden=w13.shape[2] * 2,
+                   g1=(a1 * scalars("gate", "weight_scale_2")).contiguous(), a1_inv=(1 / a1[:1]).contiguous())
     return out
 
 
@@ -103,8 +123,12 @@ class Buffers:
 def descriptor(act_codes, act_scales, amap, counts, experts, ids, weights, buffers, num_experts, shared=None):
     """The DlmMoe of one call. Keeps nothing alive: the caller owns every tensor."""
     rows, top_k = ids.shape
-    n, half_f = experts["w2"].shape[1], experts["w2"].shape[2]
+    if experts.get("tiled"):
+        n, half_f = experts["n"], experts["f"] // 2
+    else:
+        n, half_f = experts["w2"].shape[1], experts["w2"].shape[2]
     m = DlmMoe()
+    m.w_tiled = int(bool(experts.get("tiled")))
     m.act_codes, m.act_scales = act_codes.data_ptr(), act_scales.data_ptr()
     m.amap, m.counts = amap.data_ptr(), counts.data_ptr()
     m.w_codes, m.w_scales, m.g2 = experts["w2"].data_ptr(), experts["s2"].data_ptr(), experts["g2"].data_ptr()
@@ -194,8 +218,9 @@ def trtllm_moe(x, packed, experts, out, num_experts, lo, intermediate, quantized
     count, top_k = experts["w2"].shape[0], packed.shape[1]
     if experts["lo"] != lo or "w13" not in experts:
         raise ValueError("experts were laid out for another rank, or without their gate / up weights (b200_experts)")
-    if experts["w13"].shape[1] != 2 * intermediate or experts["w13"].shape[2] * 2 != hidden:
-        raise ValueError(f"experts are {tuple(experts['w13'].shape)}; the call says hidden {hidden}, intermediate {intermediate}")
+    if experts["f"] != intermediate or experts["hidden"] != hidden:
+        raise ValueError(f"experts are hidden {experts['hidden']}, intermediate {experts['f']}; the call says {hidden}, "
+                         f"{intermediate}")
     cache = experts.setdefault("_buffers", {})
     if rows not in cache:  # first call with this row count: before any graph capture, as the reference tunes
         cache[rows] = FrontBuffers(rows, hidden, intermediate, count, num_experts, top_k, device)
@@ -213,6 +238,7 @@ def trtllm_moe(x, packed, experts, out, num_experts, lo, intermediate, quantized
     f.act_codes, f.act_scales = b.act_codes.data_ptr(), b.act_scales.data_ptr()
     f.m, f.hidden, f.f, f.top_k, f.m_max = rows, hidden, intermediate, top_k, rows
     f.lo, f.e_local, f.e_total, f.activation = lo, count, num_experts, ACTIVATIONS[activation]
+    f.w13_tiled = 1
     if packed.dtype != torch.int32 or not packed.is_contiguous():
         raise ValueError("packed must be a contiguous int32 [rows, top_k] tensor")
     stream = torch.cuda.current_stream(device).cuda_stream

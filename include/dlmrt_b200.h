@@ -158,6 +158,11 @@ typedef struct DlmMoe {
     int32_t lo, e_local, e_total; /* this rank's experts are [lo, lo + e_local), e_local <= 256 */
     void* workspace;         /* dlm_moe_workspace_bytes(m, n, top_k) bytes, zero-initialised once, 256-byte aligned */
     int64_t workspace_bytes;
+    int32_t w_tiled;         /* 0: w_codes is [e_local, n, f / 2] as exported. 1: pre-tiled for streaming,
+                                [e_local][n / 128][ceil(f / 256)] tiles of 128 rows x 128 bytes (16 KB, contiguous, zero-padded
+                                along f), the 16-byte chunk c of tile row r stored at chunk position c ^ (r % 8) (the
+                                128-byte shared-memory swizzle): one bulk copy brings a tile in */
+    int32_t reserved;
 } DlmMoe;
 
 /* What runs in front of the expert down-projection inside the reference's one FlashInfer call
@@ -176,7 +181,8 @@ typedef struct DlmMoeFront {
     const void* xs;           /* [m, hidden / 16] E4M3 scales, linear (x NULL) */
     const float* a1_inv;      /* device scalar: 1 / (GEMM1 input scale), the global scale of the input's rounding */
     const int32_t* packed;    /* [m, top_k] expert << 16 | BF16 routing-weight bits, ascending experts per token */
-    const void* w13_codes;    /* [e_local, 2F, hidden / 2] uint8, rows interleaved gate / up */
+    const void* w13_codes;    /* [e_local, 2F, hidden / 2] uint8, rows interleaved gate / up; or, with w13_tiled, the same
+                                 pre-tiled like DlmMoe.w_codes: [e_local][2F / 128][ceil(hidden / 256)][16 KB] */
     const void* w13_scales;   /* [e_local, 2F / 128, hidden / 64, 512] E4M3 atoms */
     const float* g1;          /* [e_local] GEMM1 alpha = input scale x weight scale */
     const float* a2_inv;      /* [e_local] 1 / (GEMM2 input scale) */
@@ -192,7 +198,7 @@ typedef struct DlmMoeFront {
     int32_t m_max;            /* rows reserved per expert (<= 256); rows beyond it are dropped */
     int32_t lo, e_local, e_total;
     int32_t activation;       /* 0 SwiGLU (g * sigmoid(g) * u), 1 GeGLU (tanh GELU) */
-    int32_t reserved;
+    int32_t w13_tiled;        /* see w13_codes */
 } DlmMoeFront;
 
 /* Device status read back by dlm_status_read(). */
