@@ -92,8 +92,19 @@ def test_front_half_matches_the_oracle(prefix):
     used = np.concatenate([np.arange(e * rows, e * rows + counts[e]) for e in range(e_total)])
     tokens = np.concatenate([amap[e, :counts[e]] // k for e in range(e_total)])
     codes_close(slot_codes[used], slot_scales[used], xq[tokens], xs[tokens], "quantised input rows")
-    codes_close(b.act_codes.cpu().numpy()[used], b.act_scales.cpu().numpy()[used], act_codes[used], act_scales[used],
-                "re-quantised activations")
+    # GEMM1 + activation + re-quantisation, fed with the very rows the GPU quantised (so that a flipped input code
+    # does not count against it).
+    a13, a2 = G[f"{prefix}_gate_input_scale"], G[f"{prefix}_down_input_scale"]
+    g1 = (a13 * G[f"{prefix}_gate_scale2"]).astype(np.float32)
+    got_codes, got_scales = b.act_codes.cpu().numpy(), b.act_scales.cpu().numpy()
+    want_codes, want_scales = np.zeros_like(got_codes), np.zeros_like(got_scales)
+    for e in range(e_total):
+        if counts[e]:
+            sl = slice(e * rows, e * rows + counts[e])
+            want_codes[sl], want_scales[sl], _ = onv.expert_gate_up(
+                slot_codes[sl], slot_scales[sl], G[f"{prefix}_gate_packed"][e], G[f"{prefix}_gate_scale"][e],
+                G[f"{prefix}_up_packed"][e], G[f"{prefix}_up_scale"][e], g1[e], np.float32(1) / a2[e], prefix)
+    codes_close(got_codes[used], got_scales[used], want_codes[used], want_scales[used], "re-quantised activations")
 
 
 @pytest.mark.parametrize("prefix", ["swiglu", "geglu"])
