@@ -48,17 +48,19 @@ def oracle_front(prefix, lo=0, count=None, quantized=None):
                          (np.float32(1) / a2).astype(np.float32)[sl], lo, prefix, quantized=quantized)
 
 
-def codes_close(got_codes, got_scales, want_codes, want_scales, what):
-    """The GPU's approximate reciprocals and exponentials against the oracle's exact ones: a value within an ulp of a
-    rounding boundary may come out one code apart, and a block maximum on a boundary may move the block's scale."""
+def codes_close(got_codes, got_scales, want_codes, want_scales, what, fraction=1e-2):
+    """The GPU's approximate reciprocals and exponentials (and, behind GEMM1, the FP4 tensor cores' own summation of
+    each 64-element group) against the oracle's exact float64 dots: a value near a rounding boundary may come out one
+    code apart, and a block maximum near a boundary may move the block's scale by one E4M3 step. Never more than one
+    step, and only on a small `fraction` of the blocks / codes."""
     scale_diff = (got_scales != want_scales).mean()
-    assert scale_diff <= 1e-2, f"{what}: {scale_diff:.4%} of the block scales differ"
+    assert scale_diff <= fraction, f"{what}: {scale_diff:.4%} of the block scales differ"
     step = np.abs(got_scales.astype(np.int32) - want_scales.astype(np.int32))
     assert step.max(initial=0) <= 1, f"{what}: a block scale is off by more than one E4M3 step"
     g, w = onv.unpack_codes(got_codes).astype(np.int32), onv.unpack_codes(want_codes).astype(np.int32)
     same_scale = np.repeat(got_scales == want_scales, 16, axis=-1)
     differ = (g != w) & same_scale
-    assert differ.mean() <= 1e-2, f"{what}: {differ.mean():.4%} of the codes differ"
+    assert differ.mean() <= fraction, f"{what}: {differ.mean():.4%} of the codes differ"
     mag = np.abs((g & 7) - (w & 7))
     assert mag[differ].max(initial=0) <= 1, f"{what}: a code is off by more than one step"
 
@@ -104,7 +106,7 @@ def test_front_half_matches_the_oracle(prefix):
             want_codes[sl], want_scales[sl], _ = onv.expert_gate_up(
                 slot_codes[sl], slot_scales[sl], G[f"{prefix}_gate_packed"][e], G[f"{prefix}_gate_scale"][e],
                 G[f"{prefix}_up_packed"][e], G[f"{prefix}_up_scale"][e], g1[e], np.float32(1) / a2[e], prefix)
-    codes_close(got_codes[used], got_scales[used], want_codes[used], want_scales[used], "re-quantised activations")
+    codes_close(got_codes[used], got_scales[used], want_codes[used], want_scales[used], "re-quantised activations", 5e-2)
 
 
 @pytest.mark.parametrize("prefix", ["swiglu", "geglu"])
