@@ -8,9 +8,13 @@
 namespace dlm {
 
 constexpr int kFusedThreads = 384;  // 12 warps: TMA producer, MMA issuer, TMEM allocator, spare, 8 epilogue warps
-constexpr int kGemmRegs = 80;       // registers per thread of the GEMM kernel and of the tail kernel: 12 warps of the one
+// Registers per thread of the GEMM kernels and of their tail kernels. A GEMM block and a tail block must fit an SM
+// together, and the register file is split over the SM's four sub-cores (16 K registers each) with a block's warps dealt
+// round-robin: three warps of the one (12 warps) and three of the other (up to 12) land on a sub-core,
+// 3 * 32 * (72 + 96) = 16128 <= 16384. (With 80 + 96 the blocks never shared an SM although 64 K registers would do.)
+constexpr int kGemmRegs = 72;
 constexpr int kTailRegs = 96;
-constexpr int kMoeRegs = 96;        // the expert GEMM kernel; its tail kernel compiles to 80 or fewer       // and 11 of the other (hidden <= 2816) must fit an SM's 64 K registers together
+constexpr int kMoeRegs = 72;        // the expert GEMM kernel (it needs fewer)
 constexpr int kBlockF = 128;        // weight rows (output features) per tile: the MMA's M
 constexpr int kBlockK = 64;         // BF16 per k-block: one 128-byte swizzled row
 constexpr int kUmmaK = 16;          // K of one tcgen05.mma kind::f16

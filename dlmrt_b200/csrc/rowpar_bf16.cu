@@ -166,6 +166,7 @@ __global__ void __maxnreg__(kGemmRegs) rowpar_kernel(const __grid_constant__ Row
     // the value is the same, bit for bit, as pushing and summing one rank.
     const bool local_rows = p.fused && c.world == 1 && g.splits > 1;
 
+    const int pre = iters < g.stages ? iters : g.stages;
     if (threadIdx.x == 0) {
         for (int i = 0; i < g.stages; ++i) {
             mbar_init(&sm->full[i], 1);
@@ -173,7 +174,26 @@ __global__ void __maxnreg__(kGemmRegs) rowpar_kernel(const __grid_constant__ Row
         }
         mbar_init(&sm->acc_full, static_cast<uint32_t>(issuers));
         fence_barrier_init();
-        if (!g.w_tiles) tma_prefetch_descriptor(&g.tm_w);
+        // The first ring-full of weights is requested at once, by the thread that has just set the barriers up: weights
+        // depend on nothing, neither on the kernels in front of this one nor on the rest of this block's set-up.
+        for (int it = 0; it < pre; ++it) {
+            mbar_expect_tx(&sm->full[it], static_cast<uint32_t>(stage_bytes));
+            if (g.w_tiles)
+                bulk_load(tiles + it * stage_bytes, g.w_tiles + (static_cast<size_t>(f) * nkb + kb0 + it) * kTileBytesW,
+                          kTileBytesW, &sm->full[it], kEvictFirst);
+            else
+                tma_load_2d(tiles + it * stage_bytes, &g.tm_w, &sm->full[it], (kb0 + it) * kBlockK, f * kBlockF, kEvictFirst);
+        }
+        // The rest of this CTA's weight slab is pulled into L2 now, while the previous kernel of the stream is still
+        // finishing: the ring then refills at L2 latency instead of HBM latency.
+        if (iters > pre && prefetch_rest_of_slab(mt)) {
+            if (g.w_tiles) {
+                bulk_prefetch_l2(g.w_tiles + (static_cast<size_t>(f) * nkb + kb0 + pre) * kTileBytesW,
+                                 static_cast<uint32_t>(iters - pre) * kTileBytesW);
+            } else {
+                for (int it = pre; it < iters; ++it) tma_prefetch_l2_2d(&g.tm_w, (kb0 + it) * kBlockK, f * kBlockF);
+            }
+        }
         tma_prefetch_descriptor(&g.tm_x);
     }
     if (warp == 2) tmem_alloc(&sm->tmem_base, cols * issuers);
@@ -188,26 +208,6 @@ __global__ void __maxnreg__(kGemmRegs) rowpar_kernel(const __grid_constant__ Row
 
     if (warp == 0) {
         if (lane == 0) {
-            const int pre = iters < g.stages ? iters : g.stages;
-            for (int it = 0; it < pre; ++it) {
-                mbar_expect_tx(&sm->full[it], static_cast<uint32_t>(stage_bytes));
-                if (g.w_tiles)
-                    bulk_load(tiles + it * stage_bytes, g.w_tiles + (static_cast<size_t>(f) * nkb + kb0 + it) * kTileBytesW,
-                              kTileBytesW, &sm->full[it], kEvictFirst);
-                else
-                    tma_load_2d(tiles + it * stage_bytes, &g.tm_w, &sm->full[it], (kb0 + it) * kBlockK, f * kBlockF,
-                                kEvictFirst);
-            }
-            // The rest of this CTA's weight slab is pulled into L2 now, while the previous kernel of the stream is still
-            // finishing: weights never depend on it, and the ring then refills at L2 latency instead of HBM latency.
-            if (iters > pre && prefetch_rest_of_slab(mt)) {
-                if (g.w_tiles) {
-                    bulk_prefetch_l2(g.w_tiles + (static_cast<size_t>(f) * nkb + kb0 + pre) * kTileBytesW,
-                                     static_cast<uint32_t>(iters - pre) * kTileBytesW);
-                } else {
-                    for (int it = pre; it < iters; ++it) tma_prefetch_l2_2d(&g.tm_w, (kb0 + it) * kBlockK, f * kBlockF);
-                }
-            }
             pdl_wait();
             if (c.stamps) c.stamps[block * kStampSlots + 5] = globaltimer();
             for (int it = 0; it < pre; ++it)
