@@ -417,15 +417,15 @@ def run_dense(args, rig, link_gbs):
     return line
 
 
-STAMP_NAMES = {7: "gemm kernel entry", 5: "gemm dependency released", 4: "accumulator ready", 6: "tile pushed",
-               1: "tail kernel entry", 0: "tail dependency released", 2: "owned rows broadcast", 3: "collected"}
+STAMP_NAMES = {7: "kernel entry", 5: "dependency released", 4: "accumulator ready", 0: "mainloop drained, comm begins",
+               6: "tile summed and pushed", 2: "owned rows broadcast", 3: "collected"}
 
 
 def timeline(rig, step, group, layers=(3, 4)):
     """Phase stamps (%globaltimer, written by thread 0 of every CTA when the caller passes a stamp buffer) of the two
-    fused calls (GEMM + push kernel, then the reduction's tail kernel) of a few layers inside a graph replay: per phase
-    the median and maximum over CTAs, in microseconds after the call's first GEMM CTA entered; `next_entry` is when the
-    first GEMM CTA of the following call entered. Plain run, no profiler."""
+    fused launches of a few layers inside a graph replay: per phase the median and maximum over CTAs, in microseconds
+    after the launch's first CTA entered; `next_entry` is when the first CTA of the following launch entered. Plain
+    run, no profiler."""
     import numpy as np
 
     torch = rig.torch
@@ -464,7 +464,7 @@ def timeline(rig, step, group, layers=(3, 4)):
         s = bufs[key].cpu().numpy().reshape(sms, 8)
         t0 = int(s[:, 7][s[:, 7] > 0].min())
         entries[key] = t0
-        phases = {"gemm_ctas": int((s[:, 7] > 0).sum()), "tail_ctas": int((s[:, 1] > 0).sum())}
+        phases = {"ctas": int((s[:, 7] > 0).sum())}
         for slot, name in STAMP_NAMES.items():
             v = s[:, slot]
             v = v[v > 0] - t0

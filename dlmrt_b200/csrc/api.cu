@@ -369,7 +369,7 @@ int dlm_gemm_bf16(const DlmGemm* gemm, void* out, int64_t ldo, int pdl, dlm_stre
     p.g[0].out = static_cast<__nv_bfloat16*>(out);
     p.g[0].ldo = ldo;
     p.fused = 0;
-    return launch_rowpar(p, grid, 0, {static_cast<cudaStream_t>(stream), pdl != 0, false});
+    return launch_rowpar(p, grid, {static_cast<cudaStream_t>(stream), pdl != 0, false});
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -445,7 +445,7 @@ int dlm_gemm_bf16_noalloc(const void* x, const void* w, void* out, int m, int n,
     // generation and arrival counters); the partial tiles are fully rewritten before they are read.
     const cudaError_t err = cudaMemsetAsync(scratch, 0, kWorkspaceHeader, s);
     if (err != cudaSuccess) return cuda_fail(err);
-    return launch_rowpar(p, grid, 0, {s, pdl != 0, false});
+    return launch_rowpar(p, grid, {s, pdl != 0, false});
 }
 
 static bool overlaps(const void* a, size_t a_bytes, const void* b, size_t b_bytes) {
@@ -458,12 +458,13 @@ static int check_pair(const DlmGemm* gemm, const DlmComm* comm) {
     if (rc == DLM_OK) rc = check_comm(comm);
     if (rc != DLM_OK) return rc;
     if (gemm->m != comm->rows || gemm->n != comm->n || comm->n > DLM_FUSED_MAX_N) return DLM_ERR_SHAPE;
-    // Other ranks broadcast finished rows into `out` while this rank's GEMM may still be loading x: the input must not
-    // be the output. (It MAY be `rearm`, the chain's previous output: that is re-armed by the tail launch, which starts
-    // only when the GEMM launch has completed.)
+    // The fused kernel re-arms `rearm` and fills `out` while other CTAs may still be loading x: the GEMM's input must
+    // be neither (in the reference the GEMM is an earlier kernel, so there the aliasing is harmless).
     const size_t x_bytes = (static_cast<size_t>(gemm->m - 1) * gemm->ldx + gemm->k) * 2;
     const size_t out_bytes = static_cast<size_t>(comm->rows) * comm->n * 2;
-    if (overlaps(gemm->x, x_bytes, comm->out, out_bytes)) return DLM_ERR_OVERLAP;
+    if (overlaps(gemm->x, x_bytes, comm->rearm, static_cast<size_t>(comm->rearm_bytes)) ||
+        overlaps(gemm->x, x_bytes, comm->out, out_bytes))
+        return DLM_ERR_OVERLAP;
     return DLM_OK;
 }
 
@@ -480,10 +481,7 @@ int dlm_rowpar_bf16(const DlmGemm* gemm, const DlmComm* comm, dlm_stream_t strea
     if (rc != DLM_OK) return rc;
     fill_comm(&p.c[0], comm);
     p.fused = 1;
-    // The reduction half runs as a launch of its own behind the GEMM (see rowpar_bf16.cu), on up to one CTA per SM.
-    int tail_grid = comm->max_ctas > 0 && comm->max_ctas < info.sms ? comm->max_ctas : info.sms;
-    if (tail_grid > DLM_EPOCH_SLOTS) tail_grid = DLM_EPOCH_SLOTS;
-    return launch_rowpar(p, grid, tail_grid, {static_cast<cudaStream_t>(stream), comm->pdl != 0, false});
+    return launch_rowpar(p, grid, {static_cast<cudaStream_t>(stream), comm->pdl != 0, false});
 }
 
 static int check_moe(const DlmMoe* m) {
@@ -561,7 +559,7 @@ int dlm_moe_nvfp4(const DlmMoe* moe, void* out, int64_t ldo, int pdl, dlm_stream
     p.g[0].out = static_cast<__nv_bfloat16*>(out);
     p.g[0].ldo = ldo;
     p.fused = 0;
-    return launch_moe(p, info.sms, info.sms, {static_cast<cudaStream_t>(stream), pdl != 0, false});
+    return launch_moe(p, info.sms, {static_cast<cudaStream_t>(stream), pdl != 0, false});
 }
 
 int dlm_rowpar_nvfp4_moe(const DlmMoe* moe, const DlmComm* comm, dlm_stream_t stream) {
@@ -579,7 +577,7 @@ int dlm_rowpar_nvfp4_moe(const DlmMoe* moe, const DlmComm* comm, dlm_stream_t st
     fill_comm(&p.c[0], comm);
     p.fused = 1;
     const int grid = comm->max_ctas > 0 && comm->max_ctas < info.sms ? comm->max_ctas : info.sms;
-    return launch_moe(p, grid, grid, {static_cast<cudaStream_t>(stream), comm->pdl != 0, false});
+    return launch_moe(p, grid, {static_cast<cudaStream_t>(stream), comm->pdl != 0, false});
 }
 
 static int check_front(const DlmMoeFront* a) {
@@ -710,8 +708,7 @@ int dlm_rowpar_bf16_loopback(const DlmGemm* gemm, const DlmComm* comm, int nrank
         fill_comm(&p.c[i], &comm[i]);
     }
     p.fused = 1;
-    int tail_grid = comm[0].max_ctas > 0 && comm[0].max_ctas < per_rank ? comm[0].max_ctas : per_rank;
-    return launch_rowpar_loopback(p, grid, tail_grid, nranks, {static_cast<cudaStream_t>(stream), false, true});
+    return launch_rowpar_loopback(p, grid, nranks, {static_cast<cudaStream_t>(stream), false, true});
 }
 
 size_t dlm_workspace_bytes(int m, int n, int k) {
@@ -767,7 +764,7 @@ const char* dlm_strerror(int code) {
         case DLM_ERR_WORKSPACE: return "workspace too small (dlm_workspace_bytes)";
         case DLM_ERR_TIMEOUT: return "device wait ran out: data from a rank never arrived";
         case DLM_ERR_ARCH: return "not an sm_100 device";
-        case DLM_ERR_OVERLAP: return "the fused GEMM's input overlaps the call's output buffer";
+        case DLM_ERR_OVERLAP: return "the fused GEMM's input overlaps a buffer the same launch re-arms or writes (rearm, out)";
         case DLM_ERR_SCRATCH: return "requested K splits need more than the library's built-in scratch (DLM_NOALLOC_SCRATCH_BYTES)";
         default: return "unknown error";
     }

@@ -8,13 +8,6 @@
 namespace dlm {
 
 constexpr int kFusedThreads = 384;  // 12 warps: TMA producer, MMA issuer, TMEM allocator, spare, 8 epilogue warps
-// Registers per thread of the GEMM kernels and of their tail kernels. A GEMM block and a tail block must fit an SM
-// together, and the register file is split over the SM's four sub-cores (16 K registers each) with a block's warps dealt
-// round-robin: three warps of the one (12 warps) and three of the other (up to 12) land on a sub-core,
-// 3 * 32 * (72 + 96) = 16128 <= 16384. (With 80 + 96 the blocks never shared an SM although 64 K registers would do.)
-constexpr int kGemmRegs = 72;
-constexpr int kTailRegs = 96;
-constexpr int kMoeRegs = 72;        // the expert GEMM kernel (it needs fewer)
 constexpr int kBlockF = 128;        // weight rows (output features) per tile: the MMA's M
 constexpr int kBlockK = 64;         // BF16 per k-block: one 128-byte swizzled row
 constexpr int kUmmaK = 16;          // K of one tcgen05.mma kind::f16
@@ -119,9 +112,9 @@ int launch_reduce(const ReduceParams<1>& p, int grid, int threads, const LaunchO
 int launch_reduce_loopback(const ReduceParams<kMaxWorld>& p, int grid, int nranks, int threads, const LaunchOpts& o);
 int launch_gather(const ReduceParams<1>& p, int grid, const LaunchOpts& o);
 int launch_gather_loopback(const ReduceParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o);
-int launch_rowpar(const RowparParams<1>& p, int grid, int tail_grid, const LaunchOpts& o);
-int launch_rowpar_loopback(const RowparParams<kMaxWorld>& p, int grid, int tail_grid, int nranks, const LaunchOpts& o);
-int launch_moe(const MoeParams<1>& p, int grid, int tail_grid, const LaunchOpts& o);
+int launch_rowpar(const RowparParams<1>& p, int grid, const LaunchOpts& o);
+int launch_rowpar_loopback(const RowparParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o);
+int launch_moe(const MoeParams<1>& p, int grid, const LaunchOpts& o);
 int launch_moe_loopback(const MoeParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o);
 int launch_moe_gate_up(const MoeParams<1>& p, int grid, const LaunchOpts& o);
 int launch_moe_prepare(const PrepareDev& p, const LaunchOpts& o);

@@ -18,9 +18,7 @@ __global__ void __launch_bounds__(MAXT, 1) reduce_kernel(const __grid_constant__
     const int slot = NR == 1 ? 0 : static_cast<int>(blockIdx.y);
     const CommDev& c = p.c[slot];
     __shared__ float scratch[64];
-    // The next kernel of the stream may start its prologue now (it waits for this one to complete before it reads
-    // anything this one writes); this kernel's blocks are small enough to share an SM with it.
-    pdl_launch_dependents();
+    pdl_launch_dependents();  // the next kernel may be set up while this one runs; it waits before it reads our output
     pdl_wait();
     const CommCtx x = comm_begin(c, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x), c.epochs[blockIdx.x],
                                  comm_failed(c));
@@ -111,19 +109,6 @@ int launch_gather_loopback(const ReduceParams<kMaxWorld>& p, int grid, int nrank
 
 template <int NR>
 static int launch_impl(const ReduceParams<NR>& p, dim3 grid, int threads, const LaunchOpts& o) {
-    // The same shared-memory / L1 split as the GEMM kernels of this library, so that this kernel's small blocks can
-    // share an SM with the GEMM launch that follows (an SM runs kernels of one split at a time).
-    static bool carved[64] = {};
-    int dev = 0;
-    (void)cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !carved[dev]) {
-        const bool a = cudaFuncSetAttribute(reduce_kernel<NR, 512>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                            cudaSharedmemCarveoutMaxShared) == cudaSuccess;
-        const bool b = cudaFuncSetAttribute(reduce_kernel<NR, 1024>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                            cudaSharedmemCarveoutMaxShared) == cudaSuccess;
-        carved[dev] = a && b;
-        (void)cudaGetLastError();
-    }
     cudaLaunchConfig_t config{};
     config.gridDim = grid;
     config.blockDim = dim3(static_cast<unsigned>(threads));

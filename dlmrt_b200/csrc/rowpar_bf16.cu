@@ -18,19 +18,8 @@
 //   staged in shared memory and goes straight out. With several, every CTA writes its FP32 partial tile to the
 //   workspace, the CTAs of a tile meet on an arrival counter, and each then sums its share of the tile's tokens over
 //   the splits in split order (the value never depends on timing). Either way each token row's 256 bytes are stored
-//   (plain GEMM) or pushed straight into the owner rank's receive slot over NVLink.
-//
-// A fused call is TWO launches chained by programmatic dependent launch:
-//   rowpar_kernel       the GEMM and the push, above. It waits for nothing another rank does and exits as soon as
-//                       its tile is out.
-//   rowpar_tail_kernel  re-arm / own / collect (comm.cuh): small blocks of hidden / 8 threads, a few hundred bytes of
-//                       shared memory and at most 80 registers per thread, so that it fits on an SM BESIDE a GEMM CTA.
-// That is what the split is for. A kernel whose CTAs fill an SM (a 200 KB ring) keeps its successor out until it
-// exits, and the successor's launch latency, prologue and first weight loads (about 4 us here) then sit on the
-// critical path of every projection. Split this way, the tail of call n is launched while GEMM n still runs (the GEMM
-// signals its dependents at once), and GEMM n + 1 moves into the SMs GEMM n has left while tail n is still waiting
-// for the other ranks: it initialises its barriers, allocates tensor memory and fills its whole ring with weights,
-// which depend on nothing, and only then waits for tail n to complete before it loads x.
+//   (plain GEMM) or pushed straight into the owner rank's receive slot over NVLink, and every CTA goes on to the
+//   re-arm / own / collect phases of the reduction (comm.cuh).
 #include "kernels.cuh"
 
 namespace dlm {
@@ -56,29 +45,33 @@ __device__ __forceinline__ uint32_t tmem_cols(int m) {
 
 }  // namespace
 
-// Owner phase of a single rank whose K was split: CTA `block` owns rows block, block + blocks, ... For each it sums the
-// row's FP32 split partials in split order, rounds to BF16 (that is the rank's partial, as the push path would have
-// stored it) and finishes the row as any owner does. The GEMM launch that wrote the partial tiles has completed when
-// this runs (the tail kernel waits for it), so there is nothing to wait for. Thread t < n / 8 holds columns
-// [8t, 8t + 8): feature tile t / 16, 32 bytes of that tile's row. `scratch`: 32 * kRows floats.
+// Owner phase of a single rank whose K was split: CTA `block` owns rows block, block + blocks, ... and takes them two
+// at a time (their loads and block-wide sums overlap). For each it waits until every CTA of the row's token tile has
+// announced its partial tile, sums the row's FP32 split partials in split order, rounds to BF16 (that is the rank's
+// partial, as the push path would have stored it) and finishes the row as any owner does. Thread t < n / 8 holds
+// columns [8t, 8t + 8): feature tile t / 16, 32 bytes of that tile's row. `scratch`: 64 floats.
 template <int MODE>
-__device__ __forceinline__ void own_rows_from_splits(const GemmDev& g, const CommDev& c, const CommCtx& x, int mt,
-                                                     float* scratch) {
+__device__ __forceinline__ void own_rows_from_splits(const GemmDev& g, const CommDev& c, const CommCtx& x,
+                                                     const int* counter, int mt, float* scratch) {
     constexpr int kRows = 2;
-    constexpr int kGroup = 2;  // splits whose loads are in flight together (per row)
+    constexpr int kGroup = 3;  // splits whose loads are in flight together (per row)
     const int t = threadIdx.x;
     const int threads = c.n / kVec;
     const bool active = t < threads;
     const int col = (active ? t : 0) * kVec;
     const int f = col / kBlockF, j = col % kBlockF;
+    const int expected = (g.n / kBlockF) * g.splits;
     const size_t split_stride = static_cast<size_t>(mt) * kBlockF;
     uint4 wraw = make_uint4(0, 0, 0, 0);
     if (MODE != kReduce && active) wraw = *reinterpret_cast<const uint4*>(c.weight + col);
+    int ready_tile = -1;  // rows are owned in increasing order, so token tiles are waited for in increasing order
+    bool ok = true;
     for (int r0 = x.block; r0 < c.rows; r0 += kRows * x.blocks) {
         size_t off[kRows];
         uint4 hraw[kRows];
         bool store[kRows];
         const float* src[kRows];
+        int last_tile = 0;
 #pragma unroll
         for (int i = 0; i < kRows; ++i) {
             const int r = r0 + i * x.blocks;
@@ -89,9 +82,32 @@ __device__ __forceinline__ void own_rows_from_splits(const GemmDev& g, const Com
             if (MODE == kReduceNormResidual && active && store[i]) hraw[i] = *reinterpret_cast<const uint4*>(c.h + off[i]);
             src[i] = g.ws + (static_cast<size_t>(f) * g.token_tiles + tt) * g.splits * split_stride +
                      static_cast<size_t>(token) * kBlockF + j;
+            if (store[i]) last_tile = tt;
+        }
+        if (ok && last_tile > ready_tile) {  // uniform over the block
+            if (t == 0) {
+                bool arrived_all = true;
+                for (int tt = ready_tile + 1; tt <= last_tile && arrived_all; ++tt) {
+                    int seen;
+                    do {
+                        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter + tt) : "memory");
+                        if (seen >= expected) break;
+                        if (globaltimer() > x.deadline) {
+                            report(c.status, kErrTimeout, tt, kPhasePipeline, 3);
+                            arrived_all = false;
+                            break;
+                        }
+                    } while (true);
+                }
+                scratch[0] = arrived_all ? 1.f : 0.f;
+            }
+            __syncthreads();
+            ok = scratch[0] != 0.f;
+            __syncthreads();  // scratch is reused by the block-wide sums
+            if (ok) ready_tile = last_tile;
         }
         float v[kRows][kVec] = {};
-        if (active) {
+        if (active && ok) {
             float acc[kRows][kVec];
             for (int base_sp = 0; base_sp < g.splits; base_sp += kGroup) {
                 float4 a[kRows][kGroup], b[kRows][kGroup];
@@ -125,6 +141,8 @@ __device__ __forceinline__ void own_rows_from_splits(const GemmDev& g, const Com
             for (int i = 0; i < kRows; ++i)
                 if (store[i]) add_bf16x8(v[i], pack_bf16x8(acc[i]));  // +0.0f + partial: the rank-ordered sum over one rank
         }
+#pragma unroll
+        for (int i = 0; i < kRows; ++i) store[i] = store[i] && ok;
         finish_rows<MODE, kRows>(c, v, hraw, wraw, off, active, store, scratch, threads);
     }
     stamp(c, x, 2);
@@ -136,7 +154,7 @@ __device__ __forceinline__ void own_rows_from_splits(const GemmDev& g, const Com
 __device__ __forceinline__ bool prefetch_rest_of_slab(int mt) { return mt <= 128; }
 
 template <int NR>
-__global__ void __maxnreg__(kGemmRegs) rowpar_kernel(const __grid_constant__ RowparParams<NR> p) {
+__global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_constant__ RowparParams<NR> p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const int slot = NR == 1 ? 0 : static_cast<int>(blockIdx.y);
     const GemmDev& g = p.g[slot];
@@ -161,58 +179,64 @@ __global__ void __maxnreg__(kGemmRegs) rowpar_kernel(const __grid_constant__ Row
     SmemLayout* sm = reinterpret_cast<SmemLayout*>(tiles + g.stages * stage_bytes);
     const uint32_t cols = tmem_cols(mt);                 // columns of one accumulator
     const int issuers = cols <= 128 && iters >= 2 ? 2 : 1;  // MMA-issuing threads, each with its own accumulator
-    // One rank, K split: the owner of a row (tail kernel) sums the FP32 split partials itself, in split order, so the
-    // BF16 partial never travels through the receive slots and this kernel is done once its partial tile is written;
-    // the value is the same, bit for bit, as pushing and summing one rank.
+    // One rank, K split: the owner of a row sums the FP32 split partials itself (in split order), so the BF16 partial
+    // never travels through the receive slots; the value is the same, bit for bit, as pushing and summing one rank.
     const bool local_rows = p.fused && c.world == 1 && g.splits > 1;
 
     const int pre = iters < g.stages ? iters : g.stages;
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < g.stages; ++i) {
-            mbar_init(&sm->full[i], 1);
-            mbar_init(&sm->empty[i], 1);
-        }
-        mbar_init(&sm->acc_full, static_cast<uint32_t>(issuers));
-        fence_barrier_init();
-        // The first ring-full of weights is requested at once, by the thread that has just set the barriers up: weights
-        // depend on nothing, neither on the kernels in front of this one nor on the rest of this block's set-up.
-        for (int it = 0; it < pre; ++it) {
-            mbar_expect_tx(&sm->full[it], static_cast<uint32_t>(stage_bytes));
-            if (g.w_tiles)
-                bulk_load(tiles + it * stage_bytes, g.w_tiles + (static_cast<size_t>(f) * nkb + kb0 + it) * kTileBytesW,
-                          kTileBytesW, &sm->full[it], kEvictFirst);
-            else
-                tma_load_2d(tiles + it * stage_bytes, &g.tm_w, &sm->full[it], (kb0 + it) * kBlockK, f * kBlockF, kEvictFirst);
-        }
-        // The rest of this CTA's weight slab is pulled into L2 now, while the previous kernel of the stream is still
-        // finishing: the ring then refills at L2 latency instead of HBM latency.
-        if (iters > pre && prefetch_rest_of_slab(mt)) {
-            if (g.w_tiles) {
-                bulk_prefetch_l2(g.w_tiles + (static_cast<size_t>(f) * nkb + kb0 + pre) * kTileBytesW,
-                                 static_cast<uint32_t>(iters - pre) * kTileBytesW);
-            } else {
-                for (int it = pre; it < iters; ++it) tma_prefetch_l2_2d(&g.tm_w, (kb0 + it) * kBlockK, f * kBlockF);
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < g.stages; ++i) {
+                mbar_init(&sm->full[i], 1);
+                mbar_init(&sm->empty[i], 1);
             }
+            mbar_init(&sm->acc_full, static_cast<uint32_t>(issuers));
+            fence_barrier_init();
+            if (!g.w_tiles) tma_prefetch_descriptor(&g.tm_w);
+            tma_prefetch_descriptor(&g.tm_x);
+            // The first ring-full of loads is requested at once, by the thread that has just set the barriers up, while
+            // the rest of the block is still allocating tensor memory: weights depend on nothing, x only on the kernels
+            // in front of this one.
+            for (int it = 0; it < pre; ++it) {
+                mbar_expect_tx(&sm->full[it], static_cast<uint32_t>(stage_bytes));
+                if (g.w_tiles)
+                    bulk_load(tiles + it * stage_bytes, g.w_tiles + (static_cast<size_t>(f) * nkb + kb0 + it) * kTileBytesW,
+                              kTileBytesW, &sm->full[it], kEvictFirst);
+                else
+                    tma_load_2d(tiles + it * stage_bytes, &g.tm_w, &sm->full[it], (kb0 + it) * kBlockK, f * kBlockF,
+                                kEvictFirst);
+            }
+            // The rest of this CTA's weight slab is pulled into L2 now: the ring then refills at L2 latency instead of
+            // HBM latency.
+            if (iters > pre && prefetch_rest_of_slab(mt)) {
+                if (g.w_tiles) {
+                    bulk_prefetch_l2(g.w_tiles + (static_cast<size_t>(f) * nkb + kb0 + pre) * kTileBytesW,
+                                     static_cast<uint32_t>(iters - pre) * kTileBytesW);
+                } else {
+                    for (int it = pre; it < iters; ++it) tma_prefetch_l2_2d(&g.tm_w, (kb0 + it) * kBlockK, f * kBlockF);
+                }
+            }
+            pdl_wait();
+            if (c.stamps) c.stamps[block * kStampSlots + 5] = globaltimer();
+            for (int it = 0; it < pre; ++it)
+                tma_load_2d(tiles + it * stage_bytes + kTileBytesW, &g.tm_x, &sm->full[it], (kb0 + it) * kBlockK,
+                            token0, kEvictLast);
         }
-        tma_prefetch_descriptor(&g.tm_x);
+        __syncwarp();  // the warp reaches the block-wide barrier together
     }
     if (warp == 2) tmem_alloc(&sm->tmem_base, cols * issuers);
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem = sm->tmem_base;
-    // The tail kernel may move in beside this one from now on: it touches nothing before this kernel has completed.
-    if (p.fused) pdl_launch_dependents();
+    // The next kernel of the stream may be set up from now on: its blocks move in as this kernel's blocks leave, and it
+    // waits for this kernel to complete before it reads anything this kernel writes.
+    pdl_launch_dependents();
     // Budget of the local pipeline and of the split-K rendezvous; the cross-rank waits take theirs in comm_begin.
     const long long pipeline_deadline = globaltimer() + (c.timeout_ns > 0 ? c.timeout_ns : kDefaultTimeoutNs);
 
     if (warp == 0) {
         if (lane == 0) {
-            pdl_wait();
-            if (c.stamps) c.stamps[block * kStampSlots + 5] = globaltimer();
-            for (int it = 0; it < pre; ++it)
-                tma_load_2d(tiles + it * stage_bytes + kTileBytesW, &g.tm_x, &sm->full[it], (kb0 + it) * kBlockK,
-                            token0, kEvictLast);
             int st = pre == g.stages ? 0 : pre;
             uint32_t parity = 0;  // second lap of the ring waits for the first release of each stage
             for (int it = pre; it < iters; ++it) {
@@ -285,16 +309,12 @@ __global__ void __maxnreg__(kGemmRegs) rowpar_kernel(const __grid_constant__ Row
             tcgen05_fence_after();
         }
         if (c.stamps && threadIdx.x == 128) c.stamps[block * kStampSlots + 4] = globaltimer();
-        // One K split: the tile leaves in chunks of 16 tokens. The four warps that hold a chunk's 128 features round it to
-        // BF16 into shared memory (token-major, over the drained pipeline stages), meet on a barrier of their own and
-        // store or push its 16 rows while the other four warps are already loading the next chunk from tensor memory.
-        // Several: this CTA's FP32 partial tile goes to the workspace.
-        // Either way the destination may still be in use by the kernels in front of this one, hence the wait.
+        // One K split: the BF16 tile is staged in shared memory, token-major, over the drained pipeline stages.
+        // Several: this CTA's FP32 partial tile goes to the workspace (which the previous kernel of the chain may
+        // still be reading, hence the wait).
         float* part = g.ws + (static_cast<size_t>(tile) * g.splits + s) * mt * kBlockF;
         __nv_bfloat16* staged = reinterpret_cast<__nv_bfloat16*>(tiles);
-        pdl_wait();
-        CommCtx xe{};
-        if (p.fused && g.splits == 1) xe = comm_begin(c, block, blocks, c.epochs[block], comm_failed(c));
+        if (g.splits > 1) pdl_wait();
         for (int chunk = half; chunk < mt / 16; chunk += 2) {
             uint32_t r[16];
             if (iters > 0 && ok) {
@@ -320,16 +340,6 @@ __global__ void __maxnreg__(kGemmRegs) rowpar_kernel(const __grid_constant__ Row
 #pragma unroll
                 for (int j = 0; j < 16; ++j)
                     staged[(chunk * 16 + j) * kBlockF + feature] = __float2bfloat16_rn(__uint_as_float(r[j]));
-                asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
-                const uint4* rows = reinterpret_cast<const uint4*>(staged + chunk * 16 * kBlockF);
-                for (int v = quarter * 32 + lane; v < 16 * (kBlockF / kVec); v += 128) {
-                    const int token = token0 + chunk * 16 + v / (kBlockF / kVec), col = f * kBlockF + v % (kBlockF / kVec) * kVec;
-                    if (p.fused) {
-                        push_store(c, xe, token, col, rows[v]);
-                    } else {
-                        store_v4(g.out + static_cast<size_t>(token) * g.ldo + col, rows[v]);
-                    }
-                }
             }
         }
         tcgen05_fence_before();
@@ -342,9 +352,19 @@ __global__ void __maxnreg__(kGemmRegs) rowpar_kernel(const __grid_constant__ Row
     }
 
     CommCtx x{};
-    if (p.fused && g.splits > 1) x = comm_begin(c, block, blocks, sm->epoch, sm->failed);
+    if (p.fused) {
+        x = comm_begin(c, block, blocks, sm->epoch, sm->failed);
+        stamp(c, x, 0);
+    }
     if (local_rows) {
-        // The partial tile is in the workspace; the tail kernel reads it once this launch has completed.
+        // Announce this CTA's partial tile on the counter of its token tile; the rows' owners wait for it below.
+        const int gen = sm->gen + 1;
+        if (threadIdx.x == 0) {
+            for (int j = block; j < kMaxTiles; j += blocks) g.counters[((gen + 1) & 1) * kMaxTiles + j] = 0;
+            __threadfence();  // after the block barrier: orders every thread's partial-tile stores before the announce
+            atomicAdd(g.counters + (gen & 1) * kMaxTiles + t, 1);
+            for (int j = block; j < kEpochSlots; j += blocks) g.gen[j] = gen;
+        }
     } else if (g.splits > 1) {
         // Split-K rendezvous: every CTA of the tile announces its partial, waits for the others, then sums ITS share of
         // the tile's tokens over the splits in split order (so the value never depends on timing) and pushes it.
@@ -407,43 +427,34 @@ __global__ void __maxnreg__(kGemmRegs) rowpar_kernel(const __grid_constant__ Row
                 store_v4(g.out + static_cast<size_t>(token0 + token) * g.ldo + col, packed);
             }
         }
+    } else {
+        const uint4* staged = reinterpret_cast<const uint4*>(tiles);
+        for (int v = threadIdx.x; v < mt * (kBlockF / kVec); v += kFusedThreads) {
+            const int token = v / (kBlockF / kVec), j = v % (kBlockF / kVec);
+            const uint4 packed = staged[v];
+            const int col = f * kBlockF + j * kVec;
+            if (p.fused) {
+                push_store(c, x, token0 + token, col, packed);
+            } else {
+                store_v4(g.out + static_cast<size_t>(token0 + token) * g.ldo + col, packed);
+            }
+        }
     }
     if (p.fused) {
         if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 6] = globaltimer();
-    } else {
-        pdl_launch_dependents();
-    }
-}
-
-// The reduction half of a fused call (see the top of the file). Grid: up to one CTA per SM, independent of the GEMM's
-// grid; block: hidden / 8 threads rounded up to whole warps.
-template <int NR>
-__global__ void __maxnreg__(kTailRegs) rowpar_tail_kernel(const __grid_constant__ RowparParams<NR> p) {
-    const int slot = NR == 1 ? 0 : static_cast<int>(blockIdx.y);
-    const GemmDev& g = p.g[slot];
-    const CommDev& c = p.c[slot];
-    __shared__ float scratch[64];
-    const int block = static_cast<int>(blockIdx.x), blocks = static_cast<int>(gridDim.x);
-    if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 1] = globaltimer();
-    // The next GEMM of the stream may start its prologue and weight prefetch now; it waits for this kernel to complete
-    // before it touches anything this kernel writes.
-    pdl_launch_dependents();
-    // Everything this kernel reads that is not in-band (invocation counters, status words, the residual stream, the
-    // split-K partial tiles) was last written by launches that have completed once the GEMM in front has.
-    pdl_wait();
-    const CommCtx x = comm_begin(c, block, blocks, c.epochs[block], comm_failed(c));
-    stamp(c, x, 0);
-    if (c.world == 1 && g.splits > 1) {
-        const int mt = g.m / g.token_tiles;
-        if (c.mode == kReduce) own_rows_from_splits<kReduce>(g, c, x, mt, scratch);
-        else if (c.mode == kReduceNorm) own_rows_from_splits<kReduceNorm>(g, c, x, mt, scratch);
-        else own_rows_from_splits<kReduceNormResidual>(g, c, x, mt, scratch);
-        rearm(c, x, x.block, x.blocks);
-    } else {
+        stamp(c, x, 1);
         rearm_early(c, x);
-        own_and_collect<true>(c, x, scratch);  // re-arms late shares between its own and collect phases
+        if (local_rows) {
+            const int* counter = g.counters + ((sm->gen + 1) & 1) * kMaxTiles;
+            if (c.mode == kReduce) own_rows_from_splits<kReduce>(g, c, x, counter, mt, sm->scratch);
+            else if (c.mode == kReduceNorm) own_rows_from_splits<kReduceNorm>(g, c, x, counter, mt, sm->scratch);
+            else own_rows_from_splits<kReduceNormResidual>(g, c, x, counter, mt, sm->scratch);
+            rearm_late(c, x);
+        } else {
+            own_and_collect(c, x, sm->scratch);  // re-arms late shares between its own and collect phases
+        }
+        comm_end(c, x);
     }
-    comm_end(c, x);
 }
 
 int rowpar_stages(int m) {  // m: tokens per tile
@@ -455,47 +466,6 @@ int rowpar_stages(int m) {  // m: tokens per tile
 
 int rowpar_smem_bytes(int m, int stages) {
     return stages * (kTileBytesW + m * kBlockK * 2) + static_cast<int>(sizeof(SmemLayout)) + 1024;
-}
-
-template <int NR>
-static int launch_tail(const RowparParams<NR>& p, dim3 grid, const LaunchOpts& o) {
-    // An SM runs kernels of one shared-memory / L1 split at a time. The GEMM kernels need the largest split, so the tail
-    // kernel asks for the same one although it uses next to no shared memory; otherwise it could not share an SM
-    // with them.
-    static bool carved[64] = {};
-    int dev = 0;
-    (void)cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !carved[dev]) {
-        carved[dev] = cudaFuncSetAttribute(rowpar_tail_kernel<NR>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                           cudaSharedmemCarveoutMaxShared) == cudaSuccess;
-        (void)cudaGetLastError();
-    }
-    cudaLaunchConfig_t config{};
-    config.gridDim = grid;
-    config.blockDim = dim3(static_cast<unsigned>((p.c[0].n / kVec + 31) / 32 * 32));
-    config.stream = o.stream;
-    cudaLaunchAttribute attrs[2];
-    int n = 0;
-    if (o.pdl) {
-        attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attrs[n].val.programmaticStreamSerializationAllowed = 1;
-        ++n;
-    }
-    if (o.cooperative) {
-        attrs[n].id = cudaLaunchAttributeCooperative;
-        attrs[n].val.cooperative = 1;
-        ++n;
-    }
-    config.attrs = attrs;
-    config.numAttrs = n;
-    const cudaError_t err = cudaLaunchKernelEx(&config, rowpar_tail_kernel<NR>, p);
-    if (err != cudaSuccess) {
-        g_last_cuda_error = static_cast<int>(err);
-        (void)cudaGetLastError();
-        return -6;
-    }
-    ++g_launches;
-    return 0;
 }
 
 template <int NR>
@@ -542,16 +512,10 @@ static int launch_impl(const RowparParams<NR>& p, dim3 grid, const LaunchOpts& o
     return 0;
 }
 
-int launch_rowpar(const RowparParams<1>& p, int grid, int tail_grid, const LaunchOpts& o) {
-    const int rc = launch_impl<1>(p, dim3(grid), o);
-    if (rc != 0 || !p.fused) return rc;
-    return launch_tail<1>(p, dim3(tail_grid), o);
-}
+int launch_rowpar(const RowparParams<1>& p, int grid, const LaunchOpts& o) { return launch_impl<1>(p, dim3(grid), o); }
 
-int launch_rowpar_loopback(const RowparParams<kMaxWorld>& p, int grid, int tail_grid, int nranks, const LaunchOpts& o) {
-    const int rc = launch_impl<kMaxWorld>(p, dim3(grid, nranks), o);
-    if (rc != 0) return rc;
-    return launch_tail<kMaxWorld>(p, dim3(tail_grid, nranks), o);
+int launch_rowpar_loopback(const RowparParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o) {
+    return launch_impl<kMaxWorld>(p, dim3(grid, nranks), o);
 }
 
 int rowpar_max_ctas_per_sm(int m) {

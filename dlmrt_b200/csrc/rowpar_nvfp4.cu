@@ -52,7 +52,7 @@ struct MoeSmem {
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint32_t tmem_base;
-    int n_active;
+    int n_active, epoch, gen, failed;
     int warp_count[8];
     float scratch[64];
     short active[kMaxEntries];  // expert | row block << 8
@@ -184,7 +184,7 @@ __device__ __forceinline__ float gated_activation(float gate, float up, int kind
 }
 
 template <int NR, bool GATE_UP>
-__global__ void __maxnreg__(kMoeRegs) moe_kernel(const __grid_constant__ MoeParams<NR> p) {
+__global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_constant__ MoeParams<NR> p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const int slot = NR == 1 ? 0 : static_cast<int>(blockIdx.y);
     const MoeDev& g = p.g[slot];
@@ -217,7 +217,7 @@ __global__ void __maxnreg__(kMoeRegs) moe_kernel(const __grid_constant__ MoePara
         tma_prefetch_descriptor(&g.tm_a);
     }
     if (warp == 2) tmem_alloc(&sm->tmem_base, kTmemCols);
-    // The tail kernel may move in beside this one from now on: it touches nothing before this kernel has completed.
+    // The next kernel of the stream may be set up from now on (its blocks move in as this kernel's blocks leave).
     pdl_launch_dependents();
     // Routing (counts, slots, activations) comes from the previous kernels of the stream: nothing of it may be read
     // before they are complete.
@@ -226,6 +226,12 @@ __global__ void __maxnreg__(kMoeRegs) moe_kernel(const __grid_constant__ MoePara
     {
         const int e = threadIdx.x;
         const int total_rows = e < g.e_local ? min(g.counts[g.lo + e], g.m_max) : 0;
+        int early = 0;  // the invocation counters, fetched in the same round trip as the counts
+        if (!GATE_UP) {
+            if (threadIdx.x == 352 && p.fused) early = c.epochs[block];
+            if (threadIdx.x == 353) early = g.gen[block];
+            if (threadIdx.x == 354 && p.fused) early = comm_failed(c);
+        }
         const int nb = (total_rows + kItemRows - 1) / kItemRows;
         int incl = nb;
 #pragma unroll
@@ -250,6 +256,9 @@ __global__ void __maxnreg__(kMoeRegs) moe_kernel(const __grid_constant__ MoePara
                 sm->n_active = total;
             }
         }
+        if (threadIdx.x == 352) sm->epoch = early;
+        if (threadIdx.x == 353) sm->gen = early;
+        if (threadIdx.x == 354) sm->failed = early;
         __syncthreads();
     }
     if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 0] = globaltimer();
@@ -472,6 +481,8 @@ __global__ void __maxnreg__(kMoeRegs) moe_kernel(const __grid_constant__ MoePara
             if (!ok) break;
         }
     }
+    // Every Y row this CTA produced is written; announce it and wait for the rest of the grid (the combine reads rows
+    // written by other CTAs). Counters are banked by launch generation as in the BF16 kernel.
     tcgen05_fence_before();
     __syncthreads();
     if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 4] = globaltimer();
@@ -479,38 +490,44 @@ __global__ void __maxnreg__(kMoeRegs) moe_kernel(const __grid_constant__ MoePara
         tcgen05_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
-    // GEMM1: the activation slots are written, the down-projection launch that follows does the rest. GEMM2: every Y
-    // row this CTA produced is written; the tail kernel combines them once the whole launch has completed.
-}
-
-// Combine + reduction half of the expert down-projection: out[row] = bf16(sum over k in list order of w_k * y_k)
-// (+ shared), experts of other ranks contributing 0 * 0, then the row is stored (plain call), finished in place (one
-// rank: the CTA that combines a row is also its owner) or pushed to its owner rank and reduced (comm.cuh). A launch of
-// its own behind the GEMM, chained by programmatic dependent launch, for the reason given in rowpar_bf16.cu: its small
-// blocks fit on an SM beside the next launch's GEMM CTA, whose prologue and first weight loads then cost nothing; and
-// the GEMM's completion is the grid-wide rendezvous the combine needs (rows of Y come from many CTAs).
-template <int NR>
-__global__ void __maxnreg__(kTailRegs) moe_tail_kernel(const __grid_constant__ MoeParams<NR> p) {
-    const int slot = NR == 1 ? 0 : static_cast<int>(blockIdx.y);
-    const MoeDev& g = p.g[slot];
-    const CommDev& c = p.c[slot];
-    __shared__ float scratch[64];
-    const int block = static_cast<int>(blockIdx.x), blocks = static_cast<int>(gridDim.x);
-    if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 1] = globaltimer();
-    pdl_launch_dependents();
-    pdl_wait();
+    if (GATE_UP) return;  // the activation slots are written; the down-projection launch that follows does the rest
     CommCtx x{};
-    if (p.fused) {
-        x = comm_begin(c, block, blocks, c.epochs[block], comm_failed(c));
-        stamp(c, x, 0);
-    }
+    if (p.fused) x = comm_begin(c, block, blocks, sm->epoch, sm->failed);
+    // The expert list of this CTA's first output row is fetched now, ahead of the wait for the experts' outputs.
     CombineMeta first;
     if (block < g.m) first = combine_meta(g, block, 0);
+    {
+        const int gen = sm->gen + 1;
+        int* counter = g.counters + (gen & 1) * kMaxTiles;
+        if (threadIdx.x == 0) {
+            if (block == 0) g.counters[((gen + 1) & 1) * kMaxTiles] = 0;
+            __threadfence();  // after the block barrier: orders every thread's Y stores before the announce
+            atomicAdd(counter, 1);
+            // Only CTAs that have output rows to combine need the others' Y rows; polling is paced so that the
+            // arrivals of the rest of the grid are not queued behind a storm of loads on the same word.
+            while (block < g.m) {
+                int seen;
+                asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+                if (seen >= blocks) break;
+                if (globaltimer() > deadline) {
+                    report(c.status, kErrTimeout, 0, kPhasePipeline, 3);
+                    break;
+                }
+                __nanosleep(100);
+            }
+            for (int j = block; j < kEpochSlots; j += blocks) g.gen[j] = gen;
+        }
+        __syncthreads();
+    }
+    if (c.stamps && threadIdx.x == 0) c.stamps[block * kStampSlots + 5] = globaltimer();
+    // Combine: out[row] = bf16(sum over k in list order of w_k * y_k), experts of other ranks contribute 0 * 0.
+    // With one rank the sum over ranks is the identity and the CTA that combines a row is also its owner (rows block,
+    // block + blocks, ... in both roles), so the row is finished here and never travels through the receive slots.
     const bool local_rows = p.fused && c.world == 1;
     if (local_rows) {
-        if (c.mode == kReduce) combine_and_finish<kReduce>(g, c, block, blocks, scratch, first);
-        else if (c.mode == kReduceNorm) combine_and_finish<kReduceNorm>(g, c, block, blocks, scratch, first);
-        else combine_and_finish<kReduceNormResidual>(g, c, block, blocks, scratch, first);
+        if (c.mode == kReduce) combine_and_finish<kReduce>(g, c, block, blocks, sm->scratch, first);
+        else if (c.mode == kReduceNorm) combine_and_finish<kReduceNorm>(g, c, block, blocks, sm->scratch, first);
+        else combine_and_finish<kReduceNormResidual>(g, c, block, blocks, sm->scratch, first);
     } else {
         const int t = threadIdx.x, threads = g.n / kVec;
         for (int row = block; row < g.m; row += blocks) {
@@ -525,54 +542,17 @@ __global__ void __maxnreg__(kTailRegs) moe_tail_kernel(const __grid_constant__ M
         }
     }
     if (p.fused) {
+        stamp(c, x, 1);
+        rearm_early(c, x);
         if (local_rows) {
             stamp(c, x, 2);
             stamp(c, x, 3);
-            rearm(c, x, x.block, x.blocks);
+            rearm_late(c, x);
         } else {
-            rearm_early(c, x);
-            own_and_collect<true>(c, x, scratch);  // re-arms late shares between its own and collect phases
+            own_and_collect(c, x, sm->scratch);  // re-arms late shares between its own and collect phases
         }
         comm_end(c, x);
     }
-}
-
-template <int NR>
-static int launch_tail(const MoeParams<NR>& p, dim3 grid, const LaunchOpts& o) {
-    static bool carved[64] = {};  // the same shared-memory / L1 split as the GEMM kernels, so that they can share an SM
-    int dev = 0;
-    (void)cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !carved[dev]) {
-        carved[dev] = cudaFuncSetAttribute(moe_tail_kernel<NR>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                           cudaSharedmemCarveoutMaxShared) == cudaSuccess;
-        (void)cudaGetLastError();
-    }
-    cudaLaunchConfig_t config{};
-    config.gridDim = grid;
-    config.blockDim = dim3(static_cast<unsigned>((p.g[0].n / kVec + 31) / 32 * 32));
-    config.stream = o.stream;
-    cudaLaunchAttribute attrs[2];
-    int n = 0;
-    if (o.pdl) {
-        attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attrs[n].val.programmaticStreamSerializationAllowed = 1;
-        ++n;
-    }
-    if (o.cooperative) {
-        attrs[n].id = cudaLaunchAttributeCooperative;
-        attrs[n].val.cooperative = 1;
-        ++n;
-    }
-    config.attrs = attrs;
-    config.numAttrs = n;
-    const cudaError_t err = cudaLaunchKernelEx(&config, moe_tail_kernel<NR>, p);
-    if (err != cudaSuccess) {
-        g_last_cuda_error = static_cast<int>(err);
-        (void)cudaGetLastError();
-        return -6;
-    }
-    ++g_launches;
-    return 0;
 }
 
 template <int NR, bool GATE_UP>
@@ -618,16 +598,12 @@ static int launch_impl(const MoeParams<NR>& p, dim3 grid, const LaunchOpts& o) {
     return 0;
 }
 
-int launch_moe(const MoeParams<1>& p, int grid, int tail_grid, const LaunchOpts& o) {
-    const int rc = launch_impl<1, false>(p, dim3(grid), o);
-    return rc != 0 ? rc : launch_tail<1>(p, dim3(tail_grid), o);
-}
+int launch_moe(const MoeParams<1>& p, int grid, const LaunchOpts& o) { return launch_impl<1, false>(p, dim3(grid), o); }
 
 int launch_moe_gate_up(const MoeParams<1>& p, int grid, const LaunchOpts& o) { return launch_impl<1, true>(p, dim3(grid), o); }
 
 int launch_moe_loopback(const MoeParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o) {
-    const int rc = launch_impl<kMaxWorld, false>(p, dim3(grid, nranks), o);
-    return rc != 0 ? rc : launch_tail<kMaxWorld>(p, dim3(grid, nranks), o);
+    return launch_impl<kMaxWorld, false>(p, dim3(grid, nranks), o);
 }
 
 }  // namespace dlm

@@ -280,7 +280,8 @@ class Group:
         ws = self.workspace(chain, nbytes)
         linear.describe(g)
         g.x, g.m, g.n, g.k, g.ldx = x.data_ptr(), m, linear.n, k, x.stride(0)
-        g.workspace, g.workspace_bytes, g.splits = ws.data_ptr(), ws.numel(), 0
+        g.workspace, g.workspace_bytes = ws.data_ptr(), ws.numel()
+        g.splits, g.token_tiles = linear.splits, linear.token_tiles
         return g
 
     @staticmethod
@@ -299,12 +300,15 @@ class Group:
             raise RuntimeError("this group reported a device time-out: its buffers may hold stale arrivals; build a new "
                                "Group before reducing again")
         rows, n = partial.shape
+        last = self._last.get(chain)
         comm, out = self._comm(rows, n, site, chain, mode, h, weight, eps, scale, replicated)
         stream = torch.cuda.current_stream(self.device).cuda_stream
         pending = self._pending.pop(partial.data_ptr(), None)
-        # Other ranks broadcast into `out` while this rank's GEMM may still load its input, so an input that overlaps
-        # `out` runs unfused. (The chain's previous output is a legal input: it is re-armed only after the GEMM.)
-        fusable = pending is not None and n <= _lib.FUSED_MAX_N and not self._overlap(pending[2], out)
+        # The fused kernel re-arms `last` and fills `out` while other CTAs still load the GEMM's input; an input that
+        # IS one of those (a projection fed straight from the previous reduction) therefore runs as two kernels, the
+        # order the reference has anyway.
+        fusable = pending is not None and n <= _lib.FUSED_MAX_N and not self._overlap(pending[2], last) \
+            and not self._overlap(pending[2], out)
         if fusable and pending[0] == "linear":
             gemm = self._gemm(pending[1], pending[2], chain)
             _lib.check(_lib.lib().dlm_rowpar_bf16(C.byref(gemm), C.byref(comm), stream), f"rowpar {site}")

@@ -39,7 +39,7 @@ def tile_weight(weight):
 class Linear:
     """y = x @ W^T, BF16 in and out, FP32 accumulation in increasing K (K ranges summed in order when split)."""
 
-    def __init__(self, weight, fp8=False, b200=False, group=None, tiled=True, nn=False):
+    def __init__(self, weight, fp8=False, b200=False, group=None, tiled=True, nn=False, token_tiles=0, splits=0):
         if fp8:
             raise NotImplementedError("FP8 linears are not part of the row-parallel BF16 path")
         if weight.dtype != torch.bfloat16 or weight.dim() != 2:
@@ -55,6 +55,8 @@ class Linear:
         # `tiled`: stream a re-laid copy of the weight (see tile_weight) instead of the row-major matrix.
         self.tiles = tile_weight(self.weight) if tiled and self.n % 128 == 0 and self.k % 8 == 0 else None
         self.group = group
+        # Tiling of this layer's GEMM (tiles along the tokens, K splits): 0 = chosen by the library for each call.
+        self.token_tiles, self.splits = token_tiles, splits
         self._workspace = None
         _lib.lib()
 
@@ -76,7 +78,8 @@ class Linear:
         g = DlmGemm()
         self.describe(g)
         g.x, g.m, g.n, g.k, g.ldx = x.data_ptr(), m, self.n, k, x.stride(0)
-        g.workspace, g.workspace_bytes, g.splits = self._workspace.data_ptr(), self._workspace.numel(), 0
+        g.workspace, g.workspace_bytes = self._workspace.data_ptr(), self._workspace.numel()
+        g.splits, g.token_tiles = self.splits, self.token_tiles
         stream = torch.cuda.current_stream(x.device).cuda_stream
         _lib.check(_lib.lib().dlm_gemm_bf16(C.byref(g), out.data_ptr(), out.stride(0), int(pdl), stream),
                    f"gemm [{m}, {self.n}, {k}]")

@@ -59,7 +59,7 @@ enum {
     DLM_ERR_TIMEOUT = -8,   /* device status: a bounded wait ran out (data from a rank never arrived) */
     DLM_ERR_ARCH = -9,      /* not an sm_100 device */
     DLM_ERR_SCRATCH = -10,  /* dlm_gemm_bf16_noalloc: the requested K splits do not fit the built-in scratch */
-    DLM_ERR_OVERLAP = -11   /* dlm_rowpar_bf16: the GEMM's input overlaps `out` of the same call */
+    DLM_ERR_OVERLAP = -11   /* dlm_rowpar_bf16: the GEMM's input overlaps `rearm` or `out` of the same call */
 };
 
 /* What follows the rank-ordered sum (tp_comm.cu:138 template <NORM, RESIDUAL>). */
@@ -256,11 +256,8 @@ DLM_API int dlm_gemm_bf16_noalloc(const void* x, const void* w, void* out, int m
  * Replaces the pair Linear.__call__(x, out=partial) -> Group.reduce / reduce_norm
  * (dlmrt/models/sdar/model.py:237-243, llada2/model.py:435-439, diffusion_gemma/model.py:272-292).
  * gemm->m == comm->rows, gemm->n == comm->n <= DLM_FUSED_MAX_N.
- * Two launches chained by programmatic dependent launch: the GEMM, whose finished tiles are pushed straight into the
- * owners' slots, and the reduction's tail (rank-ordered sum, residual + RMSNorm, multicast all-gather, re-arming),
- * whose small blocks share the SMs with the NEXT call's GEMM while they wait for the other ranks.
- * gemm->x must not overlap comm->out (DLM_ERR_OVERLAP): other ranks fill `out` while this rank may still load x. It
- * may be comm->rearm (a projection fed by the chain's previous output): re-arming waits for the GEMM to complete. */
+ * gemm->x must not overlap comm->rearm or comm->out (DLM_ERR_OVERLAP): CTAs re-arm and fill those while others still
+ * load x. A caller whose input IS the previous output of the chain runs dlm_gemm_bf16 + dlm_reduce_bf16 instead. */
 DLM_API int dlm_rowpar_bf16(const DlmGemm* gemm, const DlmComm* comm, dlm_stream_t stream);
 
 /* NVFP4 routed experts on one GPU: out[m, n] BF16 (ldo elements) = combine(GEMM2). Replaces the GEMM2 + finalize

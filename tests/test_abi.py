@@ -105,14 +105,11 @@ def test_fused_requires_matching_shapes():
     assert _lib.lib().dlm_rowpar_bf16(C.byref(gemm(n=512)), C.byref(c), None) == _lib.ERR_SHAPE
 
 
-def test_fused_rejects_an_input_that_is_the_output():
-    """Other ranks fill `out` while this rank's GEMM may still load x; `rearm` (the chain's previous output) is a legal
-    input, because it is re-armed by the tail launch, after the GEMM."""
+def test_fused_rejects_an_input_that_the_same_launch_rearms_or_writes():
+    """CTAs of the fused kernel re-arm `rearm` and fill `out` while others still load x, so x may be neither."""
     lib = _lib.lib()
     g = gemm()  # x at 0x1000, 32 x 128 BF16 = 8 KiB
-    peers = (C.c_void_p * 8)(0x50000)
-    assert lib.dlm_rowpar_bf16(C.byref(g), C.byref(comm(rearm=0x2000, rearm_bytes=4096, out=0x50000, out_peers=peers)),
-                               None) != _lib.ERR_OVERLAP
+    assert lib.dlm_rowpar_bf16(C.byref(g), C.byref(comm(rearm=0x2000, rearm_bytes=4096)), None) == _lib.ERR_OVERLAP
     assert lib.dlm_rowpar_bf16(C.byref(g), C.byref(comm(out=0x1800, out_peers=(C.c_void_p * 8)(0x1800))), None) \
         == _lib.ERR_OVERLAP
     assert b"overlaps" in lib.dlm_strerror(_lib.ERR_OVERLAP)

@@ -184,7 +184,7 @@ def test_prequantised_input_and_expert_parallel_ranks():
 
 def test_down_projection_is_deferred_into_the_reduction():
     """`out` a symmetric partial of the experts' group: trtllm_moe runs the front half and leaves the down-projection to
-    the Group.reduce that follows (expert GEMM launch + combine-and-reduce launch); same bits as the unfused call."""
+    the Group.reduce that follows, one fused launch; same bits as the unfused call."""
     from dlmrt_b200 import _lib
     from dlmrt_b200.distributed.parallel import Group
     from dlmrt_b200.quantization import nvfp4
@@ -203,7 +203,7 @@ def test_down_projection_is_deferred_into_the_reduction():
     p = nvfp4.trtllm_moe(x, packed, experts, partial, e_total, 0, f, activation=prefix)
     assert _lib.lib().dlm_launch_count() == before + 2   # bookkeeping + GEMM1; the down-projection waits
     out = g.reduce(p, site="0.moe", chain=1)
-    assert _lib.lib().dlm_launch_count() == before + 4   # the fused call: expert GEMM, then combine + reduction
+    assert _lib.lib().dlm_launch_count() == before + 3   # one fused launch
     torch.cuda.synchronize()
     g.check()
     assert_same_bits(bits(out), bits(plain), "fused vs unfused")

@@ -227,7 +227,7 @@ def test_linear_defers_into_group_reduce():
     assert _lib.lib().dlm_launch_count() == before  # deferred: nothing ran yet
     h_before = bits(h)[None]
     out = g.reduce_norm(p, h, weight, 1e-6, site="0.post")
-    assert _lib.lib().dlm_launch_count() == before + 2  # the fused call: GEMM + push, then the reduction's tail
+    assert _lib.lib().dlm_launch_count() == before + 1  # one fused kernel
     torch.cuda.synchronize()
     g.check()
     partial_bits = bits(Linear(w).gemm(x, torch.empty(m, n, dtype=torch.bfloat16, device="cuda")))[None]
@@ -241,11 +241,12 @@ def test_linear_defers_into_group_reduce():
     assert_same_bits(bits(p2), partial_bits[0], "flushed partial")
 
 
-def test_projection_fed_by_the_previous_output():
-    """A projection whose input IS the chain's previous output (which the call re-arms) stays fused: re-arming is the
-    tail launch's job and that starts only when the GEMM launch has completed. An input that is the call's own output
-    buffer is refused by the C entry point."""
+def test_projection_fed_by_the_previous_output_runs_unfused():
+    """The fused kernel re-arms the chain's previous output while some of its CTAs may still be loading x, so a
+    projection whose input IS that output must not be fused: the Group runs GEMM and reduction as two launches (the
+    reference's order), and the C entry point refuses the aliasing outright."""
     from dlmrt_b200 import _lib
+    from dlmrt_b200._lib import DlmGemm
     from dlmrt_b200.distributed.parallel import Group
     from dlmrt_b200.layers.linear import Linear
 
@@ -256,15 +257,16 @@ def test_projection_fed_by_the_previous_output():
     x = randn_bf16(m, n, seed=92)
     before = _lib.lib().dlm_launch_count()
     first = g.reduce(lin[0](x, out=g.partial("a", (m, n))), site="a")
+    assert _lib.lib().dlm_launch_count() == before + 1           # fused
     second = g.reduce(lin[1](first, out=g.partial("b", (m, n))), site="b")
-    assert _lib.lib().dlm_launch_count() == before + 4           # two fused calls: a GEMM and a tail launch each
+    assert _lib.lib().dlm_launch_count() == before + 3           # GEMM, then reduction
     torch.cuda.synchronize()
     g.check()
     want = Linear(w[1]).gemm(Linear(w[0]).gemm(x, torch.empty(m, n, dtype=torch.bfloat16, device="cuda")),
                              torch.empty(m, n, dtype=torch.bfloat16, device="cuda"))
     torch.cuda.synchronize()
     assert_same_bits(bits(second), bits(want), "chained projections")
-    assert bool((first.view(torch.int16) == -1).all()), "the previous output was re-armed"
-    comm, out = g._comm(m, n, "c", 0, _lib.REDUCE, None, None, 0.0, 1.0)
-    gm = g._gemm(lin[0], out, 0)   # x = the buffer this very call writes
+    # through the C ABI the same aliasing is an error
+    comm, _ = g._comm(m, n, "c", 0, _lib.REDUCE, None, None, 0.0, 1.0)
+    gm = g._gemm(lin[0], second, 0)   # x = the chain's previous output = what this call would re-arm
     assert _lib.lib().dlm_rowpar_bf16(C.byref(gm), C.byref(comm), None) == _lib.ERR_OVERLAP
