@@ -522,8 +522,8 @@ static int fill_moe(MoeDev* d, const DlmMoe* m) {
     int rc = DLM_OK;
     if (m->w_tiled) d->w_tiles = static_cast<const uint8_t*>(m->w_codes);
     else rc = make_map_u8(&d->tm_w, m->w_codes, static_cast<long long>(m->e_local) * m->n, m->f / 2, kBlockF);
-    if (rc == DLM_OK) rc = make_map_u8(&d->tm_a, m->act_codes, static_cast<long long>(m->e_local) * m->m_max, m->f / 2, 8);
     if (rc != DLM_OK) return rc;
+    d->a_codes = static_cast<const uint8_t*>(m->act_codes);
     d->a_scales = static_cast<const uint8_t*>(m->act_scales);
     d->w_scales = static_cast<const uint8_t*>(m->w_scales);
     d->amap = m->amap, d->counts = m->counts, d->g2 = m->g2, d->ids = m->ids, d->weights = m->weights;
@@ -623,9 +623,8 @@ int dlm_moe_front_nvfp4(const DlmMoeFront* a, int pdl, dlm_stream_t stream) {
     MoeDev* d = &p.g[0];
     if (a->w13_tiled) d->w_tiles = static_cast<const uint8_t*>(a->w13_codes);
     else rc = make_map_u8(&d->tm_w, a->w13_codes, static_cast<long long>(a->e_local) * 2 * a->f, a->hidden / 2, kBlockF);
-    if (rc == DLM_OK)
-        rc = make_map_u8(&d->tm_a, a->slot_codes, static_cast<long long>(a->e_local) * a->m_max, a->hidden / 2, 8);
     if (rc != DLM_OK) return rc;
+    d->a_codes = static_cast<const uint8_t*>(a->slot_codes);
     d->a_scales = static_cast<const uint8_t*>(a->slot_scales);
     d->w_scales = static_cast<const uint8_t*>(a->w13_scales);
     d->amap = a->amap, d->counts = a->counts, d->g2 = a->g1, d->a2_inv = a->a2_inv;

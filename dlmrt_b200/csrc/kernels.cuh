@@ -49,7 +49,7 @@ struct alignas(64) MoeDev {
     CUtensorMap tm_w;         // W2 codes as bytes [e_local * n, f / 2], box 128 B x 128 rows, 128-byte swizzle
     const uint8_t* w_tiles;   // or: the codes pre-tiled [e_local][n / 128][ceil(f / 256)][16 KB], each tile 128 rows x 128
                               // bytes already in the swizzled shared-memory order (zero-padded along f)
-    CUtensorMap tm_a;         // activation codes [e_local * m_max, f / 2], box 128 B x 8 rows, 128-byte swizzle
+    const uint8_t* a_codes;   // activation codes [e_local * m_max, f / 2]
     const uint8_t* a_scales;  // [e_local * m_max, f / 16] E4M3, linear
     const uint8_t* w_scales;  // [e_local][n / 128][f / 64][512] E4M3 in 128 x 4 atoms
     const int* amap;          // [e_total, m_max] pair index (token * top_k + k) of each expert's slots

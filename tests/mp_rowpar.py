@@ -159,8 +159,8 @@ def main():
     e_local = 64 // world
     args = device_args(case, rank * e_local, e_local, dev)
     want = red.reduce(np.stack([oracle_out(case, r * e_local, e_local)[0] for r in range(world)]))
-    one_hop = 0
-    for limit in (group.one_shot_bytes, 0):  # 32 rows: one NVLink hop by default; then forced onto the two-hop protocol
+    one_hop, default_limit = 0, group.one_shot_bytes
+    for limit in (default_limit, 0):  # 32 rows: one NVLink hop by default; then forced onto the two-hop protocol
         group.one_shot_bytes = limit
         one_hop += int(group.one_shot(32, 2048, 0))
         for rep in range(3):
@@ -179,6 +179,7 @@ def main():
             group.check()
             assert_same_bits(bits(out), red.reduce(all_p), f"small reduce {rep} (one-shot limit {limit})")
     assert one_hop == 1
+    group.one_shot_bytes = default_limit
     # the round's other collective: all-gather of row statistics, several invocations per key
     for key, shape in (("row_stats", (32, 4)), ("logit_stats", (256, 2))):
         for call in range(4):
