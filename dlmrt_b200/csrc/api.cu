@@ -193,8 +193,10 @@ int check_gemm(const DlmGemm* g) {
 }
 
 // Fills the device-side GEMM block; returns the per-rank grid in *grid.
+// `solo`: an ordinary launch of one rank's grid (not the cooperative several-ranks-on-one-GPU launch), which may use the
+// half-SM kernel.
 int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid, int owner_rows = 0,
-              bool single_rank = false) {
+              bool single_rank = false, bool solo = true) {
     std::memset(d, 0, sizeof(*d));
     const int avail = max_ctas > 0 && max_ctas < sms ? max_ctas : sms;
     const int feature_tiles = g->n / kBlockF, nkb = (g->k + kBlockK - 1) / kBlockK;
@@ -229,8 +231,12 @@ int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid, in
     d->k = g->k;
     d->splits = splits;
     d->token_tiles = token_tiles;
-    d->stages = rowpar_stages(mt);
     *grid = tiles * splits;
+    // The half-SM kernel where (nearly) no block owns more than one row of the reduction and its shorter ring still
+    // covers the block's k-blocks or holds three stages.
+    const int lean_stages = rowpar_stages(mt, true), kb = (nkb + splits - 1) / splits;
+    d->lean = solo && owner_rows <= *grid + *grid / 8 && (lean_stages >= 3 || lean_stages >= kb);
+    d->stages = rowpar_stages(mt, d->lean != 0);
     return DLM_OK;
 }
 
@@ -477,7 +483,8 @@ int dlm_rowpar_bf16(const DlmGemm* gemm, const DlmComm* comm, dlm_stream_t strea
     RowparParams<1> p;
     std::memset(&p, 0, sizeof(p));
     int grid = 0;
-    rc = fill_gemm(&p.g[0], gemm, comm->max_ctas, info.sms, &grid, comm->rows / comm->world, comm->world == 1);
+    const int slot_rows = comm->one_shot && comm->world > 1 ? comm->rows : comm->rows / comm->world;  // rows this rank sums
+    rc = fill_gemm(&p.g[0], gemm, comm->max_ctas, info.sms, &grid, slot_rows, comm->world == 1);
     if (rc != DLM_OK) return rc;
     fill_comm(&p.c[0], comm);
     p.fused = 1;
@@ -522,8 +529,8 @@ static int fill_moe(MoeDev* d, const DlmMoe* m) {
     int rc = DLM_OK;
     if (m->w_tiled) d->w_tiles = static_cast<const uint8_t*>(m->w_codes);
     else rc = make_map_u8(&d->tm_w, m->w_codes, static_cast<long long>(m->e_local) * m->n, m->f / 2, kBlockF);
+    if (rc == DLM_OK) rc = make_map_u8(&d->tm_a, m->act_codes, static_cast<long long>(m->e_local) * m->m_max, m->f / 2, 8);
     if (rc != DLM_OK) return rc;
-    d->a_codes = static_cast<const uint8_t*>(m->act_codes);
     d->a_scales = static_cast<const uint8_t*>(m->act_scales);
     d->w_scales = static_cast<const uint8_t*>(m->w_scales);
     d->amap = m->amap, d->counts = m->counts, d->g2 = m->g2, d->ids = m->ids, d->weights = m->weights;
@@ -623,8 +630,9 @@ int dlm_moe_front_nvfp4(const DlmMoeFront* a, int pdl, dlm_stream_t stream) {
     MoeDev* d = &p.g[0];
     if (a->w13_tiled) d->w_tiles = static_cast<const uint8_t*>(a->w13_codes);
     else rc = make_map_u8(&d->tm_w, a->w13_codes, static_cast<long long>(a->e_local) * 2 * a->f, a->hidden / 2, kBlockF);
+    if (rc == DLM_OK)
+        rc = make_map_u8(&d->tm_a, a->slot_codes, static_cast<long long>(a->e_local) * a->m_max, a->hidden / 2, 8);
     if (rc != DLM_OK) return rc;
-    d->a_codes = static_cast<const uint8_t*>(a->slot_codes);
     d->a_scales = static_cast<const uint8_t*>(a->slot_scales);
     d->w_scales = static_cast<const uint8_t*>(a->w13_scales);
     d->amap = a->amap, d->counts = a->counts, d->g2 = a->g1, d->a2_inv = a->a2_inv;
@@ -700,7 +708,7 @@ int dlm_rowpar_bf16_loopback(const DlmGemm* gemm, const DlmComm* comm, int nrank
         if (gemm[i].m != gemm[0].m || gemm[i].n != gemm[0].n || gemm[i].k != gemm[0].k) return DLM_ERR_SHAPE;
         int cap = comm[0].max_ctas > 0 && comm[0].max_ctas < per_rank ? comm[0].max_ctas : per_rank;
         int gi = 0;
-        rc = fill_gemm(&p.g[i], &gemm[i], cap, per_rank, &gi, comm[i].rows / comm[i].world, comm[i].world == 1);
+        rc = fill_gemm(&p.g[i], &gemm[i], cap, per_rank, &gi, comm[i].rows / comm[i].world, comm[i].world == 1, false);
         if (rc != DLM_OK) return rc;
         if (i > 0 && gi != grid) return DLM_ERR_SHAPE;
         grid = gi;

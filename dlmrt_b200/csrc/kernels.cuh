@@ -16,6 +16,7 @@ constexpr int kMaxTiles = 128;      // (feature tiles) x (token tiles) of one GE
 constexpr int kWorkspaceHeader = 2048;  // int32 gen[256] then int32 counters[2][128]
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 200 * 1024;
+constexpr int kLeanRingBytes = 110 * 1024;  // ring of a kernel that shares an SM with the next launch's blocks
 constexpr long long kDefaultTimeoutNs = 30000000000ll;  // budget of a device wait when the caller passes 0 (tp_comm.cu:67-70: ~30 s)
 
 // The GEMM half of one rank. `out` is used by the plain GEMM (no communication) only.
@@ -29,6 +30,7 @@ struct alignas(64) GemmDev {
     __nv_bfloat16* out;
     long long ldo;
     int m, n, k, splits, token_tiles, stages;
+    int lean;          // the half-SM variant of the kernel (see rowpar_kernel)
 };
 
 template <int NR>
@@ -49,7 +51,7 @@ struct alignas(64) MoeDev {
     CUtensorMap tm_w;         // W2 codes as bytes [e_local * n, f / 2], box 128 B x 128 rows, 128-byte swizzle
     const uint8_t* w_tiles;   // or: the codes pre-tiled [e_local][n / 128][ceil(f / 256)][16 KB], each tile 128 rows x 128
                               // bytes already in the swizzled shared-memory order (zero-padded along f)
-    const uint8_t* a_codes;   // activation codes [e_local * m_max, f / 2]
+    CUtensorMap tm_a;         // activation codes [e_local * m_max, f / 2], box 128 B x 8 rows, 128-byte swizzle
     const uint8_t* a_scales;  // [e_local * m_max, f / 16] E4M3, linear
     const uint8_t* w_scales;  // [e_local][n / 128][f / 64][512] E4M3 in 128 x 4 atoms
     const int* amap;          // [e_total, m_max] pair index (token * top_k + k) of each expert's slots
@@ -122,8 +124,7 @@ int launch_route_packed(const RouteDev& p, const LaunchOpts& o);
 int moe_stage_bytes(int rows_cap);
 int moe_stages(int rows_cap);
 int rowpar_smem_bytes(int m, int stages);
-int rowpar_stages(int m);
-int rowpar_max_ctas_per_sm(int m);
+int rowpar_stages(int m, bool lean);
 
 extern int g_last_cuda_error;
 extern long long g_launches;

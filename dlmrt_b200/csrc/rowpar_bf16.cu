@@ -32,6 +32,7 @@ struct SmemLayout {
     uint64_t acc_full;
     uint32_t tmem_base;
     int epoch, gen, failed;  // epochs[block], gen[block] and status[0], fetched by a spare warp while the pipeline runs
+    int progress[3];         // k-blocks requested by the producer and seen to arrive by each of the two issuers
     float scratch[64];
 };
 
@@ -46,15 +47,14 @@ __device__ __forceinline__ uint32_t tmem_cols(int m) {
 }  // namespace
 
 // Owner phase of a single rank whose K was split: CTA `block` owns rows block, block + blocks, ... and takes them two
-// at a time (their loads and block-wide sums overlap). For each it waits until every CTA of the row's token tile has
+// at a time (kRows = 2: their loads and block-wide sums overlap; the lean kernel has no registers for that). For each it waits until every CTA of the row's token tile has
 // announced its partial tile, sums the row's FP32 split partials in split order, rounds to BF16 (that is the rank's
 // partial, as the push path would have stored it) and finishes the row as any owner does. Thread t < n / 8 holds
 // columns [8t, 8t + 8): feature tile t / 16, 32 bytes of that tile's row. `scratch`: 64 floats.
-template <int MODE>
+template <int MODE, int kRows>
 __device__ __forceinline__ void own_rows_from_splits(const GemmDev& g, const CommDev& c, const CommCtx& x,
                                                      const int* counter, int mt, float* scratch) {
-    constexpr int kRows = 2;
-    constexpr int kGroup = 3;  // splits whose loads are in flight together (per row)
+    constexpr int kGroup = kRows == 2 ? 3 : 2;  // splits whose loads are in flight together (per row)
     const int t = threadIdx.x;
     const int threads = c.n / kVec;
     const bool active = t < threads;
@@ -93,7 +93,7 @@ __device__ __forceinline__ void own_rows_from_splits(const GemmDev& g, const Com
                         asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter + tt) : "memory");
                         if (seen >= expected) break;
                         if (globaltimer() > x.deadline) {
-                            report(c.status, kErrTimeout, tt, kPhasePipeline, 3);
+                            report(c.status, kErrTimeout, tt, kPhasePipeline, 3 << 24);
                             arrived_all = false;
                             break;
                         }
@@ -153,8 +153,12 @@ __device__ __forceinline__ void own_rows_from_splits(const GemmDev& g, const Com
 // already bandwidth-bound when the CTA starts.
 __device__ __forceinline__ bool prefetch_rest_of_slab(int mt) { return mt <= 128; }
 
-template <int NR>
-__global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_constant__ RowparParams<NR> p) {
+// LEAN: the kernel is held to half an SM (80 registers, a ring of at most kLeanRingBytes), so that under programmatic
+// dependent launch the blocks of the NEXT launch are resident, with their barriers set up and their first weight tiles
+// loaded, while this launch is still in its reduction phases: the kernel boundary then costs ~1.8 us instead of ~4 us.
+// The price is an owner phase that takes one row at a time, so the host picks it only where a block owns at most one row.
+template <int NR, bool LEAN>
+__global__ void __launch_bounds__(kFusedThreads, LEAN ? 2 : 1) rowpar_kernel(const __grid_constant__ RowparParams<NR> p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const int slot = NR == 1 ? 0 : static_cast<int>(blockIdx.y);
     const GemmDev& g = p.g[slot];
@@ -221,6 +225,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
             for (int it = 0; it < pre; ++it)
                 tma_load_2d(tiles + it * stage_bytes + kTileBytesW, &g.tm_x, &sm->full[it], (kb0 + it) * kBlockK,
                             token0, kEvictLast);
+            sm->progress[0] = pre, sm->progress[1] = 0, sm->progress[2] = 0;
         }
         __syncwarp();  // the warp reaches the block-wide barrier together
     }
@@ -234,6 +239,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
     pdl_launch_dependents();
     // Budget of the local pipeline and of the split-K rendezvous; the cross-rank waits take theirs in comm_begin.
     const long long pipeline_deadline = globaltimer() + (c.timeout_ns > 0 ? c.timeout_ns : kDefaultTimeoutNs);
+    // What a pipeline wait that ran out puts in the status' last word: who gave up (0 producer, 1 issuer, 2 epilogue,
+    // 3 split-K rendezvous) and how many k-blocks the producer and each issuer had got through.
+    auto stalled = [&](int who) {
+        volatile int* pr = sm->progress;
+        return who << 24 | (pr[0] & 255) << 16 | (pr[1] & 255) << 8 | (pr[2] & 255);
+    };
 
     if (warp == 0) {
         if (lane == 0) {
@@ -241,7 +252,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
             uint32_t parity = 0;  // second lap of the ring waits for the first release of each stage
             for (int it = pre; it < iters; ++it) {
                 if (!mbar_wait(&sm->empty[st], parity, pipeline_deadline)) {
-                    report(c.status, kErrTimeout, st, kPhasePipeline, 0);
+                    report(c.status, kErrTimeout, st, kPhasePipeline, stalled(0));
                     break;
                 }
                 uint8_t* stage = tiles + st * stage_bytes;
@@ -252,6 +263,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
                 else
                     tma_load_2d(stage, &g.tm_w, &sm->full[st], (kb0 + it) * kBlockK, f * kBlockF, kEvictFirst);
                 tma_load_2d(stage + kTileBytesW, &g.tm_x, &sm->full[st], (kb0 + it) * kBlockK, token0, kEvictLast);
+                sm->progress[0] = it + 1;
                 if (++st == g.stages) st = 0, parity ^= 1;
             }
         }
@@ -261,6 +273,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
         // descriptors, four MMAs, commit per k-block) is slower than the MMAs it issues, so tiles of up to 128 tokens
         // get a second issuer with its own accumulator: warp 1 takes the even k-blocks, warp 3 the odd ones, and the
         // epilogue adds the two accumulators.
+        // A parity wait tells a barrier's phases apart only if the waiter is never a whole phase behind. With an odd
+        // number of stages the two issuers alternate on every stage, so before an issuer waits for k-block `it` it makes
+        // sure the other one has seen k-block `it - stages` arrive (the same stage's previous phase): each publishes
+        // the k-blocks it has seen in shared memory. The loads of `it` cannot have been requested before that anyway.
         const int who = warp == 1 ? 0 : 1;
         if (lane == 0) {
             if (who == 1) {
@@ -270,17 +286,28 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
             }
             if (who < issuers) {
                 const uint32_t idesc = umma_idesc_bf16(kBlockF, mt);
+                const uint32_t acc = tmem + who * cols;
+                volatile int* seen = sm->progress + 1;  // k-blocks each issuer has seen arrive
                 const uint64_t desc_hi = umma_desc_k128(tiles) & 0xFFFFFFFF00000000ull;
                 const uint32_t stage0 = smem_u32(tiles);
-                const uint32_t acc = tmem + who * cols;
                 int st = 0;
                 uint32_t parity = 0;
                 for (int it = 0; it < iters; ++it) {
                     if ((it & (issuers - 1)) == who) {
-                        if (!mbar_wait(&sm->full[st], parity, pipeline_deadline)) {
-                            report(c.status, kErrTimeout, st, kPhasePipeline, 1);
+                        bool ok = true;
+                        if (it >= g.stages && ((it - g.stages) & (issuers - 1)) != who) {
+                            while (seen[1 - who] <= it - g.stages) {
+                                if (globaltimer() > pipeline_deadline) {
+                                    ok = false;
+                                    break;
+                                }
+                            }
+                        }
+                        if (!ok || !mbar_wait(&sm->full[st], parity, pipeline_deadline)) {
+                            report(c.status, kErrTimeout, st, kPhasePipeline, stalled(1));
                             break;
                         }
+                        seen[who] = it + 1;
                         tcgen05_fence_after();
                         const uint32_t base = stage0 + st * stage_bytes;
                         const uint64_t dw = desc_hi | ((base & 0x3FFFF) >> 4);
@@ -305,7 +332,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
         bool ok = true;
         if (iters > 0) {
             ok = mbar_wait(&sm->acc_full, 0, pipeline_deadline);
-            if (!ok) report(c.status, kErrTimeout, 0, kPhasePipeline, 2);
+            if (!ok) report(c.status, kErrTimeout, 0, kPhasePipeline, stalled(2));
             tcgen05_fence_after();
         }
         if (c.stamps && threadIdx.x == 128) c.stamps[block * kStampSlots + 4] = globaltimer();
@@ -381,7 +408,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
                 asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
                 if (seen >= g.splits) break;
                 if (globaltimer() > pipeline_deadline) {
-                    report(c.status, kErrTimeout, s, kPhasePipeline, 3);
+                    report(c.status, kErrTimeout, s, kPhasePipeline, 3 << 24);
                     break;
                 }
             } while (true);
@@ -446,20 +473,21 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
         rearm_early(c, x);
         if (local_rows) {
             const int* counter = g.counters + ((sm->gen + 1) & 1) * kMaxTiles;
-            if (c.mode == kReduce) own_rows_from_splits<kReduce>(g, c, x, counter, mt, sm->scratch);
-            else if (c.mode == kReduceNorm) own_rows_from_splits<kReduceNorm>(g, c, x, counter, mt, sm->scratch);
-            else own_rows_from_splits<kReduceNormResidual>(g, c, x, counter, mt, sm->scratch);
+            constexpr int kRows = LEAN ? 1 : 2;
+            if (c.mode == kReduce) own_rows_from_splits<kReduce, kRows>(g, c, x, counter, mt, sm->scratch);
+            else if (c.mode == kReduceNorm) own_rows_from_splits<kReduceNorm, kRows>(g, c, x, counter, mt, sm->scratch);
+            else own_rows_from_splits<kReduceNormResidual, kRows>(g, c, x, counter, mt, sm->scratch);
             rearm_late(c, x);
         } else {
-            own_and_collect(c, x, sm->scratch);  // re-arms late shares between its own and collect phases
+            own_and_collect<!LEAN>(c, x, sm->scratch);  // re-arms late shares between its own and collect phases
         }
         comm_end(c, x);
     }
 }
 
-int rowpar_stages(int m) {  // m: tokens per tile
+int rowpar_stages(int m, bool lean) {  // m: tokens per tile
     const int stage = kTileBytesW + m * kBlockK * 2;
-    int stages = kSmemBudget / stage;  // the ring takes what an SM has
+    int stages = (lean ? kLeanRingBytes : kSmemBudget) / stage;  // the ring takes what (half of) an SM has
     if (stages > kMaxStages) stages = kMaxStages;
     return stages;
 }
@@ -468,7 +496,7 @@ int rowpar_smem_bytes(int m, int stages) {
     return stages * (kTileBytesW + m * kBlockK * 2) + static_cast<int>(sizeof(SmemLayout)) + 1024;
 }
 
-template <int NR>
+template <int NR, bool LEAN>
 static int launch_impl(const RowparParams<NR>& p, dim3 grid, const LaunchOpts& o) {
     const int smem = rowpar_smem_bytes(p.g[0].m / p.g[0].token_tiles, p.g[0].stages);
     // Raised once per device to the largest configuration (not a stream operation, but kept out of graph captures).
@@ -477,8 +505,11 @@ static int launch_impl(const RowparParams<NR>& p, dim3 grid, const LaunchOpts& o
     int dev = 0;
     (void)cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !raised[dev]) {
-        err = cudaFuncSetAttribute(rowpar_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   rowpar_smem_bytes(256, rowpar_stages(256)));
+        err = cudaFuncSetAttribute(rowpar_kernel<NR, LEAN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (LEAN ? kLeanRingBytes : kSmemBudget) + static_cast<int>(sizeof(SmemLayout)) + 1024);
+        if (err == cudaSuccess && LEAN)  // two blocks per SM need the whole shared-memory carve-out
+            err = cudaFuncSetAttribute(rowpar_kernel<NR, LEAN>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                       cudaSharedmemCarveoutMaxShared);
         raised[dev] = err == cudaSuccess;
     }
     if (err == cudaSuccess) {
@@ -501,7 +532,7 @@ static int launch_impl(const RowparParams<NR>& p, dim3 grid, const LaunchOpts& o
         }
         config.attrs = attrs;
         config.numAttrs = n;
-        err = cudaLaunchKernelEx(&config, rowpar_kernel<NR>, p);
+        err = cudaLaunchKernelEx(&config, rowpar_kernel<NR, LEAN>, p);
     }
     if (err != cudaSuccess) {
         g_last_cuda_error = static_cast<int>(err);
@@ -512,21 +543,12 @@ static int launch_impl(const RowparParams<NR>& p, dim3 grid, const LaunchOpts& o
     return 0;
 }
 
-int launch_rowpar(const RowparParams<1>& p, int grid, const LaunchOpts& o) { return launch_impl<1>(p, dim3(grid), o); }
-
-int launch_rowpar_loopback(const RowparParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o) {
-    return launch_impl<kMaxWorld>(p, dim3(grid, nranks), o);
+int launch_rowpar(const RowparParams<1>& p, int grid, const LaunchOpts& o) {
+    return p.g[0].lean ? launch_impl<1, true>(p, dim3(grid), o) : launch_impl<1, false>(p, dim3(grid), o);
 }
 
-int rowpar_max_ctas_per_sm(int m) {
-    int n = 0;
-    const int smem = rowpar_smem_bytes(m, rowpar_stages(m));
-    if (cudaFuncSetAttribute(rowpar_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, rowpar_kernel<1>, kFusedThreads, smem) != cudaSuccess) {
-        (void)cudaGetLastError();
-        return 1;
-    }
-    return n < 1 ? 1 : n;
+int launch_rowpar_loopback(const RowparParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o) {
+    return launch_impl<kMaxWorld, false>(p, dim3(grid, nranks), o);
 }
 
 }  // namespace dlm

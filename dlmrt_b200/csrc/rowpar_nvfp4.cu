@@ -13,9 +13,9 @@
 // Work item = (active local expert, 128 output features): W2's [128 x F] slab sits on the MMA's M axis, the expert's
 // rows (tokens routed to it, padded to 16) on its N axis. Persistent CTAs take items round-robin:
 //   warp 0   TMA: per 256-element k-block the 16 KB code slab of W2 (one bulk copy of a pre-tiled slab, or one box)
-//   warp 3   loader of the small operands: the expert's activation rows (a few rows of 128 bytes, swizzled in place),
-//            W2's pre-interleaved 128 x 4 scale atoms and the activation rows' linear E4M3 scales rewritten into the
-//            same atom layout, all by asynchronous copies into the stage
+//            and the expert's activation rows (boxes of 8 rows)
+//   warp 3   scale loader: W2's pre-interleaved 128 x 4 scale atoms and the activation rows' linear E4M3 scales,
+//            rewritten into the same atom layout, into the stage
 //   warp 1   per k-block: tcgen05.cp the scale atoms into tensor memory, then up to four
 //            tcgen05.mma.kind::mxf4nvf4.block_scale (K = 64) into the FP32 accumulator
 //   warps 4-11  per item: tcgen05.ld, times g2, BF16, scatter rows to Y[pair] through the expert's slot map
@@ -37,6 +37,7 @@ namespace {
 
 constexpr int kMoeThreads = kFusedThreads;
 constexpr int kCodeTileW = 128 * 128;  // 128 rows x 128 bytes (256 FP4) of W2 codes
+constexpr int kBoxRows = 8;            // activation rows per TMA box (one 1 KB swizzle atom)
 constexpr int kAtom = 512;             // one 128-row x 4-scale atom
 constexpr int kStepsPerBlock = 4;      // K = 64 instructions per 256-element k-block
 constexpr int kItemRows = 128;         // rows of one work item: the MMA's N; experts with more rows take several items
@@ -53,6 +54,7 @@ struct MoeSmem {
     uint64_t acc_empty[2];
     uint32_t tmem_base;
     int n_active, epoch, gen, failed;
+    int seen[2];  // k-blocks (counted over this CTA's items) each issuer has seen arrive
     int warp_count[8];
     float scratch[64];
     short active[kMaxEntries];  // expert | row block << 8
@@ -214,6 +216,8 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
         }
         fence_barrier_init();
         tma_prefetch_descriptor(&g.tm_w);
+        tma_prefetch_descriptor(&g.tm_a);
+        sm->seen[0] = sm->seen[1] = 0;
     }
     if (warp == 2) tmem_alloc(&sm->tmem_base, kTmemCols);
     // The next kernel of the stream may be set up from now on (its blocks move in as this kernel's blocks leave).
@@ -283,6 +287,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
             uint32_t phase = 1;  // waiting for parity 1 on a fresh barrier returns at once: the first lap is free
             for (int i = block; i < n_items; i += blocks) {
                 const Item t = item_of(i);
+                const int boxes = (t.cnt + kBoxRows - 1) / kBoxRows;
                 for (int kb = 0; kb < nkb; ++kb) {
                     if (!mbar_wait(&sm->empty[st], phase, deadline)) {
                         report(c.status, kErrTimeout, st, kPhasePipeline, 0);
@@ -290,24 +295,23 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
                         break;
                     }
                     uint8_t* stage = tiles + st * stage_bytes;
-                    mbar_expect_tx(&sm->full[st], static_cast<uint32_t>(kCodeTileW));
+                    mbar_expect_tx(&sm->full[st], static_cast<uint32_t>(kCodeTileW + boxes * kBoxRows * 128));
                     if (g.w_tiles)  // one contiguous 16 KB run of HBM, already in the swizzled shared-memory order
                         bulk_load(stage, g.w_tiles + (static_cast<size_t>(t.e * feature_tiles + t.ft) * nkb + kb) * kCodeTileW,
                                   kCodeTileW, &sm->full[st], kEvictFirst);
                     else
                         tma_load_2d(stage, &g.tm_w, &sm->full[st], kb * 128, t.e * g.n + t.ft * kBlockF, kEvictFirst);
+                    for (int b = 0; b < boxes; ++b)
+                        tma_load_2d(stage + off_a + b * kBoxRows * 128, &g.tm_a, &sm->full[st], kb * 128,
+                                    t.e * g.m_max + t.row0 + b * kBoxRows, kEvictLast);
                     if (++st == g.stages) st = 0, phase ^= 1;
                 }
             }
         }
         __syncwarp();  // lanes 1-31 must not run ahead to the block-wide barrier while lane 0 is still issuing
     } else if (warp == 3) {
-        // Loader of everything small: the scale atoms of both operands and the expert's activation rows (a few rows of
-        // 128 bytes per k-block; as tensor copies they cost the producer thread one instruction per eight rows and
-        // k-block, which is what set the pace of the weight stream). Asynchronous 16- and 4-byte copies straight into
-        // place, so the warp never waits for data and runs as far ahead as the ring allows. Activation row r goes to
-        // byte offset r * 128 of the tile with its 16-byte chunk c at position c ^ (r % 8) (the 128-byte swizzle the
-        // tensor copies would have applied); atom byte (r % 32) * 16 + (r / 32) * 4 + j holds scale j of row r (< 128).
+        // Scale loader: asynchronous copies straight into the atoms, so it never waits for data and runs as far ahead
+        // as the ring allows. Atom byte (r % 32) * 16 + (r / 32) * 4 + j holds scale j of row r (< 128).
         const int last_slot = g.e_local * g.m_max - 1;
         int st = 0;
         uint32_t phase = 1;
@@ -332,14 +336,6 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
                     uint8_t* dst = stage + off_sfb + (r % 32) * 16 + (r / 32) * 4;
                     for (int s2 = 0; s2 < nsteps; ++s2) cp_async_4(dst + s2 * kAtom, src + s2 * 4);
                 }
-                // Two 16-byte chunks per K = 64 step; chunks past the row's end (a last k-block that f does not fill)
-                // belong to steps that are never issued.
-                for (int v = lane; v < rows * 2 * nsteps; v += 32) {
-                    const int r = v / (2 * nsteps), ch = v - r * 2 * nsteps;
-                    const int srow = min(t.e * g.m_max + t.row0 + r, last_slot);
-                    cp_async_16(stage + off_a + r * 128 + ((ch ^ (r & 7)) << 4),
-                                g.a_codes + static_cast<size_t>(srow) * (g.f / 2) + kb * 128 + ch * 16);
-                }
                 cp_async_arrive(&sm->full[st]);
                 if (++st == g.stages) st = 0, phase ^= 1;
             }
@@ -356,12 +352,21 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
             const uint32_t stage0 = smem_u32(tiles);
             const uint64_t desc_hi = umma_desc_k128(tiles) & 0xFFFFFFFF00000000ull;     // swizzled operand tiles
             const uint64_t sf_hi = utccp_desc(tiles) & 0xFFFFFFFF00000000ull;           // scale atoms
-            int st = 0, set = 0, item = 0;
+            int st = 0, set = 0, item = 0, seq = 0;  // seq: this k-block's number in the CTA's sequence
             uint32_t phase = 0;
             bool alive = true;
+            // A parity wait tells a barrier's phases apart only while the waiter is never a whole phase behind, and an
+            // issuer skips the phases of the other's items. So before it waits for k-block `seq` it makes sure that
+            // k-block `seq - stages` (the same stage's previous phase) has been seen to arrive by whoever owns it; the
+            // two publish what they have seen in shared memory. That k-block belongs to the other issuer iff the
+            // number of items between the two is odd: (stages / nkb), or one more for the first stages % nkb k-blocks
+            // of an item.
+            const int q_items = g.stages / nkb, r_blocks = g.stages % nkb;
+            volatile int* seen = sm->seen;
             for (int i = block; i < n_items && alive; i += blocks, ++item) {
                 if ((item & 1) != who) {  // the other issuer's item: only step over its k-blocks in the ring
                     st += nkb;
+                    seq += nkb;
                     while (st >= g.stages) st -= g.stages, phase ^= 1;
                     continue;
                 }
@@ -373,12 +378,16 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
                     report(c.status, kErrTimeout, 0, kPhasePipeline, 4);
                     break;
                 }
-                for (int kb = 0; kb < nkb; ++kb) {
-                    if (!mbar_wait(&sm->full[st], phase, deadline)) {
+                for (int kb = 0; kb < nkb; ++kb, ++seq) {
+                    if (seq >= g.stages && ((kb >= r_blocks ? q_items : q_items + 1) & 1)) {
+                        while (alive && seen[1 - who] <= seq - g.stages) alive = globaltimer() <= deadline;
+                    }
+                    if (!alive || !mbar_wait(&sm->full[st], phase, deadline)) {
                         report(c.status, kErrTimeout, st, kPhasePipeline, 1);
                         alive = false;
                         break;
                     }
+                    seen[who] = seq + 1;
                     fence_proxy_async();  // the scale atoms were written through the generic proxy
                     tcgen05_fence_after();
                     const uint32_t base = stage0 + st * stage_bytes;

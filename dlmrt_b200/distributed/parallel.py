@@ -365,8 +365,12 @@ class Group:
         _lib.check(_lib.lib().dlm_status_read(self.status.data_ptr(), C.byref(st), stream), "status")
         if st.code:
             self._failed = True
-            raise TimeoutError(f"rank {self.rank}: {_lib.lib().dlm_strerror(st.code).decode()} (block {st.block}, "
-                               f"rank slot {st.slot}, phase {st.phase}, invocation {st.epoch})")
+            where = f"rank slot {st.slot}, phase {st.phase}, invocation {st.epoch}"
+            if st.phase == 3 and st.epoch >> 24:  # the dense kernel's own pipeline: who gave up, and how far it had got
+                who = ("producer", "MMA issuer", "epilogue", "split-K rendezvous")[(st.epoch >> 24) & 3]
+                where = (f"pipeline stage or split {st.slot}: {who} gave up; k-blocks loaded {st.epoch >> 16 & 255}, "
+                         f"issued {st.epoch >> 8 & 255} / {st.epoch & 255}")
+            raise TimeoutError(f"rank {self.rank}: {_lib.lib().dlm_strerror(st.code).decode()} (block {st.block}, {where})")
 
     def all_reduce_(self, x):
         """The reference's UNFUSED switch (DLMRT_TP_FUSED=0, parallel.py:154-162), kept so model code that still calls

@@ -72,6 +72,27 @@ def test_gemm_within_tolerance_on_gaussian_operands(m, n, k):
     assert rel.max() <= 2 * rel_cublas.max() + 1e-6
 
 
+@pytest.mark.parametrize("m, n, k, token_tiles, splits", [(256, 2560, 4864, 2, 3), (96, 512, 2048, 1, 1), (64, 2560, 2048, 2, 1),
+                                                          (256, 2560, 2048, 2, 3)])
+def test_two_issuers_on_a_ring_with_an_odd_number_of_stages(m, n, k, token_tiles, splits):
+    """Tiles of up to 128 tokens have two MMA-issuing threads that take alternate k-blocks. On a ring with an odd number
+    of stages (3 for 128-token tiles of the half-SM kernel, 5 for 32-token ones) they alternate on every stage, and
+    each may only wait for a stage's barrier once the other has seen that stage's previous phase complete: without
+    that, back-to-back launches of the first shape raised a launch failure. Exact on integer operands."""
+    from dlmrt_b200.layers.linear import Linear
+
+    x, w = integer_case(m, n, k, seed=21)
+    want = f32_to_bf16(rowpar.gemm_f32(bits(x), bits(w)))
+    lins = [Linear(w, token_tiles=token_tiles, splits=splits) for _ in range(3)]
+    outs = [torch.empty(m, n, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    for _ in range(10):
+        for lin, out in zip(lins, outs):
+            lin.gemm(x, out)
+    torch.cuda.synchronize()
+    for i, out in enumerate(outs):
+        assert_same_bits(bits(out), want, f"launch chain {i}")
+
+
 @pytest.mark.parametrize("splits", [1, 2, 3, 8])
 def test_gemm_split_k_is_deterministic_and_ordered(splits):
     m, n, k = 64, 256, 2048
