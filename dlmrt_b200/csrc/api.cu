@@ -232,10 +232,10 @@ int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid, in
     d->splits = splits;
     d->token_tiles = token_tiles;
     *grid = tiles * splits;
-    // The half-SM kernel where (nearly) no block owns more than one row of the reduction and its shorter ring still
-    // covers the block's k-blocks or holds three stages.
+    // The half-SM kernel where no block owns more than one row of the reduction and its shorter ring still covers the
+    // block's k-blocks or holds three stages.
     const int lean_stages = rowpar_stages(mt, true), kb = (nkb + splits - 1) / splits;
-    d->lean = solo && owner_rows <= *grid + *grid / 8 && (lean_stages >= 3 || lean_stages >= kb);
+    d->lean = solo && owner_rows <= *grid && (lean_stages >= 3 || lean_stages >= kb);
     d->stages = rowpar_stages(mt, d->lean != 0);
     return DLM_OK;
 }

@@ -425,26 +425,40 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
         // Epilogue: lane = output feature of the tile, registers = the expert's rows.
         const int quarter = warp & 3, half = (warp - 4) >> 2;
         int item = 0;
-        for (int i = block; i < n_items; i += blocks, ++item) {
+        // What an item's epilogue needs from global memory: the expert's scale(s) and, for the down-projection, for each
+        // of this warp's 16-row chunks (at most four) the destination row of lane % 16's accumulator column. Fetched
+        // one item AHEAD: the epilogue warps go from item to item without a pause when the stream runs well, and a
+        // round trip to L2 per item would then set the pace of the whole CTA.
+        struct Meta {
+            float g2, a2i;
+            int dest[4];
+        };
+        auto fetch = [&](int i) {
+            Meta m{0.f, 0.f, {-1, -1, -1, -1}};
+            if (i >= n_items) return m;
             const Item t = item_of(i);
-            const int n_mma = max(16, (t.cnt + 15) & ~15);
-            const int buf = item & 1;
-            // Issued before the wait so that their latency overlaps the item's MMAs: the expert's scale(s) and, for the
-            // down-projection, for each of this warp's 16-row chunks (at most four) the destination row of lane % 16's
-            // accumulator column.
-            const float g2 = g.g2[t.e];
-            float a2i = 0.f;
-            int dest[4] = {-1, -1, -1, -1};
+            m.g2 = g.g2[t.e];
             if (GATE_UP) {
-                a2i = g.a2_inv[t.e];
+                m.a2i = g.a2_inv[t.e];
             } else {
                 const int* slots = g.amap + static_cast<size_t>(g.lo + t.e) * g.m_max + t.row0;
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const int row = (half + 2 * q) * 16 + (lane & 15);
-                    dest[q] = row < t.cnt ? slots[row] : -1;
+                    m.dest[q] = row < t.cnt ? slots[row] : -1;
                 }
             }
+            return m;
+        };
+        Meta next = fetch(block);
+        for (int i = block; i < n_items; i += blocks, ++item) {
+            const Item t = item_of(i);
+            const int n_mma = max(16, (t.cnt + 15) & ~15);
+            const int buf = item & 1;
+            const Meta cur = next;
+            next = fetch(i + blocks);
+            const float g2 = cur.g2, a2i = cur.a2i;
+            const int(&dest)[4] = cur.dest;
             const bool ok = mbar_wait(&sm->acc_full[buf], (item >> 1) & 1, deadline);
             if (!ok) report(c.status, kErrTimeout, 0, kPhasePipeline, 2);
             tcgen05_fence_after();
