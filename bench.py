@@ -424,25 +424,28 @@ STAMP_NAMES = {7: "kernel entry", 5: "dependency released", 4: "accumulator read
 def timeline(rig, step, group, layers=(3, 4)):
     """Phase stamps (%globaltimer, written by thread 0 of every CTA when the caller passes a stamp buffer) of the two
     fused launches of a few layers inside a graph replay: per phase the median and maximum over CTAs, in microseconds
-    after the launch's first CTA entered; `next_entry` is when the first CTA of the following launch entered. Plain
+    after the median CTA of the launch entered; `next_entry` is when the following launch's median CTA entered. Plain
     run, no profiler."""
     import numpy as np
 
     torch = rig.torch
     sms = rig.lib.dlm_device_sms()
-    bufs, order = {}, []
+    # The stamp buffers exist before the capture: a tensor created while capturing would put a fill kernel into the
+    # graph in front of the stamped launch, and that launch would then not be a programmatic dependent of its neighbour.
+    sites = {}
+    for layer in layers:
+        sites[f"{layer}.post"] = (layer, "o_proj")
+        sites[f"{layer + 1}.input"] = (layer, "down_proj")
+    bufs = {key: torch.zeros(sms * 8, dtype=torch.int64, device=rig.device) for key in sites.values()}
+    order = []
     original = group._comm
 
     def comm(rows, n, site, *a, **kw):
         c, out = original(rows, n, site, *a, **kw)
-        for layer in layers:
-            for k, name in enumerate((f"{layer}.post", f"{layer + 1}.input")):
-                if site == name:
-                    key = (layer, "o_proj" if k == 0 else "down_proj")
-                    if key not in bufs:
-                        bufs[key] = torch.zeros(sms * 8, dtype=torch.int64, device=rig.device)
-                        order.append(key)
-                    c.stamps = bufs[key].data_ptr()
+        if site in sites:
+            if sites[site] not in order:
+                order.append(sites[site])
+            c.stamps = bufs[sites[site]].data_ptr()
         return c, out
 
     group._comm = comm
@@ -462,9 +465,12 @@ def timeline(rig, step, group, layers=(3, 4)):
     report, entries = {}, {}
     for key in order:
         s = bufs[key].cpu().numpy().reshape(sms, 8)
-        t0 = int(s[:, 7][s[:, 7] > 0].min())
+        # Blocks that found an idle SM enter as soon as the previous launch has triggered its dependents, long before
+        # the rest; the launch's clock starts when the bulk of its blocks is in (the median entry).
+        enter = s[:, 7][s[:, 7] > 0]
+        t0 = int(np.median(enter))
         entries[key] = t0
-        phases = {"ctas": int((s[:, 7] > 0).sum())}
+        phases = {"ctas": int((s[:, 7] > 0).sum()), "first block entered": round(float(enter.min() - t0) / 1e3, 2)}
         for slot, name in STAMP_NAMES.items():
             v = s[:, slot]
             v = v[v > 0] - t0
@@ -570,7 +576,7 @@ def parity_block(rig):
             return np.where(x & 0x8000, -(x & 0x7FFF), x & 0x7FFF)
         return np.abs(key(a) - key(b))
 
-    def verdict(name, out, want, exact=True):
+    def record(name, out, want, exact=True):
         torch.cuda.synchronize(device)
         group.check()
         mine = bits(out)
@@ -601,11 +607,11 @@ def parity_block(rig):
                 p = lin(xs, out=group.partial("parity", (ROWS, HIDDEN)))
                 if name == "o_proj":
                     out = group.reduce(p, site=f"parity.{layer}.o")
-                    verdict(f"fused {name} K1 layer {layer}", out, red.reduce(parts))
+                    record(f"fused {name} K1 layer {layer}", out, red.reduce(parts))
                 else:
                     out = group.reduce_norm(p, h, norm, EPS, site=f"parity.{layer}.d")
                     want, h_after = red.reduce_norm(parts, bits(norm), EPS, 1.0, h_all)
-                    verdict(f"fused {name} K3 layer {layer}", out, want, exact=False)
+                    record(f"fused {name} K3 layer {layer}", out, want, exact=False)
                     ok = np.array_equal(bits(h), h_after[rank])
                     result["vs_oracle"] &= bool(ok)
                     result["checked"].append(f"residual stream after layer {layer}" + ("" if ok else ": FAILED"))
@@ -629,14 +635,14 @@ def parity_block(rig):
             h_ref = h.clone()
             if mode == 0:
                 out = group.reduce(p, site=f"parity.g{mode}")
-                verdict("given partials K1", out, red.reduce(all_p))
+                record("given partials K1", out, red.reduce(all_p))
             elif mode == 1:
                 out = group.reduce_norm(p, None, weight, EPS, 0.75, site=f"parity.g{mode}")
-                verdict("given partials K2", out, red.reduce_norm(all_p, bits(weight), EPS, 0.75)[0], exact=False)
+                record("given partials K2", out, red.reduce_norm(all_p, bits(weight), EPS, 0.75)[0], exact=False)
             else:
                 out = group.reduce_norm(p, h, weight, EPS, site=f"parity.g{mode}")
                 want, h_after = red.reduce_norm(all_p, bits(weight), EPS, 1.0, h_all)
-                verdict("given partials K3", out, want, exact=False)
+                record("given partials K3", out, want, exact=False)
                 result["vs_oracle"] &= bool(np.array_equal(bits(h), h_after[rank]))
             if ref is not None:
                 ref_partial.copy_(p)
@@ -657,7 +663,7 @@ def parity_block(rig):
         small = torch.randn(32, 2048, generator=torch.Generator().manual_seed(77 + rank)).to(torch.bfloat16).to(device)
         for rep in range(2):
             out = group.reduce(small, site=f"parity.small{rep}", chain=32)
-            verdict(f"32-row plain sum #{rep}" + (" (one hop)" if group.one_shot(32, 2048, 0) else ""), out,
+            record(f"32-row plain sum #{rep}" + (" (one hop)" if group.one_shot(32, 2048, 0) else ""), out,
                     red.reduce(np.stack([bits(t) for t in gather(small)])))
         stats = torch.randn(32, 4, generator=torch.Generator().manual_seed(88 + rank)).to(device)
         for rep in range(2):

@@ -193,10 +193,8 @@ int check_gemm(const DlmGemm* g) {
 }
 
 // Fills the device-side GEMM block; returns the per-rank grid in *grid.
-// `solo`: an ordinary launch of one rank's grid (not the cooperative several-ranks-on-one-GPU launch), which may use the
-// half-SM kernel.
 int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid, int owner_rows = 0,
-              bool single_rank = false, bool solo = true) {
+              bool single_rank = false) {
     std::memset(d, 0, sizeof(*d));
     const int avail = max_ctas > 0 && max_ctas < sms ? max_ctas : sms;
     const int feature_tiles = g->n / kBlockF, nkb = (g->k + kBlockK - 1) / kBlockK;
@@ -231,12 +229,8 @@ int fill_gemm(GemmDev* d, const DlmGemm* g, int max_ctas, int sms, int* grid, in
     d->k = g->k;
     d->splits = splits;
     d->token_tiles = token_tiles;
+    d->stages = rowpar_stages(mt);
     *grid = tiles * splits;
-    // The half-SM kernel where no block owns more than one row of the reduction and its shorter ring still covers the
-    // block's k-blocks or holds three stages.
-    const int lean_stages = rowpar_stages(mt, true), kb = (nkb + splits - 1) / splits;
-    d->lean = solo && owner_rows <= *grid && (lean_stages >= 3 || lean_stages >= kb);
-    d->stages = rowpar_stages(mt, d->lean != 0);
     return DLM_OK;
 }
 
@@ -708,7 +702,7 @@ int dlm_rowpar_bf16_loopback(const DlmGemm* gemm, const DlmComm* comm, int nrank
         if (gemm[i].m != gemm[0].m || gemm[i].n != gemm[0].n || gemm[i].k != gemm[0].k) return DLM_ERR_SHAPE;
         int cap = comm[0].max_ctas > 0 && comm[0].max_ctas < per_rank ? comm[0].max_ctas : per_rank;
         int gi = 0;
-        rc = fill_gemm(&p.g[i], &gemm[i], cap, per_rank, &gi, comm[i].rows / comm[i].world, comm[i].world == 1, false);
+        rc = fill_gemm(&p.g[i], &gemm[i], cap, per_rank, &gi, comm[i].rows / comm[i].world, comm[i].world == 1);
         if (rc != DLM_OK) return rc;
         if (i > 0 && gi != grid) return DLM_ERR_SHAPE;
         grid = gi;

@@ -16,7 +16,6 @@ constexpr int kMaxTiles = 128;      // (feature tiles) x (token tiles) of one GE
 constexpr int kWorkspaceHeader = 2048;  // int32 gen[256] then int32 counters[2][128]
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 200 * 1024;
-constexpr int kLeanRingBytes = 110 * 1024;  // ring of a kernel that shares an SM with the next launch's blocks
 constexpr long long kDefaultTimeoutNs = 30000000000ll;  // budget of a device wait when the caller passes 0 (tp_comm.cu:67-70: ~30 s)
 
 // The GEMM half of one rank. `out` is used by the plain GEMM (no communication) only.
@@ -30,7 +29,6 @@ struct alignas(64) GemmDev {
     __nv_bfloat16* out;
     long long ldo;
     int m, n, k, splits, token_tiles, stages;
-    int lean;          // the half-SM variant of the kernel (see rowpar_kernel)
 };
 
 template <int NR>
@@ -124,7 +122,7 @@ int launch_route_packed(const RouteDev& p, const LaunchOpts& o);
 int moe_stage_bytes(int rows_cap);
 int moe_stages(int rows_cap);
 int rowpar_smem_bytes(int m, int stages);
-int rowpar_stages(int m, bool lean);
+int rowpar_stages(int m);
 
 extern int g_last_cuda_error;
 extern long long g_launches;

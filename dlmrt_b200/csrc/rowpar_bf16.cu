@@ -47,14 +47,15 @@ __device__ __forceinline__ uint32_t tmem_cols(int m) {
 }  // namespace
 
 // Owner phase of a single rank whose K was split: CTA `block` owns rows block, block + blocks, ... and takes them two
-// at a time (kRows = 2: their loads and block-wide sums overlap; the lean kernel has no registers for that). For each it waits until every CTA of the row's token tile has
+// at a time (their loads and block-wide sums overlap). For each it waits until every CTA of the row's token tile has
 // announced its partial tile, sums the row's FP32 split partials in split order, rounds to BF16 (that is the rank's
 // partial, as the push path would have stored it) and finishes the row as any owner does. Thread t < n / 8 holds
 // columns [8t, 8t + 8): feature tile t / 16, 32 bytes of that tile's row. `scratch`: 64 floats.
-template <int MODE, int kRows>
+template <int MODE>
 __device__ __forceinline__ void own_rows_from_splits(const GemmDev& g, const CommDev& c, const CommCtx& x,
                                                      const int* counter, int mt, float* scratch) {
-    constexpr int kGroup = kRows == 2 ? 3 : 2;  // splits whose loads are in flight together (per row)
+    constexpr int kRows = 2;
+    constexpr int kGroup = 3;  // splits whose loads are in flight together (per row)
     const int t = threadIdx.x;
     const int threads = c.n / kVec;
     const bool active = t < threads;
@@ -153,12 +154,8 @@ __device__ __forceinline__ void own_rows_from_splits(const GemmDev& g, const Com
 // already bandwidth-bound when the CTA starts.
 __device__ __forceinline__ bool prefetch_rest_of_slab(int mt) { return mt <= 128; }
 
-// LEAN: the kernel is held to half an SM (80 registers, a ring of at most kLeanRingBytes), so that under programmatic
-// dependent launch the blocks of the NEXT launch are resident, with their barriers set up and their first weight tiles
-// loaded, while this launch is still in its reduction phases: the kernel boundary then costs ~1.8 us instead of ~4 us.
-// The price is an owner phase that takes one row at a time, so the host picks it only where a block owns at most one row.
-template <int NR, bool LEAN>
-__global__ void __launch_bounds__(kFusedThreads, LEAN ? 2 : 1) rowpar_kernel(const __grid_constant__ RowparParams<NR> p) {
+template <int NR>
+__global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_constant__ RowparParams<NR> p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const int slot = NR == 1 ? 0 : static_cast<int>(blockIdx.y);
     const GemmDev& g = p.g[slot];
@@ -473,21 +470,20 @@ __global__ void __launch_bounds__(kFusedThreads, LEAN ? 2 : 1) rowpar_kernel(con
         rearm_early(c, x);
         if (local_rows) {
             const int* counter = g.counters + ((sm->gen + 1) & 1) * kMaxTiles;
-            constexpr int kRows = LEAN ? 1 : 2;
-            if (c.mode == kReduce) own_rows_from_splits<kReduce, kRows>(g, c, x, counter, mt, sm->scratch);
-            else if (c.mode == kReduceNorm) own_rows_from_splits<kReduceNorm, kRows>(g, c, x, counter, mt, sm->scratch);
-            else own_rows_from_splits<kReduceNormResidual, kRows>(g, c, x, counter, mt, sm->scratch);
+            if (c.mode == kReduce) own_rows_from_splits<kReduce>(g, c, x, counter, mt, sm->scratch);
+            else if (c.mode == kReduceNorm) own_rows_from_splits<kReduceNorm>(g, c, x, counter, mt, sm->scratch);
+            else own_rows_from_splits<kReduceNormResidual>(g, c, x, counter, mt, sm->scratch);
             rearm_late(c, x);
         } else {
-            own_and_collect<!LEAN>(c, x, sm->scratch);  // re-arms late shares between its own and collect phases
+            own_and_collect(c, x, sm->scratch);  // re-arms late shares between its own and collect phases
         }
         comm_end(c, x);
     }
 }
 
-int rowpar_stages(int m, bool lean) {  // m: tokens per tile
+int rowpar_stages(int m) {  // m: tokens per tile
     const int stage = kTileBytesW + m * kBlockK * 2;
-    int stages = (lean ? kLeanRingBytes : kSmemBudget) / stage;  // the ring takes what (half of) an SM has
+    int stages = kSmemBudget / stage;  // the ring takes what an SM has
     if (stages > kMaxStages) stages = kMaxStages;
     return stages;
 }
@@ -496,7 +492,7 @@ int rowpar_smem_bytes(int m, int stages) {
     return stages * (kTileBytesW + m * kBlockK * 2) + static_cast<int>(sizeof(SmemLayout)) + 1024;
 }
 
-template <int NR, bool LEAN>
+template <int NR>
 static int launch_impl(const RowparParams<NR>& p, dim3 grid, const LaunchOpts& o) {
     const int smem = rowpar_smem_bytes(p.g[0].m / p.g[0].token_tiles, p.g[0].stages);
     // Raised once per device to the largest configuration (not a stream operation, but kept out of graph captures).
@@ -505,11 +501,8 @@ static int launch_impl(const RowparParams<NR>& p, dim3 grid, const LaunchOpts& o
     int dev = 0;
     (void)cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !raised[dev]) {
-        err = cudaFuncSetAttribute(rowpar_kernel<NR, LEAN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (LEAN ? kLeanRingBytes : kSmemBudget) + static_cast<int>(sizeof(SmemLayout)) + 1024);
-        if (err == cudaSuccess && LEAN)  // two blocks per SM need the whole shared-memory carve-out
-            err = cudaFuncSetAttribute(rowpar_kernel<NR, LEAN>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                       cudaSharedmemCarveoutMaxShared);
+        err = cudaFuncSetAttribute(rowpar_kernel<NR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   kSmemBudget + static_cast<int>(sizeof(SmemLayout)) + 1024);
         raised[dev] = err == cudaSuccess;
     }
     if (err == cudaSuccess) {
@@ -532,7 +525,7 @@ static int launch_impl(const RowparParams<NR>& p, dim3 grid, const LaunchOpts& o
         }
         config.attrs = attrs;
         config.numAttrs = n;
-        err = cudaLaunchKernelEx(&config, rowpar_kernel<NR, LEAN>, p);
+        err = cudaLaunchKernelEx(&config, rowpar_kernel<NR>, p);
     }
     if (err != cudaSuccess) {
         g_last_cuda_error = static_cast<int>(err);
@@ -543,12 +536,10 @@ static int launch_impl(const RowparParams<NR>& p, dim3 grid, const LaunchOpts& o
     return 0;
 }
 
-int launch_rowpar(const RowparParams<1>& p, int grid, const LaunchOpts& o) {
-    return p.g[0].lean ? launch_impl<1, true>(p, dim3(grid), o) : launch_impl<1, false>(p, dim3(grid), o);
-}
+int launch_rowpar(const RowparParams<1>& p, int grid, const LaunchOpts& o) { return launch_impl<1>(p, dim3(grid), o); }
 
 int launch_rowpar_loopback(const RowparParams<kMaxWorld>& p, int grid, int nranks, const LaunchOpts& o) {
-    return launch_impl<kMaxWorld, false>(p, dim3(grid, nranks), o);
+    return launch_impl<kMaxWorld>(p, dim3(grid, nranks), o);
 }
 
 }  // namespace dlm

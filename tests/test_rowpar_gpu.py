@@ -72,13 +72,13 @@ def test_gemm_within_tolerance_on_gaussian_operands(m, n, k):
     assert rel.max() <= 2 * rel_cublas.max() + 1e-6
 
 
-@pytest.mark.parametrize("m, n, k, token_tiles, splits", [(256, 2560, 4864, 2, 3), (96, 512, 2048, 1, 1), (64, 2560, 2048, 2, 1),
-                                                          (256, 2560, 2048, 2, 3)])
+@pytest.mark.parametrize("m, n, k, token_tiles, splits", [(256, 2560, 4864, 2, 3), (96, 512, 2048, 1, 1), (80, 2560, 2048, 1, 2),
+                                                          (160, 2560, 2048, 2, 3)])
 def test_two_issuers_on_a_ring_with_an_odd_number_of_stages(m, n, k, token_tiles, splits):
     """Tiles of up to 128 tokens have two MMA-issuing threads that take alternate k-blocks. On a ring with an odd number
-    of stages (3 for 128-token tiles of the half-SM kernel, 5 for 32-token ones) they alternate on every stage, and
-    each may only wait for a stage's barrier once the other has seen that stage's previous phase complete: without
-    that, back-to-back launches of the first shape raised a launch failure. Exact on integer operands."""
+    of stages (7 for 96- and 80-token tiles) they alternate on every stage, and each may only wait for a stage's barrier
+    once the other has seen that stage's previous phase complete; a kernel without that guard, on a 3-stage ring, raised
+    a launch failure on back-to-back launches of the first shape. Exact on integer operands."""
     from dlmrt_b200.layers.linear import Linear
 
     x, w = integer_case(m, n, k, seed=21)
