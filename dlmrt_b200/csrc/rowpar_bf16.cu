@@ -32,7 +32,7 @@ struct SmemLayout {
     uint64_t acc_full;
     uint32_t tmem_base;
     int epoch, gen, failed;  // epochs[block], gen[block] and status[0], fetched by a spare warp while the pipeline runs
-    int progress[3];         // k-blocks requested by the producer and seen to arrive by each of the two issuers
+    int seen[2];             // k-blocks each of two issuers has seen arrive (only kept on rings with an odd number of stages)
     float scratch[64];
 };
 
@@ -222,7 +222,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
             for (int it = 0; it < pre; ++it)
                 tma_load_2d(tiles + it * stage_bytes + kTileBytesW, &g.tm_x, &sm->full[it], (kb0 + it) * kBlockK,
                             token0, kEvictLast);
-            sm->progress[0] = pre, sm->progress[1] = 0, sm->progress[2] = 0;
+            sm->seen[0] = sm->seen[1] = 0;
         }
         __syncwarp();  // the warp reaches the block-wide barrier together
     }
@@ -237,19 +237,15 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
     // Budget of the local pipeline and of the split-K rendezvous; the cross-rank waits take theirs in comm_begin.
     const long long pipeline_deadline = globaltimer() + (c.timeout_ns > 0 ? c.timeout_ns : kDefaultTimeoutNs);
     // What a pipeline wait that ran out puts in the status' last word: who gave up (0 producer, 1 issuer, 2 epilogue,
-    // 3 split-K rendezvous) and how many k-blocks the producer and each issuer had got through.
-    auto stalled = [&](int who) {
-        volatile int* pr = sm->progress;
-        return who << 24 | (pr[0] & 255) << 16 | (pr[1] & 255) << 8 | (pr[2] & 255);
-    };
-
+    // 3 split-K rendezvous) and the k-block it was at.
+    auto stalled = [](int who, int it) { return who << 24 | (it & 0xFFFF); };
     if (warp == 0) {
         if (lane == 0) {
             int st = pre == g.stages ? 0 : pre;
             uint32_t parity = 0;  // second lap of the ring waits for the first release of each stage
             for (int it = pre; it < iters; ++it) {
                 if (!mbar_wait(&sm->empty[st], parity, pipeline_deadline)) {
-                    report(c.status, kErrTimeout, st, kPhasePipeline, stalled(0));
+                    report(c.status, kErrTimeout, st, kPhasePipeline, stalled(0, it));
                     break;
                 }
                 uint8_t* stage = tiles + st * stage_bytes;
@@ -260,7 +256,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
                 else
                     tma_load_2d(stage, &g.tm_w, &sm->full[st], (kb0 + it) * kBlockK, f * kBlockF, kEvictFirst);
                 tma_load_2d(stage + kTileBytesW, &g.tm_x, &sm->full[st], (kb0 + it) * kBlockK, token0, kEvictLast);
-                sm->progress[0] = it + 1;
                 if (++st == g.stages) st = 0, parity ^= 1;
             }
         }
@@ -284,7 +279,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
             if (who < issuers) {
                 const uint32_t idesc = umma_idesc_bf16(kBlockF, mt);
                 const uint32_t acc = tmem + who * cols;
-                volatile int* seen = sm->progress + 1;  // k-blocks each issuer has seen arrive
+                volatile int* seen = sm->seen;
+                const bool guarded = issuers == 2 && (g.stages & 1);  // see above; even rings need no hand-over
                 const uint64_t desc_hi = umma_desc_k128(tiles) & 0xFFFFFFFF00000000ull;
                 const uint32_t stage0 = smem_u32(tiles);
                 int st = 0;
@@ -292,7 +288,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
                 for (int it = 0; it < iters; ++it) {
                     if ((it & (issuers - 1)) == who) {
                         bool ok = true;
-                        if (it >= g.stages && ((it - g.stages) & (issuers - 1)) != who) {
+                        if (guarded && it >= g.stages) {  // k-block it - stages was the other issuer's
                             while (seen[1 - who] <= it - g.stages) {
                                 if (globaltimer() > pipeline_deadline) {
                                     ok = false;
@@ -301,10 +297,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
                             }
                         }
                         if (!ok || !mbar_wait(&sm->full[st], parity, pipeline_deadline)) {
-                            report(c.status, kErrTimeout, st, kPhasePipeline, stalled(1));
+                            report(c.status, kErrTimeout, st, kPhasePipeline, stalled(1, it));
                             break;
                         }
-                        seen[who] = it + 1;
+                        if (guarded) seen[who] = it + 1;
                         tcgen05_fence_after();
                         const uint32_t base = stage0 + st * stage_bytes;
                         const uint64_t dw = desc_hi | ((base & 0x3FFFF) >> 4);
@@ -329,7 +325,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) rowpar_kernel(const __grid_c
         bool ok = true;
         if (iters > 0) {
             ok = mbar_wait(&sm->acc_full, 0, pipeline_deadline);
-            if (!ok) report(c.status, kErrTimeout, 0, kPhasePipeline, stalled(2));
+            if (!ok) report(c.status, kErrTimeout, 0, kPhasePipeline, stalled(2, iters));
             tcgen05_fence_after();
         }
         if (c.stamps && threadIdx.x == 128) c.stamps[block * kStampSlots + 4] = globaltimer();

@@ -363,6 +363,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
             // of an item.
             const int q_items = g.stages / nkb, r_blocks = g.stages % nkb;
             volatile int* seen = sm->seen;
+            const bool guarded = (q_items & 1) || r_blocks != 0;  // otherwise a stage always belongs to the same issuer
             for (int i = block; i < n_items && alive; i += blocks, ++item) {
                 if ((item & 1) != who) {  // the other issuer's item: only step over its k-blocks in the ring
                     st += nkb;
@@ -379,7 +380,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
                     break;
                 }
                 for (int kb = 0; kb < nkb; ++kb, ++seq) {
-                    if (seq >= g.stages && ((kb >= r_blocks ? q_items : q_items + 1) & 1)) {
+                    if (guarded && seq >= g.stages && ((kb >= r_blocks ? q_items : q_items + 1) & 1)) {
                         while (alive && seen[1 - who] <= seq - g.stages) alive = globaltimer() <= deadline;
                     }
                     if (!alive || !mbar_wait(&sm->full[st], phase, deadline)) {
@@ -387,7 +388,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
                         alive = false;
                         break;
                     }
-                    seen[who] = seq + 1;
+                    if (guarded) seen[who] = seq + 1;
                     fence_proxy_async();  // the scale atoms were written through the generic proxy
                     tcgen05_fence_after();
                     const uint32_t base = stage0 + st * stage_bytes;

@@ -366,10 +366,9 @@ class Group:
         if st.code:
             self._failed = True
             where = f"rank slot {st.slot}, phase {st.phase}, invocation {st.epoch}"
-            if st.phase == 3 and st.epoch >> 24:  # the dense kernel's own pipeline: who gave up, and how far it had got
+            if st.phase == 3 and st.epoch >> 24:  # the dense kernel's own pipeline: who gave up, and at which k-block
                 who = ("producer", "MMA issuer", "epilogue", "split-K rendezvous")[(st.epoch >> 24) & 3]
-                where = (f"pipeline stage or split {st.slot}: {who} gave up; k-blocks loaded {st.epoch >> 16 & 255}, "
-                         f"issued {st.epoch >> 8 & 255} / {st.epoch & 255}")
+                where = f"pipeline stage or split {st.slot}: {who} gave up at k-block {st.epoch & 0xFFFF}"
             raise TimeoutError(f"rank {self.rank}: {_lib.lib().dlm_strerror(st.code).decode()} (block {st.block}, {where})")
 
     def all_reduce_(self, x):
