@@ -13,7 +13,7 @@
 // Work item = (active local expert, 128 output features): W2's [128 x F] slab sits on the MMA's M axis, the expert's
 // rows (tokens routed to it, padded to 16) on its N axis. Persistent CTAs take items round-robin:
 //   warp 0   TMA: per 256-element k-block the 16 KB code slab of W2 (one bulk copy of a pre-tiled slab, or one box)
-//            and the expert's activation rows (boxes of 8 rows)
+//   warp 12  TMA: the expert's activation rows of the k-block (boxes of 8 rows)
 //   warp 3   scale loader: W2's pre-interleaved 128 x 4 scale atoms and the activation rows' linear E4M3 scales,
 //            rewritten into the same atom layout, into the stage
 //   warp 1   per k-block: tcgen05.cp the scale atoms into tensor memory, then up to four
@@ -35,7 +35,7 @@ namespace dlm {
 
 namespace {
 
-constexpr int kMoeThreads = kFusedThreads;
+constexpr int kMoeThreads = kFusedThreads + 32;  // the dense kernel's twelve warps and a second producer
 constexpr int kCodeTileW = 128 * 128;  // 128 rows x 128 bytes (256 FP4) of W2 codes
 constexpr int kBoxRows = 8;            // activation rows per TMA box (one 1 KB swizzle atom)
 constexpr int kAtom = 512;             // one 128-row x 4-scale atom
@@ -301,6 +301,28 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
                                   kCodeTileW, &sm->full[st], kEvictFirst);
                     else
                         tma_load_2d(stage, &g.tm_w, &sm->full[st], kb * 128, t.e * g.n + t.ft * kBlockF, kEvictFirst);
+                    if (++st == g.stages) st = 0, phase ^= 1;
+                }
+            }
+        }
+        __syncwarp();  // lanes 1-31 must not run ahead to the block-wide barrier while lane 0 is still issuing
+    } else if (warp == 12) {
+        // Second producer: the expert's activation rows (boxes of 8 rows), so that the thread that requests the weight
+        // slabs has one copy per k-block to issue (config 5, several boxes per k-block: 47.9 instead of 49.5 us per
+        // layer; config 4: no change). It only adds bytes to a phase the weight producer announces.
+        if (lane == 0) {
+            int st = 0;
+            uint32_t phase = 1;
+            for (int i = block; i < n_items; i += blocks) {
+                const Item t = item_of(i);
+                const int boxes = (t.cnt + kBoxRows - 1) / kBoxRows;
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!mbar_wait(&sm->empty[st], phase, deadline)) {
+                        report(c.status, kErrTimeout, st, kPhasePipeline, 0);
+                        i = n_items;
+                        break;
+                    }
+                    uint8_t* stage = tiles + st * stage_bytes;
                     for (int b = 0; b < boxes; ++b)
                         tma_load_2d(stage + off_a + b * kBoxRows * 128, &g.tm_a, &sm->full[st], kb * 128,
                                     t.e * g.m_max + t.row0 + b * kBoxRows, kEvictLast);
@@ -308,7 +330,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
                 }
             }
         }
-        __syncwarp();  // lanes 1-31 must not run ahead to the block-wide barrier while lane 0 is still issuing
+        __syncwarp();
     } else if (warp == 3) {
         // Scale loader: asynchronous copies straight into the atoms, so it never waits for data and runs as far ahead
         // as the ring allows. Atom byte (r % 32) * 16 + (r / 32) * 4 + j holds scale j of row r (< 128).
@@ -422,7 +444,7 @@ __global__ void __launch_bounds__(kMoeThreads, 1) moe_kernel(const __grid_consta
             }
         }
         __syncwarp();
-    } else if (warp >= 4) {
+    } else if (warp >= 4 && warp < 12) {
         // Epilogue: lane = output feature of the tile, registers = the expert's rows.
         const int quarter = warp & 3, half = (warp - 4) >> 2;
         int item = 0;
