@@ -744,6 +744,36 @@ def run_moe(args, rig, link_gbs, workload, routing, steps):
     total, each = rig.timed(graph.replay, steps)
     clock_report = clocks.stop() if clocks else None
     group.check()
+    del graph
+
+    # The whole routed-expert call as a model makes it (trtllm_moe): per-token bookkeeping + input quantisation, GEMM1 +
+    # activation + re-quantisation, then the down-projection + combine deferred into the reduction: three launches per
+    # layer. Gate / up weights are random codes as well; the routing is the one above.
+    activation = "swiglu" if workload == "c4" else "geglu"
+    for ex in layer_experts:
+        s13 = torch.randint(0x28, 0x48, (e_local, 2 * f, hidden // 16), **u8)
+        ex.update(w13=nvfp4.tile_codes(torch.randint(0, 256, (e_local, 2 * f, hidden // 2), **u8)),
+                  s13=nvfp4.interleave_scales(s13), hidden=hidden, g1=torch.full((e_local,), 1e-4, device=device),
+                  a1_inv=torch.full((1,), 8.0, device=device), a2_inv=torch.full((e_local,), 8.0, device=device),
+                  group=group)
+    x = (torch.randn(rows, hidden, generator=torch.Generator().manual_seed(9)) * 0.5).to(torch.bfloat16).to(device)
+    packed = nvfp4.pack(t(ids), common["weights"]).contiguous()
+
+    def whole():
+        out = None
+        for i in range(layers):
+            p = nvfp4.trtllm_moe(x, packed, layer_experts[i], group.symmetric(f"{tag}.whole", (rows, hidden)), experts, lo,
+                                 f, activation=activation)
+            out = group.reduce(p, site=f"{tag}.{i}.whole", chain=tag + ".whole")
+        return out
+
+    graph, _, whole_launches = rig.capture(whole)
+    with torch.cuda.stream(rig.stream):
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+    whole_total, whole_each = rig.timed(graph.replay, steps)
+    group.check()
+    gate_up = active_max * 2 * f * hidden * 9 // 16
     weight = active_max * hidden * f * 9 // 16  # codes + E4M3 scales of the busiest rank's active experts
     per_launch = total / steps * 1e-3 / layers
     roof = roofline("moe_kernel", weight, reduction_bytes(world, rows, hidden), per_launch, link_gbs)
@@ -757,7 +787,14 @@ def run_moe(args, rig, link_gbs, workload, routing, steps):
                    f"step ({weight * layers / 1e6:.0f} MB on the busiest rank) " +
                    ("exceed the 126 MB L2" if weight * layers > 130e6 else "fit the L2: an L2-resident figure"),
                    "active_local_experts": active_max, "tp": world},
-        "gpu_launches": int(launches_per_step * steps), "roofline": roof, "clocks": clock_report}
+        "gpu_launches": int(launches_per_step * steps), "roofline": roof, "clocks": clock_report,
+        "whole_call": {"what": "trtllm_moe (routing bookkeeping + input quantisation, GEMM1 + activation + re-quantisation) "
+                               "followed by the reduction that runs the down-projection + combine: three launches per layer",
+                       "value": round(whole_total / steps * 1e3 / layers, 2), "unit": "us",
+                       "replay_us": spread(whole_each, layers), "launches_per_layer": whole_launches / layers,
+                       "weight_bytes_per_layer": int(gate_up + weight),
+                       "frac_of_hbm_peak": round((gate_up + weight) / (whole_total / steps * 1e-3 / layers) / 1e9 /
+                                                 peaks()[0], 4)}}
 
 
 # ---------------------------------------------------------------------------------------------------------------------
