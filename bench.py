@@ -21,7 +21,9 @@ reference measures a round (dlmrt/entrypoints/bench/common.py:68-80).
              run (a 256 MB copy out of a peer's memory, all ranks at once, CUDA events)
   parity     (N > 1) values checked on the real interconnect, outside the timed regions: identical bits on every rank,
              the CPU oracle, and the reference's own reduction kernel on the same partials; a mismatch exits non-zero
-  moe        the NVFP4 expert path of BASELINE configs 4 (uniform and Zipf(1.2) routing) and 5, timed the same way
+  moe        the NVFP4 expert path of BASELINE configs 4 (uniform and Zipf(1.2) routing) and 5, timed the same way:
+             `value` the down-projection + combine + reduction launch, `whole_call` the three launches of a whole routed
+             expert call (bookkeeping + input quantisation, GEMM1 + activation + re-quantisation, then that launch)
   round      a whole synthetic denoise round of the config-3 shape (36 layers: qkv / gate_up on cuBLAS, attention, the
              two fused projections, LM head + row statistics all-gather), median of the replays
   cpu_baseline / --impl reference   the CPU restatement of the same path (torch CPU matmul per K shard, rank-order FP32

@@ -20,6 +20,7 @@ namespace {
 constexpr int kPrepareThreads = 256;
 constexpr int kMaxTopK = 16;
 constexpr int kMaxHidden = 8192;
+constexpr int kMaxPairs = 256 * kMaxTopK;  // rows <= 256
 
 __device__ __forceinline__ float rcp_approx(float x) {
     float r;
@@ -49,12 +50,15 @@ __device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
 
 __global__ void __launch_bounds__(kPrepareThreads) moe_prepare_kernel(const __grid_constant__ PrepareDev p) {
     __shared__ int my_e[kMaxTopK], my_slot[kMaxTopK];
-    __shared__ int total;
+    __shared__ int expert_of[kMaxPairs];  // the whole routing, read once: both counts below scan it
     __shared__ __align__(16) uint8_t row_codes[kMaxHidden / 2];
     __shared__ __align__(16) uint8_t row_scales[kMaxHidden / 16];
     const int t = static_cast<int>(blockIdx.x), tid = static_cast<int>(threadIdx.x);
     const int k = p.top_k, pairs = p.rows * k;
     pdl_wait();  // the packed top-k and the input row come from the kernels before
+    // The experts' first GEMM may be set up from now on; it waits for this kernel before it reads the slots.
+    pdl_launch_dependents();
+    for (int i = tid; i < pairs; i += kPrepareThreads) expert_of[i] = p.packed[i] >> 16;
     if (tid < k) {
         const int word = p.packed[t * k + tid];
         my_e[tid] = word >> 16;
@@ -62,28 +66,21 @@ __global__ void __launch_bounds__(kPrepareThreads) moe_prepare_kernel(const __gr
         p.ids[t * k + tid] = word >> 16;
         p.weights[t * k + tid] = __uint_as_float(static_cast<uint32_t>(word & 0xFFFF) << 16);
     }
-    if (tid == 0) total = 0;
     __syncthreads();
     // Slot of each of this token's pairs: how many earlier pairs (lower token; a token lists an expert once) go to the
     // same expert. The count is a pure function of the routing, whatever order the threads add in.
     for (int i = tid; i < t * k; i += kPrepareThreads) {
-        const int e = p.packed[i] >> 16;
+        const int e = expert_of[i];
         for (int j = 0; j < k; ++j)
             if (e == my_e[j]) atomicAdd(&my_slot[j], 1);
     }
-    // This CTA also counts the rows of experts t, t + rows, ...
-    for (int e = t; e < p.e_total; e += p.rows) {
+    // This CTA also counts the rows of experts t, t + rows, ...: one warp per expert, no block-wide step.
+    for (int e = t + (tid >> 5) * p.rows; e < p.e_total; e += (kPrepareThreads / 32) * p.rows) {
         int mine = 0;
-        for (int i = tid; i < pairs; i += kPrepareThreads) mine += (p.packed[i] >> 16) == e;
+        for (int i = tid & 31; i < pairs; i += 32) mine += expert_of[i] == e;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffff, mine, o);
-        if ((tid & 31) == 0 && mine) atomicAdd(&total, mine);
-        __syncthreads();
-        if (tid == 0) {
-            p.counts[e] = total;
-            total = 0;
-        }
-        __syncthreads();
+        if ((tid & 31) == 0) p.counts[e] = mine;
     }
     // The token's row as NVFP4: quantised here, or copied from the caller's pre-quantised input.
     const int blocks16 = p.hidden / 16;
@@ -130,7 +127,6 @@ __global__ void __launch_bounds__(kPrepareThreads) moe_prepare_kernel(const __gr
         for (int i = tid; i < blocks16 / 16; i += kPrepareThreads)
             reinterpret_cast<uint4*>(p.slot_scales + dst * blocks16)[i] = reinterpret_cast<const uint4*>(row_scales)[i];
     }
-    pdl_launch_dependents();
 }
 
 // One token per CTA of one warp; lane l holds experts l, l + 32, ... (at most 256 experts).
