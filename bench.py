@@ -779,7 +779,8 @@ def run_moe(args, rig, link_gbs, workload, routing, steps):
     weight = active_max * hidden * f * 9 // 16  # codes + E4M3 scales of the busiest rank's active experts
     per_launch = total / steps * 1e-3 / layers
     roof = roofline("moe_kernel", weight, reduction_bytes(world, rows, hidden), per_launch, link_gbs)
-    roof["traffic"] = None
+    traffic = ROOT / "profiles" / "rowpar_kernel_traffic.json"  # ncu DRAM read + write per launch, where captured
+    roof["traffic"] = json.loads(traffic.read_text()).get(f"moe_{workload}_{routing}_tp{world}") if traffic.exists() else None
     return {
         "metric": "fused NVFP4 expert down-projection+combine+reduction latency per MoE layer",
         "value": round(per_launch * 1e6, 2), "unit": "us", "n_gpus": world, "steps": steps,
